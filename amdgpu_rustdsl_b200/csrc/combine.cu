@@ -1,0 +1,75 @@
+// fmha_fwd_hd128_mxfp8_v3_kvsplit_combine8h: merges the per-split partials of the KV-split attention into bf16 O.
+//
+// Reference: crates/amdgpu-kernels/src/fmha/io.rs:164-185 (kernel), crates/amdgpu-tile/src/epilogue.rs:89-167 (combine_splits).
+// Each thread owns 8 consecutive output elements of one row and walks the splits once with an online maximum:
+//   m' = max(m, lse_s); a = 2^(m - m'); w = 2^(lse_s - m'); den = den*a + w; acc_k = acc_k*a + w*Ohat_s[k]; out = acc/den -> bf16.
+// Partials here are f32 (the workspace contract sizes them for f32: tests/gpu/generated/..._kvsplit_abi.h:196), so one thread
+// reads 32 bytes per split as two 16-byte loads and writes one 16-byte store; a warp covers two whole rows (1 KiB per split).
+// HBM-bound: bytes = splits*rows*(512 + 4) + rows*256.
+#include "kernels.h"
+
+#include <cuda_bf16.h>
+
+namespace fmha {
+
+namespace {
+
+__device__ __forceinline__ float ex2f(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ float4 ld_stream(const float4* p) {
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+
+__global__ void __launch_bounds__(256)
+fmha_kvsplit_combine_kernel(const float* __restrict__ ohat, const float* __restrict__ lse2, uint8_t* __restrict__ out,
+                            uint32_t rows_total, uint32_t splits) {
+    const uint64_t ngroups = static_cast<uint64_t>(rows_total) * 16u;   // 16 groups of 8 elements per row
+    for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < ngroups; t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const uint64_t row = t >> 4;
+        float m = -1.0e30f, den = 0.0f;
+        float acc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
+        for (uint32_t s = 0; s < splits; ++s) {
+            const uint64_t prow = static_cast<uint64_t>(s) * rows_total + row;
+            const float ls = __ldg(lse2 + prow);
+            const float4* src = reinterpret_cast<const float4*>(ohat + (static_cast<uint64_t>(s) * rows_total * 16u + t) * 8u);
+            const float4 v0 = ld_stream(src), v1 = ld_stream(src + 1);
+            const float mn = fmaxf(m, ls);
+            const float a = ex2f(m - mn), w = ex2f(ls - mn);
+            den = den * a + w;
+            acc[0] = acc[0] * a + w * v0.x; acc[1] = acc[1] * a + w * v0.y; acc[2] = acc[2] * a + w * v0.z; acc[3] = acc[3] * a + w * v0.w;
+            acc[4] = acc[4] * a + w * v1.x; acc[5] = acc[5] * a + w * v1.y; acc[6] = acc[6] * a + w * v1.z; acc[7] = acc[7] * a + w * v1.w;
+            m = mn;
+        }
+        const float rd = 1.0f / den;
+        uint32_t wv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const __nv_bfloat162 b2 = __floats2bfloat162_rn(acc[2 * e] * rd, acc[2 * e + 1] * rd);
+            wv[e] = *reinterpret_cast<const uint32_t*>(&b2);
+        }
+        *reinterpret_cast<uint4*>(out + t * 16u) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_combine(const float* ohat, const float* lse2, uint8_t* out, uint32_t rows_total, uint32_t splits, cudaStream_t stream) {
+    const uint64_t ngroups = static_cast<uint64_t>(rows_total) * 16u;
+    uint64_t blocks = (ngroups + 255u) / 256u;
+    // cap the grid at a few waves of 148 SMs x 8 resident blocks; the grid-stride loop covers the rest
+    const uint64_t cap = 148u * 8u * 4u;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    fmha_kvsplit_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(ohat, lse2, out, rows_total, splits);
+    return cudaGetLastError();
+}
+
+}  // namespace fmha

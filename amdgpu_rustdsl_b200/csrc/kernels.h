@@ -1,0 +1,42 @@
+// Internal interface between the C-ABI host layer (host_api.cu) and the kernel translation units.
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace fmha {
+
+// Everything one attention launch needs, already decoded from the packed kernel arguments.
+struct AttnParams {
+    // outputs
+    uint8_t* o;            // bf16 [B,S,H,128] (unsplit)
+    float* ohat;           // f32 [splits][rows_total][128] (split)
+    float* lse2;           // f32 [splits][rows_total], base-2 (split)
+    float* lse_nat;        // optional f32 [B,H,S], natural log (unsplit), may be null
+    // scale inputs
+    const uint8_t* q_descale;   // E8M0 [B,S,H,4]
+    const uint8_t* k_descale;   // E8M0 [B,SK,HK,4]
+    const float* v_descale;     // one f32
+    const uint8_t* v_blockscale;  // extension: E8M0 [B,ceil(SK/32),HK,128], may be null
+    // shape
+    uint32_t S, SK, H, HK, gqa_shift;
+    uint32_t o_row_stride, o_batch_stride;    // bytes
+    uint32_t qs_batch_stride, ks_batch_stride;  // bytes
+    uint32_t splits, split_log2, rows_total;
+    uint32_t flags;
+    // diagnostics
+    float* trace;          // may be null
+    uint32_t* status;      // device status word
+};
+
+// rows_per_cta is 128 (t128) or 256 (vs128 / kvsplit): the logical block height of the reference's grids.
+cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const AttnParams& p,
+                             uint32_t B, bool split, uint32_t rows_per_cta, cudaStream_t stream);
+
+cudaError_t launch_combine(const float* ohat, const float* lse2, uint8_t* out, uint32_t rows_total, uint32_t splits, cudaStream_t stream);
+
+cudaError_t launch_mma_probe(int variant, int iters, int ctas, uint32_t* status, cudaStream_t stream);
+
+uint32_t* device_status_word();   // address of the per-device status word (device pointer)
+
+}  // namespace fmha

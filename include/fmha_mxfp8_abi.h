@@ -1,0 +1,300 @@
+/*
+ * C ABI of the B200 (sm_100a) implementation of the MXFP8 attention forward path, head dim 128:
+ * the four kernels fmha_fwd_hd128_mxfp8_v3_{vs128, t128, kvsplit, kvsplit_combine8h} and the
+ * shape-based dispatch that selects between them.
+ *
+ * The structs below are byte-for-byte the packed kernel-argument blocks that the reference's
+ * `amdc gen-host` emits (tests/gpu/generated/fmha_fwd_hd128_mxfp8_v3_*_abi.h), so a caller that
+ * fills the reference's `Args` can pass the same bytes here. Everything is plain C: pointers,
+ * integers, no C++ or framework types. All device pointers are CUDA device pointers owned by the
+ * caller; nothing in this library allocates device memory on the launch path.
+ *
+ * Return codes of every function that returns int: 0 = ok; > 0 = a host-contract class
+ * (FMHA_MXFP8_E_*); < 0 = minus a cudaError_t / CUresult value.
+ */
+#ifndef FMHA_MXFP8_ABI_H
+#define FMHA_MXFP8_ABI_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Kernel ids, in the order of the reference's shipped list (crates/amdgpu-graph/src/dispatch.rs:513-519). */
+enum fmha_mxfp8_kernel {
+    FMHA_MXFP8_VS128 = 0,     /* fmha_fwd_hd128_mxfp8_v3_vs128: 256 query rows per logical block */
+    FMHA_MXFP8_T128 = 1,      /* fmha_fwd_hd128_mxfp8_v3_t128: 128 query rows per logical block */
+    FMHA_MXFP8_KVSPLIT = 2,   /* fmha_fwd_hd128_mxfp8_v3_kvsplit: key range split over grid z, writes partials */
+    FMHA_MXFP8_COMBINE8H = 3  /* fmha_fwd_hd128_mxfp8_v3_kvsplit_combine8h: merges the partials */
+};
+
+/* Host-contract failure classes: the reference's GV-HOST-* codes (…_kvsplit_abi.h:186-226). */
+enum fmha_mxfp8_error {
+    FMHA_MXFP8_OK = 0,
+    FMHA_MXFP8_E_EXTENT = 1,   /* GV-HOST-EXTENT   */
+    FMHA_MXFP8_E_KA_RANGE = 2, /* GV-HOST-KA-RANGE */
+    FMHA_MXFP8_E_KA_IS = 3,    /* GV-HOST-KA-IS    */
+    FMHA_MXFP8_E_GRID = 4,     /* GV-HOST-GRID     */
+    FMHA_MXFP8_E_SYM = 5,      /* GV-HOST-SYM      */
+    FMHA_MXFP8_E_ARG = 6,      /* bad kernel id / null pointer (no reference counterpart) */
+    FMHA_MXFP8_E_DEVICE = 7    /* a kernel reported a bounded wait that ran out (see fmha_mxfp8_device_status) */
+};
+
+/* Bits of `ext_flags` (offset 0x058, padding in the reference's Args, so 0 = reference behaviour). */
+#define FMHA_MXFP8_FLAG_V_BLOCKSCALE 0x1u /* V carries one E8M0 per 32 keys per column at ext_ptr_v_blockscale (extension) */
+#define FMHA_MXFP8_FLAG_EXACT_REBASE 0x2u /* move the softmax reference on every tile (the short-sequence recipe) for any length */
+
+#pragma pack(push, 1)
+/*
+ * Kernel arguments of vs128 and t128: replaces amdc_hostgen::fmha_fwd_hd128_mxfp8_v3_vs128::Args
+ * (tests/gpu/generated/fmha_fwd_hd128_mxfp8_v3_vs128_abi.h:10-66; t128 is identical, …_t128_abi.h:10-66). 656 bytes.
+ * The three `ext_` fields live in bytes that are padding (`_pad3`, 0x038-0x05F) in the reference struct.
+ */
+typedef struct fmha_mxfp8_attn_args {
+    void* ptr_o;                 /* 0x000 bf16 O [B,S,H,128] */
+    uint8_t _pad0[8];
+    void* ptr_q;                 /* 0x010 e4m3 Q [B,S,H,128] */
+    uint8_t _pad1[8];
+    void* ptr_k;                 /* 0x020 e4m3 K [B,SK,HK,128] */
+    uint8_t _pad2[8];
+    void* ptr_v;                 /* 0x030 e4m3 V [B,SK,HK,128] */
+    uint8_t _pad3a[8];
+    void* ext_ptr_lse;           /* 0x040 optional f32 [B,H,S] natural-log LSE output; NULL = not written */
+    void* ext_ptr_v_blockscale;  /* 0x048 optional E8M0 [B,ceil(SK/32),HK,128] V block scales (FMHA_MXFP8_FLAG_V_BLOCKSCALE) */
+    uint8_t _pad3b[8];           /* 0x050 the vendor ABI's f32 softmax scale; never read (the scale is folded into Q) */
+    uint32_t ext_flags;          /* 0x058 */
+    uint8_t _pad3c[4];
+    uint32_t s_seq_len;          /* 0x060 S */
+    uint8_t _pad4[12];
+    uint32_t s_Seqs;             /* 0x070 Q row stride in bytes = H*128 */
+    uint8_t _pad5[28];
+    uint32_t s_Hs;               /* 0x090 = 128 */
+    uint8_t _pad6[12];
+    uint32_t s_Bs;               /* 0x0A0 Q batch stride = S*H*128 */
+    uint8_t _pad7[12];
+    uint32_t s_gqa;              /* 0x0B0 H / HK, power of two in 1..16 */
+    uint8_t _pad8[12];
+    uint32_t s_k_Seqs;           /* 0x0C0 = HK*128 */
+    uint8_t _pad9[12];
+    uint32_t s_k_Hs;             /* 0x0D0 = 128 */
+    uint8_t _pad10[12];
+    uint32_t s_k_Bs;             /* 0x0E0 = SK*HK*128 */
+    uint8_t _pad11[44];
+    uint32_t s_kv_seq_len;       /* 0x110 SK */
+    uint8_t _pad12[44];
+    uint32_t s_q_head_num;       /* 0x140 H */
+    uint8_t _pad13[12];
+    uint32_t s_v_Seqs;           /* 0x150 */
+    uint8_t _pad14[12];
+    uint32_t s_v_Hs;             /* 0x160 */
+    uint8_t _pad15[12];
+    uint32_t s_v_Bs;             /* 0x170 */
+    uint8_t _pad16[12];
+    uint32_t s_o_Seqs;           /* 0x180 = H*256 */
+    uint8_t _pad17[12];
+    uint32_t s_o_Hs;             /* 0x190 = 256 */
+    uint8_t _pad18[12];
+    uint32_t s_o_Bs;             /* 0x1A0 = S*H*256 */
+    uint8_t _pad19[92];
+    void* ptr_q_descale;         /* 0x200 E8M0 [B,S,H,4] (+ 2048*H bytes of slack) */
+    uint8_t _pad20[8];
+    void* ptr_k_descale;         /* 0x210 E8M0 [B,SK,HK,4] (+ 2560*H bytes of slack) */
+    uint8_t _pad21[8];
+    void* ptr_v_descale;         /* 0x220 one f32 in a buffer of >= 4096 bytes */
+    uint8_t _pad22[8];
+    uint32_t s_descale_q_Bs;     /* 0x230 = S*H*4 */
+    uint8_t _pad23[12];
+    uint32_t s_descale_q_Hs;     /* 0x240 = 4 */
+    uint8_t _pad24[12];
+    uint32_t s_descale_k_Bs;     /* 0x250 = SK*HK*4 */
+    uint8_t _pad25[12];
+    uint32_t s_descale_k_Hs;     /* 0x260 = 4 */
+    uint8_t _pad26[28];
+    uint8_t abi_tail[16];        /* 0x280 */
+} fmha_mxfp8_attn_args;
+
+/*
+ * Kernel arguments of kvsplit: replaces amdc_hostgen::fmha_fwd_hd128_mxfp8_v3_kvsplit::Args
+ * (tests/gpu/generated/fmha_fwd_hd128_mxfp8_v3_kvsplit_abi.h:10-72). 648 bytes; same as above up to 0x26F.
+ */
+typedef struct fmha_mxfp8_kvsplit_args {
+    void* ptr_o;
+    uint8_t _pad0[8];
+    void* ptr_q;
+    uint8_t _pad1[8];
+    void* ptr_k;
+    uint8_t _pad2[8];
+    void* ptr_v;
+    uint8_t _pad3a[8];
+    void* ext_ptr_lse;           /* unused by kvsplit */
+    void* ext_ptr_v_blockscale;
+    uint8_t _pad3b[8];
+    uint32_t ext_flags;
+    uint8_t _pad3c[4];
+    uint32_t s_seq_len;
+    uint8_t _pad4[12];
+    uint32_t s_Seqs;
+    uint8_t _pad5[28];
+    uint32_t s_Hs;
+    uint8_t _pad6[12];
+    uint32_t s_Bs;
+    uint8_t _pad7[12];
+    uint32_t s_gqa;
+    uint8_t _pad8[12];
+    uint32_t s_k_Seqs;
+    uint8_t _pad9[12];
+    uint32_t s_k_Hs;
+    uint8_t _pad10[12];
+    uint32_t s_k_Bs;
+    uint8_t _pad11[44];
+    uint32_t s_kv_seq_len;
+    uint8_t _pad12[44];
+    uint32_t s_q_head_num;
+    uint8_t _pad13[12];
+    uint32_t s_v_Seqs;
+    uint8_t _pad14[12];
+    uint32_t s_v_Hs;
+    uint8_t _pad15[12];
+    uint32_t s_v_Bs;
+    uint8_t _pad16[12];
+    uint32_t s_o_Seqs;
+    uint8_t _pad17[12];
+    uint32_t s_o_Hs;
+    uint8_t _pad18[12];
+    uint32_t s_o_Bs;
+    uint8_t _pad19[92];
+    void* ptr_q_descale;
+    uint8_t _pad20[8];
+    void* ptr_k_descale;
+    uint8_t _pad21[8];
+    void* ptr_v_descale;
+    uint8_t _pad22[8];
+    uint32_t s_descale_q_Bs;
+    uint8_t _pad23[12];
+    uint32_t s_descale_q_Hs;
+    uint8_t _pad24[12];
+    uint32_t s_descale_k_Bs;
+    uint8_t _pad25[12];
+    uint32_t s_descale_k_Hs;
+    uint8_t _pad26[12];
+    void* ptr_ohat;              /* 0x270 f32 partial O, [splits][rows_total][128], normalised per split */
+    void* ptr_lse;               /* 0x278 f32 base-2 log-sum-exp, [splits][rows_total] */
+    uint32_t kvs_splits;         /* 0x280 2, 4 or 8 (1 is accepted) */
+    uint32_t kvs_rows_total;     /* 0x284 B*S*H */
+} fmha_mxfp8_kvsplit_args;
+
+/*
+ * Kernel arguments of the combine kernel: replaces amdc_hostgen::fmha_fwd_hd128_mxfp8_v3_kvsplit_combine8h::Args
+ * (tests/gpu/generated/fmha_fwd_hd128_mxfp8_v3_kvsplit_combine8h_abi.h:10-19). 36 bytes.
+ */
+typedef struct fmha_mxfp8_combine_args {
+    void* ptr_ohat;      /* 0x00 */
+    void* ptr_lse;       /* 0x08 */
+    void* ptr_out;       /* 0x10 bf16 [rows_total][128] */
+    uint32_t rows_total; /* 0x18 */
+    uint32_t d;          /* 0x1C = 128 */
+    uint32_t splits;     /* 0x20 */
+} fmha_mxfp8_combine_args;
+#pragma pack(pop)
+
+/* Contract symbols: replaces the per-kernel `Symbols` structs (…_kvsplit_abi.h:137-141). */
+typedef struct fmha_mxfp8_symbols {
+    int64_t B;  /* batch (kvsplit only; the unsplit kernels take the batch from grid z) */
+    int64_t HK; /* KV heads */
+    int64_t KL; /* free symbol of the reference's verifier; only its range (>= 0) is checked */
+} fmha_mxfp8_symbols;
+
+/* Allocation sizes in bytes of the caller's buffers: replaces the per-kernel `BufferSizes` structs (…_kvsplit_abi.h:142-152, …_combine8h_abi.h:36-40). */
+typedef struct fmha_mxfp8_buffer_sizes {
+    uint64_t ptr_q, ptr_k, ptr_v, ptr_o;
+    uint64_t ptr_q_descale, ptr_k_descale, ptr_v_descale;
+    uint64_t ptr_ohat, ptr_lse; /* kvsplit, combine */
+    uint64_t ptr_out;           /* combine */
+} fmha_mxfp8_buffer_sizes;
+
+/* Name / kernarg size / reference workgroup size of a kernel id (…_abi.json "kernel", "kernarg_size", "workgroup_size"). */
+const char* fmha_mxfp8_kernel_name(int kernel);
+size_t fmha_mxfp8_kernarg_size(int kernel);
+unsigned fmha_mxfp8_workgroup_size(int kernel);
+
+/*
+ * Host-contract check: replaces `validate(const Args&, const BufferSizes&, dim3 grid, const Symbols&, std::string* err)`
+ * (…_vs128_abi.h:170-204, …_kvsplit_abi.h:186-226, …_combine8h_abi.h:56-66). Same checks in the same order; on the first
+ * failure writes "<GV-HOST-CODE>: <message>" into err (if non-NULL, NUL-terminated, at most cap bytes) and returns the class.
+ * `grid` is the reference's logical grid: (ceil(S/256 or 128), H, B or B*splits); the combine kernel's grid is not checked.
+ */
+int fmha_mxfp8_validate(int kernel, const void* args, const fmha_mxfp8_buffer_sizes* sizes, const uint32_t grid[3],
+                        const fmha_mxfp8_symbols* syms, char* err, size_t cap);
+
+/* The logical grid a kernel expects: replaces `grid(const Args&, const Symbols&)` (…_kvsplit_abi.h:234) and, for the combine
+ * kernel, ceil(rows_total*128 / (256*8)) (tests/gpu/ref_host.cpp:510-515). */
+int fmha_mxfp8_grid(int kernel, const void* args, const fmha_mxfp8_symbols* syms, uint32_t grid[3]);
+
+/*
+ * Enqueue one kernel on a CUDA stream: replaces `launch(hipFunction_t, const Args&, dim3 grid, dim3 block, size_t lds, hipStream_t)`
+ * (…_vs128_abi.h:205-210). `grid` is the logical grid above; the physical CTA grid is this library's business. `args` is read
+ * before the call returns. `stream` is a cudaStream_t (NULL = default stream). Does not validate: call fmha_mxfp8_validate first.
+ */
+int fmha_mxfp8_launch(int kernel, const void* args, const uint32_t grid[3], void* stream);
+
+/*
+ * Shape -> path: replaces `mxfp8_prefill_path(b, h, s, sk) -> (path, splits)` (crates/amdgpu-graph/src/dispatch.rs:494-511,
+ * mirrored in tests/gpu/ref_host.cpp:124-155). *path is FMHA_MXFP8_VS128, _T128 or _KVSPLIT; *splits is 0, 2 or 4.
+ */
+void fmha_mxfp8_dispatch(uint64_t b, uint64_t h, uint64_t s, uint64_t sk, int* path, uint32_t* splits);
+
+/* Tensors and workspaces of one forward call, all device pointers, packed BSHD as the contract demands. */
+typedef struct fmha_mxfp8_problem {
+    uint32_t B, H, HK, S, SK;
+    const void* q;          /* e4m3 [B,S,H,128] */
+    const void* k;          /* e4m3 [B,SK,HK,128] */
+    const void* v;          /* e4m3 [B,SK,HK,128] */
+    const void* q_descale;  /* E8M0 [B,S,H,4]   + slack, q_descale_bytes in total */
+    const void* k_descale;  /* E8M0 [B,SK,HK,4] + slack, k_descale_bytes in total */
+    const void* v_descale;  /* f32, v_descale_bytes >= 4096 */
+    void* out;              /* bf16 [B,S,H,128] */
+    uint64_t q_descale_bytes, k_descale_bytes, v_descale_bytes;
+    void* ws_ohat;          /* kvsplit workspace, >= splits*B*S*H*512 bytes (may be NULL when the path is not kvsplit) */
+    void* ws_lse;           /* kvsplit workspace, >= splits*B*S*H*4 bytes */
+    uint64_t ws_ohat_bytes, ws_lse_bytes;
+    const void* v_blockscale; /* NULL, or the extension's per-32-key V scales (sets FMHA_MXFP8_FLAG_V_BLOCKSCALE) */
+    uint32_t flags;         /* extra FMHA_MXFP8_FLAG_* bits */
+} fmha_mxfp8_problem;
+
+/*
+ * The whole default path `fmha_fwd_hd128_mxfp8_auto`: dispatch (or a forced path), fill the Args, validate, launch (kvsplit: both
+ * kernels, same stream). Mirrors python/amdgpu_jit/ops.py:88-143 (`fmha_fwd_mxfp8`) and tests/gpu/ref_host.cpp:342-397,516-569.
+ * path: -1 = auto, else FMHA_MXFP8_VS128 / _T128 / _KVSPLIT; splits: used when path is _KVSPLIT (2, 4 or 8; 0 = 4).
+ * On return *path_out / *splits_out (if non-NULL) hold what ran. Allocates nothing.
+ */
+int fmha_mxfp8_auto(const fmha_mxfp8_problem* prob, int path, uint32_t splits, void* stream, int* path_out, uint32_t* splits_out,
+                    char* err, size_t cap);
+
+/*
+ * Device status word: 0 when no kernel of this library ever gave up a bounded wait on the current device, else a bit mask of the
+ * roles that did. Synchronises the device. No counterpart in the reference (its kernels have no bounded waits); it stands where
+ * the reference harness checks hipDeviceSynchronize() after a launch (tests/gpu/ref_host.cpp:400).
+ */
+int fmha_mxfp8_device_status(uint32_t* status);
+
+/*
+ * Diagnostics hook in the spirit of the reference's stamp buffer (docs/stamps.md): when a device buffer of at least
+ * FMHA_MXFP8_TRACE_BYTES is attached, logical block (0,0,0) of the next attention launches records its first score tile, the
+ * unnormalised O, the row sums and the row references there. Pass NULL to detach.
+ */
+#define FMHA_MXFP8_TRACE_BYTES (4u * (16384u + 16384u + 256u + 4096u))
+int fmha_mxfp8_trace_attach(void* dev_buf, size_t bytes);
+
+/*
+ * Issue-only ceiling of the tensor pipe: every CTA issues `iters` x 4 tcgen05.mma (M128 N128 K32, e4m3) back to back on resident
+ * operands. variant 0 = block-scaled, A from shared memory; 1 = block-scaled, A from tensor memory; 2 = kind::f8f6f4, A from
+ * tensor memory. Writes the elapsed milliseconds (CUDA events on `stream`) and returns 0. Used for the roofline denominator.
+ */
+int fmha_mxfp8_probe_mma_peak(int variant, int iters, int ctas, void* stream, float* ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FMHA_MXFP8_ABI_H */
