@@ -15,7 +15,7 @@ PATH_NAMES = {VS128: "vs128", T128: "t128", KVSPLIT: "kvsplit"}
 PATH_IDS = {v: k for k, v in PATH_NAMES.items()}
 FLAG_V_BLOCKSCALE = 0x1
 FLAG_EXACT_REBASE = 0x2
-TRACE_BYTES = 4 * (16384 + 16384 + 256 + 4096)
+TRACE_BYTES = 4 * (16384 + 16384 + 256 + 4096 + 2048)
 
 ERROR_CLASSES = {1: "GV-HOST-EXTENT", 2: "GV-HOST-KA-RANGE", 3: "GV-HOST-KA-IS", 4: "GV-HOST-GRID", 5: "GV-HOST-SYM", 6: "ARG", 7: "DEVICE"}
 

@@ -12,14 +12,19 @@
 //            log-sum-exp per row (block3.rs:291-356).
 //
 // Mapping onto the SM (not a translation of the gfx950 wave layout):
-//   warps 0-3  softmax + epilogue: thread r owns query row r = TMEM lane r; reads S with tcgen05.ld, writes P (packed e4m3)
-//              back into the first 32 columns of the same S buffer with tcgen05.st, rescales O in TMEM when its reference moves.
-//   warp  4    MMA issuer: one lane issues tcgen05.mma; S = Q K^T is kind::mxf8f6f4.block_scale with both operands in swizzled
+//   warps 4-11 softmax + epilogue, two warpgroups that take alternate key tiles (warpgroup w owns tiles j = w mod 2), so that one
+//              group's TMEM round trips overlap the other group's arithmetic. Thread r of either group owns query row r = TMEM
+//              lane r: it reads the whole score row with tcgen05.ld and hands the S buffer back at once, takes the row's reference
+//              from the thread that handled the previous tile (one 8-byte shared-memory slot per row), writes P (packed e4m3) to
+//              the group's own P columns with tcgen05.st, and rescales O in TMEM when the reference moves.
+//   warp  0    MMA issuer: one lane issues tcgen05.mma; S = Q K^T is kind::mxf8f6f4.block_scale with both operands in swizzled
 //              shared memory and the E8M0 factors in TMEM (tcgen05.cp); O += P V takes P from TMEM and V (keys x head dim, i.e.
-//              MN-major B) from shared memory. S is double buffered so Q K^T of tile j+1 overlaps the softmax of tile j.
-//   warp  5    producer: TMA loads of the Q tile and of the K/V tiles into a ring, plus the 4-byte-per-row scale gathers, which
+//              MN-major B) from shared memory; L += P 1 (a 16-column MMA against a tile of e4m3 ones) is the row sum of the
+//              quantised P, which costs no ALU work (the reference sums P with a matrix instruction too, reduce.rs:163-173).
+//              Issue order QK(0) QK(1) | QK(j+2) PV(j) ...: two score tiles are always ahead of the softmax.
+//   warp  1    producer: TMA loads of the Q tile and of the K/V tiles into a ring, plus the 4-byte-per-row scale gathers, which
 //              a TMA box cannot express, written in the 32x16-byte layout tcgen05.cp expects.
-// TMEM columns: S0 [0,128) S1 [128,256) O [256,384) SFQ [384,388) SFK0 [388,392) SFK1 [392,396) SFP [396,400) SFV [400,404).
+// TMEM columns: S0 [0,128) S1 [128,256) O [256,384) L [384,400) P0 [400,432) P1 [432,464) SFQ [464,468) SFK0 [468,472) SFK1 [472,476).
 #include "kernels.h"
 #include "ptx_sm100.cuh"
 
@@ -33,29 +38,44 @@ namespace {
 
 constexpr int kRows = 128;          // query rows per CTA tile
 constexpr int kKeys = 128;          // keys per tile
-constexpr int kStages = 3;          // K/V ring depth
-constexpr int kThreads = 192;
+constexpr int kStages = 5;          // depth of the K ring and of the V ring (freed separately: K after Q K^T, V after P V)
+constexpr int kSoftmaxThreads = 256;
+// The two single-lane service warps get the lowest warp ids: the warp schedulers favour older warps, and a service warp that polls behind
+// two arithmetic-dense softmax warps on its scheduler is otherwise only issued when they stall. Warps 2-3 idle; softmax = warps 4-11.
+constexpr int kMmaWarp = 0, kProducerWarp = 1, kFirstSoftmaxWarp = 4;
+constexpr int kThreads = 384;
 constexpr uint32_t kTileBytes = 128 * 128;   // one e4m3 tile
 constexpr uint32_t kSfBytes = 512;           // 128 rows x 4 scale bytes
 
-constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256, kColSfQ = 384, kColSfK0 = 388, kColSfK1 = 392;
+constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256, kColL = 384, kColP0 = 400, kColP1 = 432, kColSfQ = 464, kColSfK0 = 468, kColSfK1 = 472;
 constexpr uint32_t kTmemCols = 512;
 
-// P = 2^(s - ref + kPOffset): the reference row maximum maps to 2^kPOffset, and the reference is left alone while the running
-// maximum stays within kLazyThreshold binades of it, so P <= 2^(5 + 3.5) = 362 < 448 never saturates e4m3.
+// P = 2^(s - ref + kPOffset): the row's reference maps to 2^kPOffset.
+// Long sequences (>= 4 key tiles): the reference is an integer, ceil(tile maximum), and is left alone while a tile's maximum stays
+// within kLazyThreshold binades above it, so P <= 2^(5 + 3.5) = 362 < 448 never saturates e4m3. Integer references make every
+// rescale an exact power of two, so the same keys give the same P mantissas whatever the reference: a KV split and the unsplit
+// kernel then differ only by f32 summation order.
+// Short sequences move the reference to the tile's own maximum on every tile whose maximum is less than kFollowWindow binades
+// below it (so every tile's largest P is exactly 2^kPOffset, which is what keeps the error on sharply peaked rows at the level of
+// the reference's short-sequence recipe: thr 120/512 vs target 131/512, crates/amdgpu-tile/src/softmax.rs:26-30).
 constexpr float kPOffset = 5.0f;
 constexpr float kLazyThreshold = 3.5f;
+constexpr float kFollowWindow = 11.0f;
 
 struct SmemLayout {
     // all tile buffers are 1024-byte aligned (128-byte swizzle atom = 8 rows x 128 B)
     static constexpr uint32_t q = 0;
     static constexpr uint32_t k = q + kTileBytes;
     static constexpr uint32_t v = k + kStages * kTileBytes;
-    static constexpr uint32_t sfq = v + kStages * kTileBytes;
+    // 32 keys x 128 B of e4m3 1.0 behind the V ring: a second MN-major atom of the P V B operand, of which the MMA uses 16 columns,
+    // so that O[:, 128..143] accumulates the row sums of P
+    static constexpr uint32_t ones = v + kStages * kTileBytes;
+    static constexpr uint32_t sfq = ones + 4096;
     static constexpr uint32_t sfk = sfq + kSfBytes;
-    static constexpr uint32_t bars = sfk + kStages * kSfBytes;
-    // barriers (8 bytes each): q_full, kv_full[kStages], kv_empty[kStages], s_full[2], p_full[2], o_done
-    static constexpr uint32_t n_bars = 1 + 2 * kStages + 2 + 2 + 1;
+    static constexpr uint32_t xref = sfk + kStages * kSfBytes;   // [tile parity 2][row 128] x {reference bits, tile index}
+    static constexpr uint32_t bars = xref + 2 * 128 * 8;
+    // barriers (8 bytes each): q_full, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], s_free[2], p_full[2], o_done[2]
+    static constexpr uint32_t n_bars = 1 + 4 * kStages + 8;
     static constexpr uint32_t tmem_slot = bars + 8 * n_bars;
     static constexpr uint32_t abort_flag = tmem_slot + 4;
     static constexpr uint32_t total = abort_flag + 4;
@@ -72,16 +92,50 @@ __device__ __forceinline__ float lg2_approx(float x) {
     asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float y;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+    return y;
+}
 
 // Two floats -> two e4m3 bytes (round to nearest even, saturating), `a` in the low byte.
 __device__ __forceinline__ uint32_t cvt_e4m3x2(float a, float b) {
-    return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3));
+    uint16_t h;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(h) : "f"(b), "f"(a));
+    return static_cast<uint32_t>(h);
 }
-// Sum of the two e4m3 values of a packed pair, as f32.
-__device__ __forceinline__ float sum_e4m3x2(uint32_t pair) {
-    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(pair), __NV_E4M3);
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
-    return f.x + f.y;
+
+// Four scores -> one 32-bit word of four e4m3 P values, key order = byte order.
+__device__ __forceinline__ uint32_t p_word(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t s3, float sh) {
+    const uint32_t lo = cvt_e4m3x2(ex2_approx(__uint_as_float(s0) + sh), ex2_approx(__uint_as_float(s1) + sh));
+    const uint32_t hi = cvt_e4m3x2(ex2_approx(__uint_as_float(s2) + sh), ex2_approx(__uint_as_float(s3) + sh));
+    return lo | (hi << 16);
+}
+
+__device__ __forceinline__ void st_shared_v2(uint32_t addr, uint32_t a, uint32_t b) {
+    asm volatile("st.volatile.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ uint2 ld_shared_v2(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.volatile.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
+    return v;
+}
+
+// Time stamps of logical block (0,0,0) for the first 32 key tiles (the analogue of the reference's in-kernel stamp buffer,
+// docs/stamps.md): [role 4: softmax group 0, 1, score MMAs, P V MMAs][tile 32][slot 8] 64-bit SM clock values behind the first 37120 words of the trace buffer.
+constexpr int kStampBase = 37120;
+__device__ __forceinline__ void stamp(float* trace, int role, int tile, int slot) {
+    if (trace != nullptr && tile < 32) reinterpret_cast<long long*>(trace + kStampBase)[(role * 32 + tile) * 8 + slot] = clock64();
+}
+
+// O columns [col, col + 32) of this thread's lane *= f
+__device__ __forceinline__ void scale_tmem32(uint32_t taddr, float f) {
+    uint32_t o[32];
+    tmem_ld32(taddr, o);
+    tmem_wait_ld();
+#pragma unroll
+    for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f);
+    tmem_st32(taddr, o);
 }
 
 }  // namespace
@@ -97,15 +151,19 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const uint32_t q_smem = smem_base + SmemLayout::q;
     const uint32_t k_smem = smem_base + SmemLayout::k;
     const uint32_t v_smem = smem_base + SmemLayout::v;
+    const uint32_t ones_smem = smem_base + SmemLayout::ones;
     const uint32_t sfq_smem = smem_base + SmemLayout::sfq;
     const uint32_t sfk_smem = smem_base + SmemLayout::sfk;
     const uint32_t bar0 = smem_base + SmemLayout::bars;
     const uint32_t bar_q_full = bar0;
-    auto bar_kv_full = [&](int st) { return bar0 + 8u * (1 + st); };
-    auto bar_kv_empty = [&](int st) { return bar0 + 8u * (1 + kStages + st); };
-    auto bar_s_full = [&](int b) { return bar0 + 8u * (1 + 2 * kStages + b); };
-    auto bar_p_full = [&](int b) { return bar0 + 8u * (3 + 2 * kStages + b); };
-    const uint32_t bar_o_done = bar0 + 8u * (5 + 2 * kStages);
+    auto bar_k_full = [&](int st) { return bar0 + 8u * (1 + st); };
+    auto bar_k_empty = [&](int st) { return bar0 + 8u * (1 + kStages + st); };
+    auto bar_v_full = [&](int st) { return bar0 + 8u * (1 + 2 * kStages + st); };
+    auto bar_v_empty = [&](int st) { return bar0 + 8u * (1 + 3 * kStages + st); };
+    auto bar_s_full = [&](int b) { return bar0 + 8u * (1 + 4 * kStages + b); };
+    auto bar_s_free = [&](int b) { return bar0 + 8u * (3 + 4 * kStages + b); };
+    auto bar_p_full = [&](int b) { return bar0 + 8u * (5 + 4 * kStages + b); };
+    auto bar_o_done = [&](int b) { return bar0 + 8u * (7 + 4 * kStages + b); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + SmemLayout::tmem_slot);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + SmemLayout::abort_flag);
 
@@ -132,28 +190,37 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const int n_tiles = (key_hi > key_lo) ? static_cast<int>((key_hi - key_lo + kKeys - 1) / kKeys) : 0;
     // the recipe is chosen from the whole sequence's tile count, also in a split (block3.rs:180-184)
     const bool lazy = (ntiles_total >= 4) && !(p.flags & 0x2u);
-    const float thr = lazy ? kLazyThreshold : 0.0f;
+    const float thr = lazy ? kLazyThreshold : -kFollowWindow;
 
     // ---- one-time setup ----
     if (threadIdx.x == 0) {
         *abort_flag = 0u;
         mbar_init(bar_q_full, 1);
         for (int st = 0; st < kStages; ++st) {
-            mbar_init(bar_kv_full(st), 1);
-            mbar_init(bar_kv_empty(st), 1);
+            mbar_init(bar_k_full(st), 1);
+            mbar_init(bar_k_empty(st), 1);
+            mbar_init(bar_v_full(st), 1);
+            mbar_init(bar_v_empty(st), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_s_full(b), 1);
+            mbar_init(bar_s_free(b), kRows);
             mbar_init(bar_p_full(b), kRows);
+            mbar_init(bar_o_done(b), 1);
         }
-        mbar_init(bar_o_done, 1);
         fence_mbar_init();
     }
-    if (warp == 4) {
+    if (threadIdx.x < kSoftmaxThreads) {
+        for (int i = 0; i < 4; ++i) reinterpret_cast<uint32_t*>(smem_gen + SmemLayout::ones)[threadIdx.x + 256 * i] = 0x38383838u;
+        // hand-over slots start with a tile index no tile has
+        reinterpret_cast<uint2*>(smem_gen + SmemLayout::xref)[threadIdx.x] = make_uint2(0u, 0xFFFFFFFFu);
+        fence_proxy_async_smem();
+    }
+    if (warp == kMmaWarp) {
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
         tmem_relinquish();
     }
-    if (warp == 5 && lane == 0) {
+    if (warp == kProducerWarp && lane == 0) {
         prefetch_tmap(&tm_q);
         prefetch_tmap(&tm_k);
         prefetch_tmap(&tm_v);
@@ -163,7 +230,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 5) {
+    if (warp == kProducerWarp) {
         // =========================================================== producer ===========================================================
         {   // Q scale bytes -> [row % 32][row / 32][4] (the layout tcgen05.cp 32x128b.warpx4 spreads over the four lane quadrants)
             uint32_t w[4];
@@ -182,78 +249,108 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 tma_load_4d(q_smem, &tm_q, bar_q_full, 0, static_cast<int>(head), static_cast<int>(row0), static_cast<int>(batch));
             }
         }
-        int armed = 0;
-        for (int j = 0; j < n_tiles; ++j) {
-            const int st = j % kStages;
-            if (j >= kStages) {
-                if (!mbar_wait(bar_kv_empty(st), ((j / kStages) - 1) & 1, abort_flag)) break;
-            }
+        // K scale words are fetched two tiles ahead into registers, so their global-load latency never sits on the ring's critical path
+        auto load_k_scales = [&](int j, uint32_t (&w)[4]) {
             const uint32_t key0 = key_lo + j * kKeys;
-            uint32_t w[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const uint32_t key = key0 + lane + 32 * i;
-                if (key < p.SK) {
+                w[i] = 0x7F7F7F7Fu;   // keys past the sequence: data is zero-filled by TMA, any finite scale does
+                if (j < n_tiles && key < p.SK) {
                     const size_t off = static_cast<size_t>(batch) * p.ks_batch_stride + (static_cast<size_t>(key) * p.HK + kv_head) * 4u;
-                    w[i] = *reinterpret_cast<const uint32_t*>(p.k_descale + off);
-                } else {
-                    w[i] = 0x7F7F7F7Fu;   // keys past the sequence: data is zero-filled by TMA, any finite scale does
+                    w[i] = __ldg(reinterpret_cast<const uint32_t*>(p.k_descale + off));
                 }
             }
-            *reinterpret_cast<uint4*>(smem_gen + SmemLayout::sfk + st * kSfBytes + lane * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive_expect_tx(bar_kv_full(st), 2 * kTileBytes);
-                tma_load_4d(k_smem + st * kTileBytes, &tm_k, bar_kv_full(st), 0, static_cast<int>(kv_head), static_cast<int>(key0), static_cast<int>(batch));
-                tma_load_4d(v_smem + st * kTileBytes, &tm_v, bar_kv_full(st), 0, static_cast<int>(kv_head), static_cast<int>(key0), static_cast<int>(batch));
+        };
+        uint32_t wa[4], wb[4];
+        load_k_scales(0, wa);
+        load_k_scales(1, wb);
+        // Event loop over the two rings: the next K tile (with its scales) goes out as soon as Q K^T of the tile that held its stage is
+        // done, the next V tile as soon as P V of the tile that held its stage is done; neither waits for the other.
+        int k_next = 0, v_next = 0;
+        bool ok = true;
+        long long t_idle = clock64();
+        while (ok && (k_next < n_tiles || v_next < n_tiles)) {
+            bool progressed = false;
+            if (k_next < n_tiles) {
+                const int j = k_next, st = j % kStages;
+                bool rdy = j < kStages || mbar_test_wait(bar_k_empty(st), ((j / kStages) - 1) & 1);
+                rdy = __shfl_sync(0xFFFFFFFFu, rdy ? 1 : 0, 0) != 0;
+                if (rdy) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) w[i] = (j & 1) ? wb[i] : wa[i];
+                    if (j & 1) load_k_scales(j + 2, wb); else load_k_scales(j + 2, wa);
+                    *reinterpret_cast<uint4*>(smem_gen + SmemLayout::sfk + st * kSfBytes + lane * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(bar_k_full(st), kTileBytes);
+                        tma_load_4d(k_smem + st * kTileBytes, &tm_k, bar_k_full(st), 0, static_cast<int>(kv_head), static_cast<int>(key_lo + j * kKeys), static_cast<int>(batch));
+                    }
+                    ++k_next;
+                    progressed = true;
+                }
             }
-            armed = j + 1;
+            if (v_next < n_tiles) {
+                const int j = v_next, st = j % kStages;
+                bool rdy = j < kStages || mbar_test_wait(bar_v_empty(st), ((j / kStages) - 1) & 1);
+                rdy = __shfl_sync(0xFFFFFFFFu, rdy ? 1 : 0, 0) != 0;
+                if (rdy) {
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(bar_v_full(st), kTileBytes);
+                        tma_load_4d(v_smem + st * kTileBytes, &tm_v, bar_v_full(st), 0, static_cast<int>(kv_head), static_cast<int>(key_lo + j * kKeys), static_cast<int>(batch));
+                    }
+                    ++v_next;
+                    progressed = true;
+                }
+            }
+            if (progressed) {
+                t_idle = clock64();
+            } else {
+
+                if (*abort_flag != 0u || clock64() - t_idle > kWaitBudgetCycles) {
+                    *abort_flag = 1u;
+                    ok = false;
+                }
+            }
         }
         if (*abort_flag != 0u) {
             // leaving early: let the copies already in flight land before the CTA's shared memory is given back
-            for (int j = max(0, armed - kStages); j < armed; ++j) {
-                const int st = j % kStages;
+            for (int j = max(0, k_next - kStages); j < k_next; ++j) {
                 const long long t0 = clock64();
-                while (!mbar_try_wait(bar_kv_full(st), (j / kStages) & 1) && clock64() - t0 < kWaitBudgetCycles) {}
+                while (!mbar_test_wait(bar_k_full(j % kStages), (j / kStages) & 1) && clock64() - t0 < kWaitBudgetCycles) {}
+            }
+            for (int j = max(0, v_next - kStages); j < v_next; ++j) {
+                const long long t0 = clock64();
+                while (!mbar_test_wait(bar_v_full(j % kStages), (j / kStages) & 1) && clock64() - t0 < kWaitBudgetCycles) {}
             }
         }
-    } else if (warp == 4) {
+    } else if (warp == kMmaWarp) {
         // =========================================================== MMA issuer ===========================================================
         const uint32_t idesc_qk = idesc_mxf8_block_scaled(128, 128, 0, 0, 0, 0);
-        const uint32_t idesc_pv = idesc_f8_dense(128, 128, 0, 1);
+        // P V with N = 144: head dims 0..127 from the V tile, 16 more columns from the tile of ones (O | L are adjacent in TMEM)
+        const uint32_t idesc_pv = idesc_f8_dense(128, 144, 0, 1);
         const uint32_t t_sfq = tmem + kColSfQ;
         bool ok = mbar_wait(bar_q_full, 0, abort_flag);
         tc_fence_after_sync();
         if (ok && lane == 0) tmem_cp_sf(t_sfq, make_smem_desc(sfq_smem, 0, 128, kSwizzleNone));
 
-        auto issue_pv = [&](int i) -> bool {
-            // O (+)= P(i) V(i): P from TMEM (first 32 columns of S[i&1], 8 columns per 32 keys), V tile = 128 keys x 128 B, MN-major
-            if (!mbar_wait(bar_p_full(i & 1), (i >> 1) & 1, abort_flag)) return false;
-            tc_fence_after_sync();
-            if (lane == 0) {
-                const int st = i % kStages;
-                const uint32_t t_p = tmem + ((i & 1) ? kColS1 : kColS0);
-#pragma unroll
-                for (int kb = 0; kb < 4; ++kb) {
-                    const uint64_t dv = make_smem_desc(v_smem + st * kTileBytes + kb * 4096, 1024, 1024, kSwizzle128B);
-                    mma_f8_ts(tmem + kColO, t_p + 8 * kb, dv, idesc_pv, (i > 0 || kb > 0) ? 1u : 0u);
-                }
-                tc_commit(bar_kv_empty(st));
-                tc_commit(bar_o_done);
-            }
-            __syncwarp();
-            return true;
-        };
-
-        for (int j = 0; ok && j < n_tiles; ++j) {
+        float* mma_trace = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
+        auto issue_qk = [&](int j) -> bool {
+            // S[j&1] = Q K(j)^T: needs the K tile and its scales, and the softmax of tile j-2 to have read S[j&1] out
             const int st = j % kStages;
-            if (!mbar_wait(bar_kv_full(st), (j / kStages) & 1, abort_flag)) { ok = false; break; }
+            if (lane == 0) stamp(mma_trace, 2, j, 0);
+            if (!mbar_wait(bar_k_full(st), (j / kStages) & 1, abort_flag)) return false;
+            if (lane == 0) stamp(mma_trace, 2, j, 1);
+            if (j >= 2 && !mbar_wait(bar_s_free(j & 1), ((j >> 1) - 1) & 1, abort_flag)) return false;
             tc_fence_after_sync();
+            if (lane == 0) stamp(mma_trace, 2, j, 2);
             if (lane == 0) {
                 const uint32_t t_sfk = tmem + ((j & 1) ? kColSfK1 : kColSfK0);
                 const uint32_t t_s = tmem + ((j & 1) ? kColS1 : kColS0);
                 tmem_cp_sf(t_sfk, make_smem_desc(sfk_smem + st * kSfBytes, 0, 128, kSwizzleNone));
+                stamp(mma_trace, 2, j, 3);
 #pragma unroll
                 for (int kb = 0; kb < 4; ++kb) {
                     // K-major 128-byte-swizzled tiles: 8-row groups 1024 B apart, 32 head-dim bytes per MMA
@@ -262,31 +359,121 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     const uint32_t id = idesc_qk | (static_cast<uint32_t>(kb) << 29) | (static_cast<uint32_t>(kb) << 4);
                     mma_mxf8_ss(t_s, dq, dk, id, t_sfq + (static_cast<uint32_t>(kb) << 30), t_sfk + (static_cast<uint32_t>(kb) << 30), kb > 0 ? 1u : 0u);
                 }
+                stamp(mma_trace, 2, j, 4);
                 tc_commit(bar_s_full(j & 1));
+                tc_commit(bar_k_empty(st));
+                stamp(mma_trace, 2, j, 5);
             }
             __syncwarp();
-            if (j > 0) ok = issue_pv(j - 1);
+            return true;
+        };
+        auto issue_pv = [&](int i) -> bool {
+            // O (+)= P(i) V(i), L (+)= P(i) 1: P from TMEM (32 columns, 8 per 32 keys), V tile = 128 keys x 128 B, MN-major
+            if (lane == 0) stamp(mma_trace, 3, i, 0);
+            if (!mbar_wait(bar_p_full(i & 1), (i >> 1) & 1, abort_flag)) return false;
+            if (lane == 0) stamp(mma_trace, 3, i, 1);
+            if (!mbar_wait(bar_v_full(i % kStages), (i / kStages) & 1, abort_flag)) return false;
+            tc_fence_after_sync();
+            if (lane == 0) stamp(mma_trace, 3, i, 2);
+            if (lane == 0) {
+                const int st = i % kStages;
+                const uint32_t t_p = tmem + ((i & 1) ? kColP1 : kColP0);
+#pragma unroll
+                for (int kb = 0; kb < 4; ++kb) {
+                    // MN-major B: 8-key groups 1024 B apart; the second 128-byte-wide atom (columns 128..) is the tile of ones
+                    const uint32_t v_addr = v_smem + st * kTileBytes + kb * 4096;
+                    const uint64_t dv = make_smem_desc(v_addr, ones_smem - v_addr, 1024, kSwizzle128B);
+                    mma_f8_ts(tmem + kColO, t_p + 8 * kb, dv, idesc_pv, (i > 0 || kb > 0) ? 1u : 0u);
+                }
+                stamp(mma_trace, 3, i, 3);
+                tc_commit(bar_v_empty(st));
+                tc_commit(bar_o_done(i & 1));
+                stamp(mma_trace, 3, i, 4);
+            }
+            __syncwarp();
+            return true;
+        };
+
+        // Event loop: whichever of "next score tile" and "next P V" has its inputs ready is issued; neither ever blocks the other, so a
+        // warpgroup that has handed its S buffer back gets its next score tile while the other group is still working on its P.
+        auto qk_ready = [&](int j) -> bool {
+            bool rdy = mbar_test_wait(bar_k_full(j % kStages), (j / kStages) & 1);
+            if (rdy && j >= 2) rdy = mbar_test_wait(bar_s_free(j & 1), ((j >> 1) - 1) & 1);
+            return __shfl_sync(0xFFFFFFFFu, rdy ? 1 : 0, 0) != 0;
+        };
+        auto pv_ready = [&](int i) -> bool {
+            const bool rdy = mbar_test_wait(bar_p_full(i & 1), (i >> 1) & 1) && mbar_test_wait(bar_v_full(i % kStages), (i / kStages) & 1);
+            return __shfl_sync(0xFFFFFFFFu, rdy ? 1 : 0, 0) != 0;
+        };
+        int qk_next = 0, pv_next = 0;
+        long long t_idle = clock64();
+        while (ok && pv_next < n_tiles) {
+            bool progressed = false;
+            if (qk_next < n_tiles && qk_ready(qk_next)) {
+                ok = issue_qk(qk_next++);
+                progressed = true;
+            }
+            if (ok && pv_next < qk_next && pv_ready(pv_next)) {
+                ok = issue_pv(pv_next++);
+                progressed = true;
+            }
+            if (progressed) {
+                t_idle = clock64();
+            } else {
+                // (no sleep: nanosleep wakes on a coarse timer tick)
+                if (*abort_flag != 0u || clock64() - t_idle > kWaitBudgetCycles) {
+                    *abort_flag = 1u;
+                    ok = false;
+                }
+            }
         }
-        if (ok && n_tiles > 0) issue_pv(n_tiles - 1);
-    } else {
+    } else if (warp >= kFirstSoftmaxWarp) {
         // =========================================================== softmax + epilogue ===========================================================
-        const uint32_t r = threadIdx.x;                        // query row within the tile = TMEM lane
-        const uint32_t lane_base = (static_cast<uint32_t>(warp) * 32u) << 16;
-        float ref = -INFINITY;   // the row's reference (log2 units)
-        float l = 0.0f;          // running sum of the quantised P
+        const uint32_t g = (threadIdx.x - 32u * kFirstSoftmaxWarp) >> 7;   // warpgroup: key tiles j = g mod 2; in the epilogue head dims [64 g, 64 g + 64) of O
+        const uint32_t r = (threadIdx.x - 32u * kFirstSoftmaxWarp) & 127u;   // query row within the tile = TMEM lane
+        const uint32_t lane_base = (static_cast<uint32_t>(warp & 3) * 32u) << 16;
+        const uint32_t xref = smem_base + SmemLayout::xref;   // 8-byte slots, accessed with single 64-bit shared loads / stores
+        const uint32_t t_s = tmem + (g ? kColS1 : kColS0) + lane_base;
+        const uint32_t t_p = tmem + (g ? kColP1 : kColP0) + lane_base;
+        const uint32_t t_o_all = tmem + kColO + lane_base;
+        const uint32_t t_l = tmem + kColL + lane_base;
+        float ref = -INFINITY;   // the row's reference (log2 units) after the last tile this thread has seen
         bool ok = true;
         const bool tracing = (p.trace != nullptr) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 
-        for (int j = 0; j < n_tiles; ++j) {
-            if (!mbar_wait(bar_s_full(j & 1), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+        // the reference the row has after tile j, published by the thread that handled tile j
+        auto wait_ref = [&](int j, float& out) -> bool {
+            const uint32_t slot = xref + 8u * (static_cast<uint32_t>(j & 1) * 128u + r);
+            uint2 o = ld_shared_v2(slot);
+            if (o.y != static_cast<uint32_t>(j)) {
+                const long long t0 = clock64();
+                while (true) {
+
+                    o = ld_shared_v2(slot);
+                    if (o.y == static_cast<uint32_t>(j)) break;
+                    if (*abort_flag != 0u || clock64() - t0 > kWaitBudgetCycles) { *abort_flag = 1u; return false; }
+                }
+            }
+            out = __uint_as_float(o.x);
+            return true;
+        };
+
+        for (int j = static_cast<int>(g); j < n_tiles; j += 2) {
+            const int k = j >> 1;   // this group's tile counter
+            float* st_trace = (tracing && r == 0) ? p.trace : nullptr;
+            stamp(st_trace, g, j, 0);
+            if (!mbar_wait(bar_s_full(g), k & 1, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            const uint32_t t_s = tmem + ((j & 1) ? kColS1 : kColS0) + lane_base;
+            stamp(st_trace, g, j, 1);
             uint32_t s0[32], s1[32], s2[32], s3[32];
             tmem_ld32(t_s + 0, s0);
             tmem_ld32(t_s + 32, s1);
             tmem_ld32(t_s + 64, s2);
             tmem_ld32(t_s + 96, s3);
             tmem_wait_ld();
+            tc_fence_before_sync();
+            mbar_arrive(bar_s_free(g));   // the score buffer can take tile j + 2
+            stamp(st_trace, g, j, 2);
 
             const int nvalid = static_cast<int>(min(static_cast<uint32_t>(kKeys), key_hi - (key_lo + j * kKeys)));
             if (nvalid < kKeys) {   // keys past the range: -inf for the maximum, 0 for P (crates/amdgpu-tile/src/reduce.rs:35-49)
@@ -307,98 +494,109 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     p.trace[r * 128 + 96 + c] = __uint_as_float(s3[c]);
                 }
             }
-            float mt = -INFINITY;
+            float m0 = __uint_as_float(s0[0]), m1 = __uint_as_float(s1[0]), m2 = __uint_as_float(s2[0]), m3 = __uint_as_float(s3[0]);
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                mt = fmaxf(mt, fmaxf(fmaxf(__uint_as_float(s0[c]), __uint_as_float(s1[c])), fmaxf(__uint_as_float(s2[c]), __uint_as_float(s3[c]))));
+            for (int c = 1; c < 31; c += 2) {   // four independent chains of three-input maxima
+                m0 = max3(m0, __uint_as_float(s0[c]), __uint_as_float(s0[c + 1]));
+                m1 = max3(m1, __uint_as_float(s1[c]), __uint_as_float(s1[c + 1]));
+                m2 = max3(m2, __uint_as_float(s2[c]), __uint_as_float(s2[c + 1]));
+                m3 = max3(m3, __uint_as_float(s3[c]), __uint_as_float(s3[c + 1]));
             }
-            // lazily moved reference: only when this tile's maximum passes it by more than the threshold
+            float mt = fmaxf(max3(m0, m1, __uint_as_float(s0[31])), max3(m2, m3, __uint_as_float(s1[31])));
+            mt = max3(mt, __uint_as_float(s2[31]), __uint_as_float(s3[31]));
+            stamp(st_trace, g, j, 3);
+            // take over the row's reference from the thread that handled tile j - 1
+            if (j > 0 && !wait_ref(j - 1, ref)) ok = false;
+            if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+            // the reference moves when this tile's maximum passes it by more than the threshold (negative for short sequences: it then
+            // also follows the tile maximum down, and f > 1 scales O and L up)
             const bool move = mt > ref + thr;
-            if (__any_sync(0xFFFFFFFFu, move)) {
-                float f = 1.0f;
-                if (move) {
-                    f = ex2_approx(ref - mt);   // 0 on the first tile (ref = -inf)
-                    ref = mt;
-                    l *= f;
-                }
-                if (j > 0) {
-                    // O must be complete (P V of tile j-1) before it is rescaled; P V of tile j cannot start before this thread's arrive below
-                    if (!mbar_wait(bar_o_done, (j - 1) & 1, abort_flag)) { ok = false; break; }
-                    tc_fence_after_sync();
-                    const uint32_t t_o = tmem + kColO + lane_base;
-#pragma unroll 1
-                    for (int cc = 0; cc < 4; ++cc) {
-                        uint32_t o[32];
-                        tmem_ld32(t_o + 32 * cc, o);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f);
-                        tmem_st32(t_o + 32 * cc, o);
-                    }
-                    tmem_wait_st();
-                }
+            float f = 1.0f;
+            if (move) {
+                const float nref = lazy ? ceilf(mt) : mt;
+                f = ex2_approx(ref - nref);   // 0 on the first tile (ref = -inf); an exact power of two for integer references
+                ref = nref;
             }
-            // P = e4m3(2^(s - ref + offset)), four keys per 32-bit TMEM column; l adds what P V will add
+            st_shared_v2(xref + 8u * (static_cast<uint32_t>(j & 1) * 128u + r), __float_as_uint(ref), static_cast<uint32_t>(j));
+            // P V of this group's previous tile must be done before its P columns are overwritten (and, observed in order, this keeps
+            // the parity of the other group's barrier below unambiguous)
+            stamp(st_trace, g, j, 4);
+            if (k > 0 && !mbar_wait(bar_o_done(g), (k - 1) & 1, abort_flag)) { ok = false; break; }
+            stamp(st_trace, g, j, 5);
+            if (j > 0 && __any_sync(0xFFFFFFFFu, move)) {
+                // O holds P V of all tiles before j once the other group's last P V is done; P V of tile j cannot start before this thread's arrive below
+                if (!mbar_wait(bar_o_done(g ^ 1u), ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+#pragma unroll 1
+                for (int cc = 0; cc < 4; ++cc) scale_tmem32(t_o_all + 32 * cc, f);
+                {   // the row sum lives in column 0 of L
+                    uint32_t lv;
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(lv) : "r"(t_l) : "memory");
+                    tmem_wait_ld();
+                    lv = __float_as_uint(__uint_as_float(lv) * f);
+                    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(t_l), "r"(lv) : "memory");
+                }
+                tmem_wait_st();
+            }
+            // P = e4m3(2^(s - ref + offset)), four keys per 32-bit TMEM column
             const float sh = kPOffset - ref;
             uint32_t pw[32];
-            float lsum = 0.0f;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
-                uint32_t lo, hi;
-                lo = cvt_e4m3x2(ex2_approx(__uint_as_float(s0[4 * c]) + sh), ex2_approx(__uint_as_float(s0[4 * c + 1]) + sh));
-                hi = cvt_e4m3x2(ex2_approx(__uint_as_float(s0[4 * c + 2]) + sh), ex2_approx(__uint_as_float(s0[4 * c + 3]) + sh));
-                lsum += sum_e4m3x2(lo) + sum_e4m3x2(hi);
-                pw[c] = lo | (hi << 16);
-                lo = cvt_e4m3x2(ex2_approx(__uint_as_float(s1[4 * c]) + sh), ex2_approx(__uint_as_float(s1[4 * c + 1]) + sh));
-                hi = cvt_e4m3x2(ex2_approx(__uint_as_float(s1[4 * c + 2]) + sh), ex2_approx(__uint_as_float(s1[4 * c + 3]) + sh));
-                lsum += sum_e4m3x2(lo) + sum_e4m3x2(hi);
-                pw[8 + c] = lo | (hi << 16);
-                lo = cvt_e4m3x2(ex2_approx(__uint_as_float(s2[4 * c]) + sh), ex2_approx(__uint_as_float(s2[4 * c + 1]) + sh));
-                hi = cvt_e4m3x2(ex2_approx(__uint_as_float(s2[4 * c + 2]) + sh), ex2_approx(__uint_as_float(s2[4 * c + 3]) + sh));
-                lsum += sum_e4m3x2(lo) + sum_e4m3x2(hi);
-                pw[16 + c] = lo | (hi << 16);
-                lo = cvt_e4m3x2(ex2_approx(__uint_as_float(s3[4 * c]) + sh), ex2_approx(__uint_as_float(s3[4 * c + 1]) + sh));
-                hi = cvt_e4m3x2(ex2_approx(__uint_as_float(s3[4 * c + 2]) + sh), ex2_approx(__uint_as_float(s3[4 * c + 3]) + sh));
-                lsum += sum_e4m3x2(lo) + sum_e4m3x2(hi);
-                pw[24 + c] = lo | (hi << 16);
+                pw[c] = p_word(s0[4 * c], s0[4 * c + 1], s0[4 * c + 2], s0[4 * c + 3], sh);
+                pw[8 + c] = p_word(s1[4 * c], s1[4 * c + 1], s1[4 * c + 2], s1[4 * c + 3], sh);
+                pw[16 + c] = p_word(s2[4 * c], s2[4 * c + 1], s2[4 * c + 2], s2[4 * c + 3], sh);
+                pw[24 + c] = p_word(s3[4 * c], s3[4 * c + 1], s3[4 * c + 2], s3[4 * c + 3], sh);
             }
-            l += lsum;
             if (tracing && j == 0) {
 #pragma unroll
                 for (int c = 0; c < 32; ++c) reinterpret_cast<uint32_t*>(p.trace)[32768 + 256 + r * 32 + c] = pw[c];
             }
-            tmem_st32(t_s, pw);
+            stamp(st_trace, g, j, 6);
+            tmem_st32(t_p, pw);
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(bar_p_full(j & 1));
+            mbar_arrive(bar_p_full(g));
+            stamp(st_trace, g, j, 7);
         }
 
-        // ---- epilogue: O * v_descale / l ----
-        if (ok && n_tiles > 0) ok = mbar_wait(bar_o_done, (n_tiles - 1) & 1, abort_flag);
+        // ---- epilogue: O * v_descale / l; group g stores head dims [64 g, 64 g + 64) ----
+        if (ok && n_tiles > 0) {
+            const int last = n_tiles - 1;
+            const int mine = ((last & 1) == static_cast<int>(g)) ? last : last - 1;   // this group's last tile (-1: none)
+            if (mine >= 0) ok = mbar_wait(bar_o_done(g), (mine >> 1) & 1, abort_flag);
+            const int theirs = ((last & 1) == static_cast<int>(g)) ? last - 1 : last;
+            if (ok && theirs >= 0) ok = mbar_wait(bar_o_done(g ^ 1u), (theirs >> 1) & 1, abort_flag);
+            if (ok) ok = wait_ref(last, ref);
+        }
         tc_fence_after_sync();
         if (ok && n_tiles > 0) {
+            uint32_t lv;
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(lv) : "r"(t_l) : "memory");
+            tmem_wait_ld();
+            const float l = __uint_as_float(lv);
             const float vd = *p.v_descale;
             const float fin = vd / l;   // crates/amdgpu-stage/src/attention/state.rs:79-82
             const uint32_t row = row0 + r;
             const bool row_ok = row < p.S;   // rows past the sequence are computed on clamped scales and not stored (block3.rs:194)
-            const uint32_t t_o = tmem + kColO + lane_base;
-            if (tracing) {
+            const uint32_t t_o = t_o_all + 64 * g;
+            if (tracing && g == 0) {
                 p.trace[32768 + r] = l;
                 p.trace[32768 + 128 + r] = ref;
             }
 #pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
+            for (int cc = 0; cc < 2; ++cc) {
                 uint32_t o[32];
                 tmem_ld32(t_o + 32 * cc, o);
                 tmem_wait_ld();
                 if (tracing) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) p.trace[16384 + r * 128 + 32 * cc + c] = __uint_as_float(o[c]);
+                    for (int c = 0; c < 32; ++c) p.trace[16384 + r * 128 + 64 * g + 32 * cc + c] = __uint_as_float(o[c]);
                 }
                 if (!row_ok) continue;
                 if (kSplit) {
                     const size_t prow = static_cast<size_t>(split) * p.rows_total + (static_cast<size_t>(batch) * p.S + row) * p.H + head;
-                    float4* dst = reinterpret_cast<float4*>(p.ohat + prow * 128 + 32 * cc);
+                    float4* dst = reinterpret_cast<float4*>(p.ohat + prow * 128 + 64 * g + 32 * cc);
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
                         dst[c] = make_float4(__uint_as_float(o[4 * c]) * fin, __uint_as_float(o[4 * c + 1]) * fin,
@@ -406,7 +604,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     }
                 } else {
                     uint8_t* orow = p.o + static_cast<size_t>(batch) * p.o_batch_stride + static_cast<size_t>(row) * p.o_row_stride + head * 256u;
-                    uint4* dst = reinterpret_cast<uint4*>(orow + 64 * cc);
+                    uint4* dst = reinterpret_cast<uint4*>(orow + 128 * g + 64 * cc);
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t wv[4];
@@ -419,7 +617,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     }
                 }
             }
-            if (row_ok) {
+            if (row_ok && g == 0) {
                 const float lse2 = ref - kPOffset + lg2_approx(l);   // log2 of sum_j 2^(s_j)
                 if (kSplit) {
                     const size_t prow = static_cast<size_t>(split) * p.rows_total + (static_cast<size_t>(batch) * p.S + row) * p.H + head;
@@ -435,7 +633,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     tc_fence_before_sync();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag != 0u) atomicOr(p.status, 1u);
-    if (warp == 4) {
+    if (warp == kMmaWarp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, kTmemCols);
     }

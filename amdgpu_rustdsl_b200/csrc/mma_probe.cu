@@ -65,9 +65,23 @@ __global__ void __launch_bounds__(128, 1) mma_probe_kernel(int variant, int iter
                 } else if (variant == 1) {
                     const uint64_t db = make_smem_desc(b_smem + kb * 4096, 1024, 1024, kSwizzle128B);
                     mma_mxf8_ts(d, tmem + 256 + 8 * kb, db, id_bs_mn | (kb << 29) | (kb << 4), t_sfa + (kb << 30), t_sfb + (kb << 30), kb > 0);
-                } else {
+                } else if (variant == 2) {
                     const uint64_t db = make_smem_desc(b_smem + kb * 4096, 1024, 1024, kSwizzle128B);
                     mma_f8_ts(d, tmem + 256 + 8 * kb, db, id_f8_mn, kb > 0);
+                } else if (variant == 3) {   // plain fp8, A from shared memory, B MN-major
+                    const uint64_t da = make_smem_desc(a_smem + kb * 32, 16, 1024, kSwizzle128B);
+                    const uint64_t db = make_smem_desc(b_smem + kb * 4096, 1024, 1024, kSwizzle128B);
+                    mma_f8_ss(d, da, db, id_f8_mn, kb > 0);
+                } else if (variant == 4) {   // plain fp8, A from tensor memory, B K-major
+                    const uint64_t db = make_smem_desc(b_smem + kb * 32, 16, 1024, kSwizzle128B);
+                    mma_f8_ts(d, tmem + 256 + 8 * kb, db, idesc_f8_dense(128, 128, 0, 0), kb > 0);
+                } else if (variant == 5) {   // plain fp8, both from shared memory, K-major
+                    const uint64_t da = make_smem_desc(a_smem + kb * 32, 16, 1024, kSwizzle128B);
+                    const uint64_t db = make_smem_desc(b_smem + kb * 32, 16, 1024, kSwizzle128B);
+                    mma_f8_ss(d, da, db, idesc_f8_dense(128, 128, 0, 0), kb > 0);
+                } else {   // 6: the 16-column row-sum MMA (A from tensor memory, unswizzled K-major B)
+                    const uint64_t db = make_smem_desc(b_smem, 128, 256, kSwizzleNone);
+                    mma_f8_ts(d, tmem + 256 + 8 * kb, db, idesc_f8_dense(128, 16, 0, 0), kb > 0);
                 }
             }
         }

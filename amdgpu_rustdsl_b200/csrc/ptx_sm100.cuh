@@ -38,6 +38,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking poll (try_wait may suspend the thread for a hardware time slice; test_wait never does).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Clock budget of one wait (SM cycles). ~2 s at 1.9 GHz: far above any legitimate wait in these kernels
 // (a whole launch takes well under 100 ms), small enough that a protocol bug ends by itself.
 constexpr long long kWaitBudgetCycles = 4000000000LL;

@@ -1,0 +1,95 @@
+"""Sharding of the MXFP8 attention path over the GPUs of one node, one process per GPU.
+
+The reference has no multi-GPU code; the two shardings below follow from the structure of its path:
+  * by (batch x head): the logical blocks of the unsplit kernels are independent (grid y = H, z = B,
+    tests/gpu/generated/fmha_fwd_hd128_mxfp8_v3_vs128_abi.h:200-201), so each rank runs the path on its own packed tensors with
+    H/world heads. Whole KV-head groups stay on one rank (kv head = head >> log2 gqa, crates/amdgpu-stage/src/components.rs:8-17).
+    No collective.
+  * by key range: the KV-split algebra with "split = rank" (crates/amdgpu-stage/src/components.rs:58-74,
+    crates/amdgpu-tile/src/epilogue.rs:117-146): every rank runs the split kernel over its local keys for all queries, the f32
+    partials (O, base-2 LSE) are exchanged once (all-gather: NCCL on GPUs, gloo in the CPU tests) into local memory, and the
+    combine kernel merges them with splits = world.
+`torch.distributed` is the plumbing; the kernels are the library's.
+"""
+from __future__ import annotations
+
+import math
+
+D = 128
+
+
+def head_shard(H: int, HK: int, rank: int, world: int):
+    """Heads [h0, h1) and KV heads [k0, k1) of `rank`: KV-head groups are dealt out contiguously, as evenly as possible."""
+    if H % HK:
+        raise ValueError("H must be a multiple of HK")
+    gqa = H // HK
+    base, extra = divmod(HK, world)
+    k0 = rank * base + min(rank, extra)
+    k1 = k0 + base + (1 if rank < extra else 0)
+    return (k0 * gqa, k1 * gqa), (k0, k1)
+
+
+def kv_range_shard(SK: int, rank: int, world: int):
+    """Keys [lo, hi) of `rank`: 128-key tiles dealt out like the split kernel's ranges (tiles [r*tps, min(ntiles, (r+1)*tps))); every rank
+    must own a tile, as the reference demands of every split (tests/gpu/ref_host.cpp:117-120)."""
+    ntiles = -(-SK // 128)
+    tps = -(-ntiles // world)
+    if (world - 1) * tps >= ntiles:
+        raise ValueError(f"SK={SK} gives {ntiles} key tiles: too few for {world} ranks")
+    lo = rank * tps * 128
+    hi = min((rank + 1) * tps * 128, SK)
+    return lo, hi
+
+
+def local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, lse, *, stream=None, check=True):
+    """One rank's contribution to a key-range-sharded forward: the split kernel with splits = 1 over the local keys, writing the
+    normalised f32 partial O [rows_total,128] and base-2 log-sum-exp [rows_total] of all queries."""
+    import ctypes as C
+    import torch
+    from . import _abi
+    from .ops import _check_launch, _nbytes, fill_common
+    lib = _abi.load()
+    B, S, H, _ = q.shape
+    _, SKl, HK, _ = k_local.shape
+    if stream is None:
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+    rows_total = B * S * H
+    a = fill_common(_abi.KvSplitArgs(), q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, B, S, H, SKl, HK)
+    a.ptr_o = None
+    a.ptr_ohat, a.ptr_lse, a.kvs_splits, a.kvs_rows_total = ohat.data_ptr(), lse.data_ptr(), 1, rows_total
+    sizes = _abi.BufferSizes(ptr_q=_nbytes(q), ptr_k=_nbytes(k_local), ptr_v=_nbytes(v_local), ptr_o=B * S * H * 256, ptr_q_descale=_nbytes(q_scale),
+                             ptr_k_descale=_nbytes(k_scale_local), ptr_v_descale=_nbytes(v_scale), ptr_ohat=_nbytes(ohat), ptr_lse=_nbytes(lse))
+    syms = _abi.Symbols(B=B, HK=HK, KL=0)
+    _check_launch(lib, _abi.KVSPLIT, a, sizes, _abi.grid3(math.ceil(S / 256), H, B), syms, stream, check)
+
+
+def combine_gathered(ohat_all, lse_all, out, world: int, *, stream=None, check=True):
+    """The combine kernel over the gathered partials: ohat_all f32 [world, rows_total, 128], lse_all f32 [world, rows_total] -> bf16 out."""
+    import torch
+    from . import _abi
+    from .ops import _check_launch, _nbytes
+    lib = _abi.load()
+    rows_total = out.numel() // D
+    if stream is None:
+        stream = torch.cuda.current_stream(out.device).cuda_stream
+    c = _abi.CombineArgs(ptr_ohat=ohat_all.data_ptr(), ptr_lse=lse_all.data_ptr(), ptr_out=out.data_ptr(), rows_total=rows_total, d=D, splits=world)
+    sizes = _abi.BufferSizes(ptr_ohat=_nbytes(ohat_all), ptr_lse=_nbytes(lse_all), ptr_out=_nbytes(out))
+    _check_launch(lib, _abi.COMBINE8H, c, sizes, _abi.grid3(max(1, math.ceil(rows_total * D / 2048)), 1, 1), None, stream, check)
+
+
+def exchange_partials(ohat, lse, ohat_all, lse_all, group=None):
+    """The one exchange step of the key-range sharding: all-gather of every rank's partials into local memory (rank-major, which is the
+    [splits][rows_total] layout the combine kernel reads)."""
+    import torch.distributed as dist
+    dist.all_gather_into_tensor(ohat_all, ohat, group=group)
+    dist.all_gather_into_tensor(lse_all, lse, group=group)
+
+
+def fmha_fwd_mxfp8_kv_sharded(q, k_local, v_local, q_scale, k_scale_local, v_scale, out, ws, group=None):
+    """Key-range-sharded forward on every rank of `group`: local partials -> all-gather -> combine. `ws` holds the caller's workspaces
+    {"ohat": f32 [rows_total,128], "lse": f32 [rows_total], "ohat_all": f32 [world,rows_total,128], "lse_all": f32 [world,rows_total]}."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ws["ohat"], ws["lse"])
+    exchange_partials(ws["ohat"], ws["lse"], ws["ohat_all"], ws["lse_all"], group)
+    combine_gathered(ws["ohat_all"], ws["lse_all"], out, world)

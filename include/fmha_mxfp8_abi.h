@@ -282,15 +282,16 @@ int fmha_mxfp8_device_status(uint32_t* status);
 /*
  * Diagnostics hook in the spirit of the reference's stamp buffer (docs/stamps.md): when a device buffer of at least
  * FMHA_MXFP8_TRACE_BYTES is attached, logical block (0,0,0) of the next attention launches records its first score tile, the
- * unnormalised O, the row sums and the row references there. Pass NULL to detach.
+ * unnormalised O, the row sums, the row references and per-tile SM-clock stamps of its warp roles there. Pass NULL to detach.
  */
-#define FMHA_MXFP8_TRACE_BYTES (4u * (16384u + 16384u + 256u + 4096u))
+#define FMHA_MXFP8_TRACE_BYTES (4u * (16384u + 16384u + 256u + 4096u + 2048u))
 int fmha_mxfp8_trace_attach(void* dev_buf, size_t bytes);
 
 /*
  * Issue-only ceiling of the tensor pipe: every CTA issues `iters` x 4 tcgen05.mma (M128 N128 K32, e4m3) back to back on resident
- * operands. variant 0 = block-scaled, A from shared memory; 1 = block-scaled, A from tensor memory; 2 = kind::f8f6f4, A from
- * tensor memory. Writes the elapsed milliseconds (CUDA events on `stream`) and returns 0. Used for the roofline denominator.
+ * operands. variant 0 = block-scaled, A from shared memory; 1 = block-scaled, A from tensor memory, B MN-major; 2 = kind::f8f6f4, A
+ * from tensor memory, B MN-major; 3 = f8f6f4, A from shared memory, B MN-major; 4 = f8f6f4, A from tensor memory, B K-major;
+ * 5 = f8f6f4, both from shared memory, K-major; 6 = the N16 row-sum MMA (counted as if it were N128). Writes the elapsed milliseconds (CUDA events on `stream`) and returns 0. Used for the roofline denominator.
  */
 int fmha_mxfp8_probe_mma_peak(int variant, int iters, int ctas, void* stream, float* ms);
 
