@@ -40,9 +40,9 @@ constexpr int kRows = 128;          // query rows per CTA tile
 constexpr int kKeys = 128;          // keys per tile
 constexpr int kStages = 5;          // depth of the K ring and of the V ring (freed separately: K after Q K^T, V after P V)
 constexpr int kSoftmaxThreads = 256;
-// The two single-lane service warps get the lowest warp ids: the warp schedulers favour older warps, and a service warp that polls behind
-// two arithmetic-dense softmax warps on its scheduler is otherwise only issued when they stall. Warps 2-3 idle; softmax = warps 4-11.
-constexpr int kMmaWarp = 0, kProducerWarp = 1, kFirstSoftmaxWarp = 4;
+// The three single-lane service warps get the lowest warp ids: the warp schedulers favour older warps, and a service warp that polls behind
+// two arithmetic-dense softmax warps on its scheduler is otherwise only issued when they stall. Warp 3 idles; softmax = warps 4-11.
+constexpr int kMmaWarp = 0, kProducerWarp = 1, kPvWarp = 2, kFirstSoftmaxWarp = 4;
 constexpr int kThreads = 384;
 constexpr uint32_t kTileBytes = 128 * 128;   // one e4m3 tile
 constexpr uint32_t kSfBytes = 512;           // 128 rows x 4 scale bytes
@@ -110,6 +110,25 @@ __device__ __forceinline__ uint32_t p_word(uint32_t s0, uint32_t s1, uint32_t s2
     const uint32_t lo = cvt_e4m3x2(ex2_approx(__uint_as_float(s0) + sh), ex2_approx(__uint_as_float(s1) + sh));
     const uint32_t hi = cvt_e4m3x2(ex2_approx(__uint_as_float(s2) + sh), ex2_approx(__uint_as_float(s3) + sh));
     return lo | (hi << 16);
+}
+
+// The long-sequence conversion: the exp2 unit delivers 16 results per clock per SM, a quarter of what the score tiles need at full
+// tensor rate, so two of every four P values are produced on the FMA pipe instead, straight as e4m3 bit patterns:
+// byte = rne(8 (x + 7)) with x = log2 P, i.e. exponent field = floor(x) + 7 and a mantissa that is linear in the fraction of x
+// (the piecewise-linear exp2 the reference uses for all of P, crates/amdgpu-tile/src/reduce.rs:94-113, docs/vendor-spec.md:271-281).
+// fma.sat clamps to [0, 1] = bytes 0..256 (so -inf scores give 0), and adding 2^15 leaves rne(256 t) in the low byte of the sum.
+// The linear mantissa overestimates 2^frac by 3.97 % on average; kFastBias shifts x so that the two kinds of P values agree on
+// average, otherwise mixing them in one row sum would bias the weights.
+constexpr float kFastBias = 0.0562f;
+__device__ __forceinline__ uint32_t fast_p_bits(uint32_t s, float c) {
+    float t;
+    asm("fma.rn.sat.f32 %0, %1, 0f3D000000, %2;" : "=f"(t) : "f"(__uint_as_float(s)), "f"(c));   // s / 32 + c
+    return __float_as_uint(t + 32768.0f);
+}
+__device__ __forceinline__ uint32_t p_word_hybrid(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t s3, float sh, float c) {
+    const uint32_t lo = cvt_e4m3x2(ex2_approx(__uint_as_float(s0) + sh), ex2_approx(__uint_as_float(s1) + sh));
+    const uint32_t hi = __byte_perm(fast_p_bits(s2, c), fast_p_bits(s3, c), 0x0040);
+    return __byte_perm(lo, hi, 0x5410);
 }
 
 __device__ __forceinline__ void st_shared_v2(uint32_t addr, uint32_t a, uint32_t b) {
@@ -285,6 +304,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
+                        stamp((blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr, 2, j, 6);
                         mbar_arrive_expect_tx(bar_k_full(st), kTileBytes);
                         tma_load_4d(k_smem + st * kTileBytes, &tm_k, bar_k_full(st), 0, static_cast<int>(kv_head), static_cast<int>(key_lo + j * kKeys), static_cast<int>(batch));
                     }
@@ -298,6 +318,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 rdy = __shfl_sync(0xFFFFFFFFu, rdy ? 1 : 0, 0) != 0;
                 if (rdy) {
                     if (lane == 0) {
+                        stamp((blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr, 3, j, 6);
                         mbar_arrive_expect_tx(bar_v_full(st), kTileBytes);
                         tma_load_4d(v_smem + st * kTileBytes, &tm_v, bar_v_full(st), 0, static_cast<int>(kv_head), static_cast<int>(key_lo + j * kKeys), static_cast<int>(batch));
                     }
@@ -327,106 +348,88 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             }
         }
     } else if (warp == kMmaWarp) {
-        // =========================================================== MMA issuer ===========================================================
-        const uint32_t idesc_qk = idesc_mxf8_block_scaled(128, 128, 0, 0, 0, 0);
-        // P V with N = 144: head dims 0..127 from the V tile, 16 more columns from the tile of ones (O | L are adjacent in TMEM)
-        const uint32_t idesc_pv = idesc_f8_dense(128, 144, 0, 1);
-        const uint32_t t_sfq = tmem + kColSfQ;
-        bool ok = mbar_wait(bar_q_full, 0, abort_flag);
-        tc_fence_after_sync();
-        if (ok && lane == 0) tmem_cp_sf(t_sfq, make_smem_desc(sfq_smem, 0, 128, kSwizzleNone));
+        // =========================================================== MMA issuer: score tiles ===========================================================
+        // One lane runs the role. A tcgen05.mma costs its issuing thread about as long as the tensor pipe needs for a 128 x 128 x 32
+        // tile, so Q K^T and P V are issued by two different threads (this warp and kPvWarp): their streams share no operand, and the
+        // pipe interleaves them. Polls are non-blocking and descriptors are prepared once.
+        if (lane == 0) {
+            const uint32_t idesc_qk = idesc_mxf8_block_scaled(128, 128, 0, 0, 0, 0);
+            const uint32_t t_sfq = tmem + kColSfQ;
+            float* mma_trace = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
+            // K-major 128-byte-swizzled Q / K tiles: 8-row groups 1024 B apart, 32 head-dim bytes (two 16-byte units) per MMA
+            const uint64_t dq0 = make_smem_desc(q_smem, 16, 1024, kSwizzle128B);
+            const uint64_t dk0 = make_smem_desc(k_smem, 16, 1024, kSwizzle128B);
+            const uint64_t dsf0 = make_smem_desc(sfk_smem, 0, 128, kSwizzleNone);
 
-        float* mma_trace = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
-        auto issue_qk = [&](int j) -> bool {
-            // S[j&1] = Q K(j)^T: needs the K tile and its scales, and the softmax of tile j-2 to have read S[j&1] out
-            const int st = j % kStages;
-            if (lane == 0) stamp(mma_trace, 2, j, 0);
-            if (!mbar_wait(bar_k_full(st), (j / kStages) & 1, abort_flag)) return false;
-            if (lane == 0) stamp(mma_trace, 2, j, 1);
-            if (j >= 2 && !mbar_wait(bar_s_free(j & 1), ((j >> 1) - 1) & 1, abort_flag)) return false;
+            bool ok = mbar_wait(bar_q_full, 0, abort_flag);
             tc_fence_after_sync();
-            if (lane == 0) stamp(mma_trace, 2, j, 2);
-            if (lane == 0) {
-                const uint32_t t_sfk = tmem + ((j & 1) ? kColSfK1 : kColSfK0);
-                const uint32_t t_s = tmem + ((j & 1) ? kColS1 : kColS0);
-                tmem_cp_sf(t_sfk, make_smem_desc(sfk_smem + st * kSfBytes, 0, 128, kSwizzleNone));
-                stamp(mma_trace, 2, j, 3);
-#pragma unroll
-                for (int kb = 0; kb < 4; ++kb) {
-                    // K-major 128-byte-swizzled tiles: 8-row groups 1024 B apart, 32 head-dim bytes per MMA
-                    const uint64_t dq = make_smem_desc(q_smem + kb * 32, 16, 1024, kSwizzle128B);
-                    const uint64_t dk = make_smem_desc(k_smem + st * kTileBytes + kb * 32, 16, 1024, kSwizzle128B);
-                    const uint32_t id = idesc_qk | (static_cast<uint32_t>(kb) << 29) | (static_cast<uint32_t>(kb) << 4);
-                    mma_mxf8_ss(t_s, dq, dk, id, t_sfq + (static_cast<uint32_t>(kb) << 30), t_sfk + (static_cast<uint32_t>(kb) << 30), kb > 0 ? 1u : 0u);
-                }
-                stamp(mma_trace, 2, j, 4);
-                tc_commit(bar_s_full(j & 1));
-                tc_commit(bar_k_empty(st));
-                stamp(mma_trace, 2, j, 5);
-            }
-            __syncwarp();
-            return true;
-        };
-        auto issue_pv = [&](int i) -> bool {
-            // O (+)= P(i) V(i), L (+)= P(i) 1: P from TMEM (32 columns, 8 per 32 keys), V tile = 128 keys x 128 B, MN-major
-            if (lane == 0) stamp(mma_trace, 3, i, 0);
-            if (!mbar_wait(bar_p_full(i & 1), (i >> 1) & 1, abort_flag)) return false;
-            if (lane == 0) stamp(mma_trace, 3, i, 1);
-            if (!mbar_wait(bar_v_full(i % kStages), (i / kStages) & 1, abort_flag)) return false;
-            tc_fence_after_sync();
-            if (lane == 0) stamp(mma_trace, 3, i, 2);
-            if (lane == 0) {
-                const int st = i % kStages;
-                const uint32_t t_p = tmem + ((i & 1) ? kColP1 : kColP0);
-#pragma unroll
-                for (int kb = 0; kb < 4; ++kb) {
-                    // MN-major B: 8-key groups 1024 B apart; the second 128-byte-wide atom (columns 128..) is the tile of ones
-                    const uint32_t v_addr = v_smem + st * kTileBytes + kb * 4096;
-                    const uint64_t dv = make_smem_desc(v_addr, ones_smem - v_addr, 1024, kSwizzle128B);
-                    mma_f8_ts(tmem + kColO, t_p + 8 * kb, dv, idesc_pv, (i > 0 || kb > 0) ? 1u : 0u);
-                }
-                stamp(mma_trace, 3, i, 3);
-                tc_commit(bar_v_empty(st));
-                tc_commit(bar_o_done(i & 1));
-                stamp(mma_trace, 3, i, 4);
-            }
-            __syncwarp();
-            return true;
-        };
+            if (ok) tmem_cp_sf(t_sfq, make_smem_desc(sfq_smem, 0, 128, kSwizzleNone));
 
-        // Event loop: whichever of "next score tile" and "next P V" has its inputs ready is issued; neither ever blocks the other, so a
-        // warpgroup that has handed its S buffer back gets its next score tile while the other group is still working on its P.
-        auto qk_ready = [&](int j) -> bool {
-            bool rdy = mbar_test_wait(bar_k_full(j % kStages), (j / kStages) & 1);
-            if (rdy && j >= 2) rdy = mbar_test_wait(bar_s_free(j & 1), ((j >> 1) - 1) & 1);
-            return __shfl_sync(0xFFFFFFFFu, rdy ? 1 : 0, 0) != 0;
-        };
-        auto pv_ready = [&](int i) -> bool {
-            const bool rdy = mbar_test_wait(bar_p_full(i & 1), (i >> 1) & 1) && mbar_test_wait(bar_v_full(i % kStages), (i / kStages) & 1);
-            return __shfl_sync(0xFFFFFFFFu, rdy ? 1 : 0, 0) != 0;
-        };
-        int qk_next = 0, pv_next = 0;
-        long long t_idle = clock64();
-        while (ok && pv_next < n_tiles) {
-            bool progressed = false;
-            if (qk_next < n_tiles && qk_ready(qk_next)) {
-                ok = issue_qk(qk_next++);
-                progressed = true;
-            }
-            if (ok && pv_next < qk_next && pv_ready(pv_next)) {
-                ok = issue_pv(pv_next++);
-                progressed = true;
-            }
-            if (progressed) {
-                t_idle = clock64();
-            } else {
-                // (no sleep: nanosleep wakes on a coarse timer tick)
-                if (*abort_flag != 0u || clock64() - t_idle > kWaitBudgetCycles) {
+            long long t_idle = clock64();
+            for (int j = 0; ok && j < n_tiles;) {
+                // S[j&1] = Q K(j)^T: needs the K tile and its scales, and the softmax of tile j-2 to have read S[j&1] out
+                const int st = j % kStages;
+                if (mbar_test_wait(bar_k_full(st), (j / kStages) & 1) && (j < 2 || mbar_test_wait(bar_s_free(j & 1), ((j >> 1) - 1) & 1))) {
+                    tc_fence_after_sync();
+                    stamp(mma_trace, 2, j, 2);
+                    const uint32_t t_sfk = tmem + ((j & 1) ? kColSfK1 : kColSfK0);
+                    const uint32_t t_s = tmem + ((j & 1) ? kColS1 : kColS0);
+                    tmem_cp_sf(t_sfk, dsf0 + static_cast<uint64_t>((st * kSfBytes) >> 4));
+                    const uint64_t dk = dk0 + static_cast<uint64_t>((st * kTileBytes) >> 4);
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) {
+                        const uint32_t id = idesc_qk | (static_cast<uint32_t>(kb) << 29) | (static_cast<uint32_t>(kb) << 4);
+                        mma_mxf8_ss(t_s, dq0 + 2u * kb, dk + 2u * kb, id, t_sfq + (static_cast<uint32_t>(kb) << 30),
+                                    t_sfk + (static_cast<uint32_t>(kb) << 30), kb > 0 ? 1u : 0u);
+                    }
+                    stamp(mma_trace, 2, j, 4);
+                    tc_commit(bar_s_full(j & 1));
+                    tc_commit(bar_k_empty(st));
+                    stamp(mma_trace, 2, j, 5);
+                    ++j;
+                    t_idle = clock64();
+                } else if (*abort_flag != 0u || clock64() - t_idle > kWaitBudgetCycles) {
                     *abort_flag = 1u;
                     ok = false;
                 }
             }
         }
+        __syncwarp();
+    } else if (warp == kPvWarp) {
+        // =========================================================== MMA issuer: P V ===========================================================
+        if (lane == 0) {
+            // P V with N = 144: head dims 0..127 from the V tile, 16 more columns from the tile of ones (O | L are adjacent in TMEM)
+            const uint32_t idesc_pv = idesc_f8_dense(128, 144, 0, 1);
+            float* mma_trace = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
+            bool ok = true;
+            long long t_idle = clock64();
+            for (int i = 0; ok && i < n_tiles;) {
+                // O (+)= P(i) V(i) with the row sums riding along: P from TMEM (32 columns, 8 per 32 keys), V tile = 128 keys x 128 B, MN-major
+                const int st = i % kStages;
+                if (mbar_test_wait(bar_p_full(i & 1), (i >> 1) & 1) && mbar_test_wait(bar_v_full(st), (i / kStages) & 1)) {
+                    tc_fence_after_sync();
+                    stamp(mma_trace, 3, i, 2);
+                    const uint32_t t_p = tmem + ((i & 1) ? kColP1 : kColP0);
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) {
+                        // MN-major B: 8-key groups 1024 B apart; the second 128-byte-wide atom (columns 128..) is the tile of ones
+                        const uint32_t v_addr = v_smem + st * kTileBytes + kb * 4096;
+                        const uint64_t dv = make_smem_desc(v_addr, ones_smem - v_addr, 1024, kSwizzle128B);
+                        mma_f8_ts(tmem + kColO, t_p + 8 * kb, dv, idesc_pv, (i > 0 || kb > 0) ? 1u : 0u);
+                    }
+                    stamp(mma_trace, 3, i, 3);
+                    tc_commit(bar_v_empty(st));
+                    tc_commit(bar_o_done(i & 1));
+                    stamp(mma_trace, 3, i, 4);
+                    ++i;
+                    t_idle = clock64();
+                } else if (*abort_flag != 0u || clock64() - t_idle > kWaitBudgetCycles) {
+                    *abort_flag = 1u;
+                    ok = false;
+                }
+            }
+        }
+        __syncwarp();
     } else if (warp >= kFirstSoftmaxWarp) {
         // =========================================================== softmax + epilogue ===========================================================
         const uint32_t g = (threadIdx.x - 32u * kFirstSoftmaxWarp) >> 7;   // warpgroup: key tiles j = g mod 2; in the epilogue head dims [64 g, 64 g + 64) of O
@@ -440,6 +443,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         float ref = -INFINITY;   // the row's reference (log2 units) after the last tile this thread has seen
         bool ok = true;
         const bool tracing = (p.trace != nullptr) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+        const bool dumping = tracing && !(p.flags & 0x4u);   // flag 0x4: time stamps only, no tile dumps
 
         // the reference the row has after tile j, published by the thread that handled tile j
         auto wait_ref = [&](int j, float& out) -> bool {
@@ -485,7 +489,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     if (c + 96 >= nvalid) s3[c] = 0xFF800000u;
                 }
             }
-            if (tracing && j == 0) {
+            if (dumping && j == 0) {
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     p.trace[r * 128 + c] = __uint_as_float(s0[c]);
@@ -541,14 +545,25 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             // P = e4m3(2^(s - ref + offset)), four keys per 32-bit TMEM column
             const float sh = kPOffset - ref;
             uint32_t pw[32];
+            if (lazy) {
+                const float cf = (kPOffset + 7.0f - kFastBias - ref) * 0.03125f;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                pw[c] = p_word(s0[4 * c], s0[4 * c + 1], s0[4 * c + 2], s0[4 * c + 3], sh);
-                pw[8 + c] = p_word(s1[4 * c], s1[4 * c + 1], s1[4 * c + 2], s1[4 * c + 3], sh);
-                pw[16 + c] = p_word(s2[4 * c], s2[4 * c + 1], s2[4 * c + 2], s2[4 * c + 3], sh);
-                pw[24 + c] = p_word(s3[4 * c], s3[4 * c + 1], s3[4 * c + 2], s3[4 * c + 3], sh);
+                for (int c = 0; c < 8; ++c) {
+                    pw[c] = p_word_hybrid(s0[4 * c], s0[4 * c + 1], s0[4 * c + 2], s0[4 * c + 3], sh, cf);
+                    pw[8 + c] = p_word_hybrid(s1[4 * c], s1[4 * c + 1], s1[4 * c + 2], s1[4 * c + 3], sh, cf);
+                    pw[16 + c] = p_word_hybrid(s2[4 * c], s2[4 * c + 1], s2[4 * c + 2], s2[4 * c + 3], sh, cf);
+                    pw[24 + c] = p_word_hybrid(s3[4 * c], s3[4 * c + 1], s3[4 * c + 2], s3[4 * c + 3], sh, cf);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    pw[c] = p_word(s0[4 * c], s0[4 * c + 1], s0[4 * c + 2], s0[4 * c + 3], sh);
+                    pw[8 + c] = p_word(s1[4 * c], s1[4 * c + 1], s1[4 * c + 2], s1[4 * c + 3], sh);
+                    pw[16 + c] = p_word(s2[4 * c], s2[4 * c + 1], s2[4 * c + 2], s2[4 * c + 3], sh);
+                    pw[24 + c] = p_word(s3[4 * c], s3[4 * c + 1], s3[4 * c + 2], s3[4 * c + 3], sh);
+                }
             }
-            if (tracing && j == 0) {
+            if (dumping && j == 0) {
 #pragma unroll
                 for (int c = 0; c < 32; ++c) reinterpret_cast<uint32_t*>(p.trace)[32768 + 256 + r * 32 + c] = pw[c];
             }
@@ -589,7 +604,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 uint32_t o[32];
                 tmem_ld32(t_o + 32 * cc, o);
                 tmem_wait_ld();
-                if (tracing) {
+                if (dumping) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) p.trace[16384 + r * 128 + 64 * g + 32 * cc + c] = __uint_as_float(o[c]);
                 }

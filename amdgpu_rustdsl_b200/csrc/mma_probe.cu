@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(128, 1) mma_probe_kernel(int variant, int iter
     for (uint32_t i = threadIdx.x; i < (32768 + 1024) / 16; i += blockDim.x) reinterpret_cast<uint4*>(gen)[i] = make_uint4(0, 0, 0, 0);
     if (threadIdx.x == 0) {
         *abort_flag = 0u;
-        mbar_init(bar, 1);
+        mbar_init(bar, variant == 8 ? 2 : 1);
         fence_mbar_init();
     }
     if (threadIdx.x < 32) {
@@ -79,10 +79,25 @@ __global__ void __launch_bounds__(128, 1) mma_probe_kernel(int variant, int iter
                     const uint64_t da = make_smem_desc(a_smem + kb * 32, 16, 1024, kSwizzle128B);
                     const uint64_t db = make_smem_desc(b_smem + kb * 32, 16, 1024, kSwizzle128B);
                     mma_f8_ss(d, da, db, idesc_f8_dense(128, 128, 0, 0), kb > 0);
-                } else {   // 6: the 16-column row-sum MMA (A from tensor memory, unswizzled K-major B)
+                } else if (variant == 6) {   // the 16-column row-sum MMA (A from tensor memory, unswizzled K-major B)
                     const uint64_t db = make_smem_desc(b_smem, 128, 256, kSwizzleNone);
                     mma_f8_ts(d, tmem + 256 + 8 * kb, db, idesc_f8_dense(128, 16, 0, 0), kb > 0);
+                } else {   // 7 and 8: plain fp8, both from shared memory, N = 256 (B rows wrap inside the 16 KiB tile: timing only)
+                    const uint64_t da = make_smem_desc(a_smem + kb * 32, 16, 1024, kSwizzle128B);
+                    const uint64_t db = make_smem_desc(a_smem + kb * 32, 16, 1024, kSwizzle128B);
+                    mma_f8_ss(tmem, da, db, idesc_f8_dense(128, 256, 0, 0), kb > 0);
                 }
+            }
+        }
+        tc_commit(bar);
+    } else if (threadIdx.x == 32 && variant == 8) {
+        // a second issuing thread, to see whether the issue rate of one thread or the tensor pipe is the limit
+        for (int it = 0; it < iters; ++it) {
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
+                const uint64_t da = make_smem_desc(a_smem + kb * 32, 16, 1024, kSwizzle128B);
+                const uint64_t db = make_smem_desc(b_smem + kb * 32, 16, 1024, kSwizzle128B);
+                mma_f8_ss(tmem + 256, da, db, idesc_f8_dense(128, 128, 0, 0), kb > 0);
             }
         }
         tc_commit(bar);

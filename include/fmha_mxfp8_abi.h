@@ -45,6 +45,7 @@ enum fmha_mxfp8_error {
 /* Bits of `ext_flags` (offset 0x058, padding in the reference's Args, so 0 = reference behaviour). */
 #define FMHA_MXFP8_FLAG_V_BLOCKSCALE 0x1u /* V carries one E8M0 per 32 keys per column at ext_ptr_v_blockscale (extension) */
 #define FMHA_MXFP8_FLAG_EXACT_REBASE 0x2u /* move the softmax reference on every tile (the short-sequence recipe) for any length */
+#define FMHA_MXFP8_FLAG_TRACE_STAMPS_ONLY 0x4u /* with a trace buffer attached: record the time stamps but not the tile dumps */
 
 #pragma pack(push, 1)
 /*
