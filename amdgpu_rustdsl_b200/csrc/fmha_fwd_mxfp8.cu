@@ -39,11 +39,10 @@ namespace {
 constexpr int kRows = 128;          // query rows per CTA tile
 constexpr int kKeys = 128;          // keys per tile
 constexpr int kStages = 5;          // depth of the K ring and of the V ring (freed separately: K after Q K^T, V after P V)
-constexpr int kSoftmaxThreads = 256;
-// The three single-lane service warps get the lowest warp ids: the warp schedulers favour older warps, and a service warp that polls behind
-// two arithmetic-dense softmax warps on its scheduler is otherwise only issued when they stall. Warp 3 idles; softmax = warps 4-11.
-constexpr int kMmaWarp = 0, kProducerWarp = 1, kPvWarp = 2, kFirstSoftmaxWarp = 4;
-constexpr int kThreads = 384;
+// The three service warps get the lowest warp ids: the warp schedulers favour older warps, and a service warp that polls behind
+// two arithmetic-dense softmax warps on its scheduler is otherwise only issued when they stall. Softmax = warps 3-18 (a warp's TMEM lane quadrant is warp % 4, so any four consecutive warps cover the 128 rows).
+constexpr int kMmaWarp = 0, kProducerWarp = 1, kPvWarp = 2, kFirstSoftmaxWarp = 3;
+constexpr int kThreads = 32 * (3 + 16);   // 19 warps: five on three of the four schedulers, hence 96 registers per thread
 constexpr uint32_t kTileBytes = 128 * 128;   // one e4m3 tile
 constexpr uint32_t kSfBytes = 512;           // 128 rows x 4 scale bytes
 
@@ -72,8 +71,9 @@ struct SmemLayout {
     static constexpr uint32_t ones = v + kStages * kTileBytes;
     static constexpr uint32_t sfq = ones + 4096;
     static constexpr uint32_t sfk = sfq + kSfBytes;
-    static constexpr uint32_t xref = sfk + kStages * kSfBytes;   // [tile parity 2][row 128] x {reference bits, tile index}
-    static constexpr uint32_t bars = xref + 2 * 128 * 8;
+    static constexpr uint32_t xref = sfk + kStages * kSfBytes;   // [tile parity 2][half 2][row 128] x {reference bits, tile index}
+    static constexpr uint32_t xmax = xref + 2 * 2 * 128 * 8;     // [buffer 2][tile parity 2][half 2][row 128] x {half-row maximum bits, tile index}
+    static constexpr uint32_t bars = xmax + 2 * 2 * 2 * 128 * 8;
     // barriers (8 bytes each): q_full, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], s_free[2], p_full[2], o_done[2]
     static constexpr uint32_t n_bars = 1 + 4 * kStages + 8;
     static constexpr uint32_t tmem_slot = bars + 8 * n_bars;
@@ -143,8 +143,9 @@ __device__ __forceinline__ uint2 ld_shared_v2(uint32_t addr) {
 // Time stamps of logical block (0,0,0) for the first 32 key tiles (the analogue of the reference's in-kernel stamp buffer,
 // docs/stamps.md): [role 4: softmax group 0, 1, score MMAs, P V MMAs][tile 32][slot 8] 64-bit SM clock values behind the first 37120 words of the trace buffer.
 constexpr int kStampBase = 37120;
-__device__ __forceinline__ void stamp(float* trace, int role, int tile, int slot) {
-    if (trace != nullptr && tile < 32) reinterpret_cast<long long*>(trace + kStampBase)[(role * 32 + tile) * 8 + slot] = clock64();
+template <bool kTrace>
+__device__ __forceinline__ void stamp_t(float* trace, int role, int tile, int slot) {
+    if (kTrace && trace != nullptr && tile < 32) reinterpret_cast<long long*>(trace + kStampBase)[(role * 32 + tile) * 8 + slot] = clock64();
 }
 
 // O columns [col, col + 32) of this thread's lane *= f
@@ -159,10 +160,12 @@ __device__ __forceinline__ void scale_tmem32(uint32_t taddr, float f) {
 
 }  // namespace
 
-template <bool kSplit>
-__global__ void __launch_bounds__(kThreads, 1)
+// kTrace = false compiles every diagnostic (tile dumps, time stamps) out of the tile loop: the production launches use that variant.
+template <bool kSplit, bool kTrace>
+__global__ void __maxnreg__(96)
 fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+    auto stamp = [](float* trace, int role, int tile, int slot) { stamp_t<kTrace>(trace, role, tile, slot); };
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -223,16 +226,16 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_s_full(b), 1);
-            mbar_init(bar_s_free(b), kRows);
-            mbar_init(bar_p_full(b), kRows);
+            mbar_init(bar_s_free(b), 2 * kRows);
+            mbar_init(bar_p_full(b), 2 * kRows);
             mbar_init(bar_o_done(b), 1);
         }
         fence_mbar_init();
     }
-    if (threadIdx.x < kSoftmaxThreads) {
-        for (int i = 0; i < 4; ++i) reinterpret_cast<uint32_t*>(smem_gen + SmemLayout::ones)[threadIdx.x + 256 * i] = 0x38383838u;
-        // hand-over slots start with a tile index no tile has
-        reinterpret_cast<uint2*>(smem_gen + SmemLayout::xref)[threadIdx.x] = make_uint2(0u, 0xFFFFFFFFu);
+    if (threadIdx.x < 512) {
+        for (int i = 0; i < 2; ++i) reinterpret_cast<uint32_t*>(smem_gen + SmemLayout::ones)[threadIdx.x + 512 * i] = 0x38383838u;
+        // hand-over slots (512 reference slots, then 1024 maximum slots) start with a tile index no tile has
+        for (int i = 0; i < 3; ++i) reinterpret_cast<uint2*>(smem_gen + SmemLayout::xref)[threadIdx.x + 512 * i] = make_uint2(0u, 0xFFFFFFFFu);
         fence_proxy_async_smem();
     }
     if (warp == kMmaWarp) {
@@ -432,27 +435,30 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         __syncwarp();
     } else if (warp >= kFirstSoftmaxWarp) {
         // =========================================================== softmax + epilogue ===========================================================
-        const uint32_t g = (threadIdx.x - 32u * kFirstSoftmaxWarp) >> 7;   // warpgroup: key tiles j = g mod 2; in the epilogue head dims [64 g, 64 g + 64) of O
-        const uint32_t r = (threadIdx.x - 32u * kFirstSoftmaxWarp) & 127u;   // query row within the tile = TMEM lane
+        // Four warpgroups: wg = 2 * half + parity. Parity = which key tiles (j = parity mod 2) and which S / P buffer; half = which 64 key
+        // columns of the tile (and, in the epilogue, which 32 head dims together with the parity). Thread r of a group owns query row r.
+        const uint32_t st_id = threadIdx.x - 32u * kFirstSoftmaxWarp;
+        const uint32_t wg = st_id >> 7;
+        const uint32_t par = wg & 1u, half = wg >> 1;
+        const uint32_t r = 32u * (static_cast<uint32_t>(warp) & 3u) + static_cast<uint32_t>(lane);   // TMEM lane = 32 * (warp % 4) + lane
         const uint32_t lane_base = (static_cast<uint32_t>(warp & 3) * 32u) << 16;
         const uint32_t xref = smem_base + SmemLayout::xref;   // 8-byte slots, accessed with single 64-bit shared loads / stores
-        const uint32_t t_s = tmem + (g ? kColS1 : kColS0) + lane_base;
-        const uint32_t t_p = tmem + (g ? kColP1 : kColP0) + lane_base;
-        const uint32_t t_o_all = tmem + kColO + lane_base;
+        const uint32_t xmax = smem_base + SmemLayout::xmax;
+        const uint32_t t_s = tmem + (par ? kColS1 : kColS0) + lane_base + 64u * half;
+        const uint32_t t_p = tmem + (par ? kColP1 : kColP0) + lane_base + 16u * half;
+        const uint32_t t_o_half = tmem + kColO + lane_base + 64u * half;
         const uint32_t t_l = tmem + kColL + lane_base;
         float ref = -INFINITY;   // the row's reference (log2 units) after the last tile this thread has seen
         bool ok = true;
-        const bool tracing = (p.trace != nullptr) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+        const bool tracing = kTrace && (p.trace != nullptr) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
         const bool dumping = tracing && !(p.flags & 0x4u);   // flag 0x4: time stamps only, no tile dumps
 
-        // the reference the row has after tile j, published by the thread that handled tile j
-        auto wait_ref = [&](int j, float& out) -> bool {
-            const uint32_t slot = xref + 8u * (static_cast<uint32_t>(j & 1) * 128u + r);
+        // bounded poll of an 8-byte {value, tile index} slot
+        auto wait_slot = [&](uint32_t slot, int j, float& out) -> bool {
             uint2 o = ld_shared_v2(slot);
             if (o.y != static_cast<uint32_t>(j)) {
                 const long long t0 = clock64();
                 while (true) {
-
                     o = ld_shared_v2(slot);
                     if (o.y == static_cast<uint32_t>(j)) break;
                     if (*abort_flag != 0u || clock64() - t0 > kWaitBudgetCycles) { *abort_flag = 1u; return false; }
@@ -461,59 +467,63 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             out = __uint_as_float(o.x);
             return true;
         };
+        // the reference the row has after tile j: published by both half-row threads that handled tile j, read from the same half
+        auto ref_slot = [&](int j) { return xref + 8u * ((static_cast<uint32_t>(j & 1) * 2u + half) * 128u + r); };
+        // the half-row maximum of tile j: double buffered over this parity's consecutive tiles
+        auto max_slot = [&](int j, uint32_t h) { return xmax + 8u * (((static_cast<uint32_t>((j >> 1) & 1) * 2u + par) * 2u + h) * 128u + r); };
 
-        for (int j = static_cast<int>(g); j < n_tiles; j += 2) {
-            const int k = j >> 1;   // this group's tile counter
-            float* st_trace = (tracing && r == 0) ? p.trace : nullptr;
-            stamp(st_trace, g, j, 0);
-            if (!mbar_wait(bar_s_full(g), k & 1, abort_flag)) { ok = false; break; }
+        for (int j = static_cast<int>(par); j < n_tiles; j += 2) {
+            const int k = j >> 1;   // this parity's tile counter
+            float* st_trace = (tracing && r == 0 && half == 0) ? p.trace : nullptr;
+            stamp(st_trace, par, j, 0);
+            if (!mbar_wait(bar_s_full(par), k & 1, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            stamp(st_trace, g, j, 1);
-            uint32_t s0[32], s1[32], s2[32], s3[32];
-            tmem_ld32(t_s + 0, s0);
-            tmem_ld32(t_s + 32, s1);
-            tmem_ld32(t_s + 64, s2);
-            tmem_ld32(t_s + 96, s3);
-            tmem_wait_ld();
-            tc_fence_before_sync();
-            mbar_arrive(bar_s_free(g));   // the score buffer can take tile j + 2
-            stamp(st_trace, g, j, 2);
-
-            const int nvalid = static_cast<int>(min(static_cast<uint32_t>(kKeys), key_hi - (key_lo + j * kKeys)));
-            if (nvalid < kKeys) {   // keys past the range: -inf for the maximum, 0 for P (crates/amdgpu-tile/src/reduce.rs:35-49)
+            stamp(st_trace, par, j, 1);
+            // Pass 1 over the 64 scores of this half row, 32 at a time: the maximum only. The scores are read again for the conversion
+            // below instead of being kept, which keeps a softmax thread under 96 registers (18 warps share the register file).
+            const int nvalid = static_cast<int>(min(static_cast<uint32_t>(kKeys), key_hi - (key_lo + j * kKeys))) - 64 * static_cast<int>(half);
+            float mt;
+            {
+                float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll 1
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t s[32];
+                    tmem_ld32(t_s + 32 * ch, s);
+                    tmem_wait_ld();
+                    if (nvalid < 64) {   // keys past the range: -inf for the maximum, 0 for P (crates/amdgpu-tile/src/reduce.rs:35-49)
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    if (c >= nvalid) s0[c] = 0xFF800000u;
-                    if (c + 32 >= nvalid) s1[c] = 0xFF800000u;
-                    if (c + 64 >= nvalid) s2[c] = 0xFF800000u;
-                    if (c + 96 >= nvalid) s3[c] = 0xFF800000u;
+                        for (int c = 0; c < 32; ++c) {
+                            if (c + 32 * ch >= nvalid) s[c] = 0xFF800000u;
+                        }
+                    }
+                    if (dumping && j == 0) {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) p.trace[r * 128 + 64 * half + 32 * ch + c] = __uint_as_float(s[c]);
+                    }
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {   // four independent chains of three-input maxima
+                        m0 = max3(m0, __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
+                        m1 = max3(m1, __uint_as_float(s[c + 2]), __uint_as_float(s[c + 3]));
+                        m2 = max3(m2, __uint_as_float(s[c + 4]), __uint_as_float(s[c + 5]));
+                        m3 = max3(m3, __uint_as_float(s[c + 6]), __uint_as_float(s[c + 7]));
+                    }
                 }
+                mt = fmaxf(max3(m0, m1, m2), m3);
             }
-            if (dumping && j == 0) {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    p.trace[r * 128 + c] = __uint_as_float(s0[c]);
-                    p.trace[r * 128 + 32 + c] = __uint_as_float(s1[c]);
-                    p.trace[r * 128 + 64 + c] = __uint_as_float(s2[c]);
-                    p.trace[r * 128 + 96 + c] = __uint_as_float(s3[c]);
-                }
+            stamp(st_trace, par, j, 2);
+            // exchange the half-row maxima with the thread that holds the other 64 keys of this row
+            st_shared_v2(max_slot(j, half), __float_as_uint(mt), static_cast<uint32_t>(j));
+            stamp(st_trace, par, j, 3);
+            {
+                float other = mt;
+                if (!wait_slot(max_slot(j, half ^ 1u), j, other)) ok = false;
+                mt = fmaxf(mt, other);
             }
-            float m0 = __uint_as_float(s0[0]), m1 = __uint_as_float(s1[0]), m2 = __uint_as_float(s2[0]), m3 = __uint_as_float(s3[0]);
-#pragma unroll
-            for (int c = 1; c < 31; c += 2) {   // four independent chains of three-input maxima
-                m0 = max3(m0, __uint_as_float(s0[c]), __uint_as_float(s0[c + 1]));
-                m1 = max3(m1, __uint_as_float(s1[c]), __uint_as_float(s1[c + 1]));
-                m2 = max3(m2, __uint_as_float(s2[c]), __uint_as_float(s2[c + 1]));
-                m3 = max3(m3, __uint_as_float(s3[c]), __uint_as_float(s3[c + 1]));
-            }
-            float mt = fmaxf(max3(m0, m1, __uint_as_float(s0[31])), max3(m2, m3, __uint_as_float(s1[31])));
-            mt = max3(mt, __uint_as_float(s2[31]), __uint_as_float(s3[31]));
-            stamp(st_trace, g, j, 3);
-            // take over the row's reference from the thread that handled tile j - 1
-            if (j > 0 && !wait_ref(j - 1, ref)) ok = false;
+            // take over the row's reference from the threads that handled tile j - 1
+            if (ok && j > 0 && !wait_slot(ref_slot(j - 1), j - 1, ref)) ok = false;
             if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
             // the reference moves when this tile's maximum passes it by more than the threshold (negative for short sequences: it then
-            // also follows the tile maximum down, and f > 1 scales O and L up)
+            // also follows the tile maximum down, and f > 1 scales O and L up). Both halves of a row see the same mt and ref.
             const bool move = mt > ref + thr;
             float f = 1.0f;
             if (move) {
@@ -521,19 +531,19 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 f = ex2_approx(ref - nref);   // 0 on the first tile (ref = -inf); an exact power of two for integer references
                 ref = nref;
             }
-            st_shared_v2(xref + 8u * (static_cast<uint32_t>(j & 1) * 128u + r), __float_as_uint(ref), static_cast<uint32_t>(j));
-            // P V of this group's previous tile must be done before its P columns are overwritten (and, observed in order, this keeps
-            // the parity of the other group's barrier below unambiguous)
-            stamp(st_trace, g, j, 4);
-            if (k > 0 && !mbar_wait(bar_o_done(g), (k - 1) & 1, abort_flag)) { ok = false; break; }
-            stamp(st_trace, g, j, 5);
+            st_shared_v2(ref_slot(j), __float_as_uint(ref), static_cast<uint32_t>(j));
+            stamp(st_trace, par, j, 4);
+            // P V of this parity's previous tile must be done before its P columns are overwritten (and, observed in order, this keeps
+            // the phase parity of the other parity's barrier below unambiguous)
+            if (k > 0 && !mbar_wait(bar_o_done(par), (k - 1) & 1, abort_flag)) { ok = false; break; }
+            stamp(st_trace, par, j, 5);
             if (j > 0 && __any_sync(0xFFFFFFFFu, move)) {
-                // O holds P V of all tiles before j once the other group's last P V is done; P V of tile j cannot start before this thread's arrive below
-                if (!mbar_wait(bar_o_done(g ^ 1u), ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                // O holds P V of all tiles before j once the other parity's last P V is done; P V of tile j cannot start before this thread's arrive below
+                if (!mbar_wait(bar_o_done(par ^ 1u), ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
-#pragma unroll 1
-                for (int cc = 0; cc < 4; ++cc) scale_tmem32(t_o_all + 32 * cc, f);
-                {   // the row sum lives in column 0 of L
+                scale_tmem32(t_o_half, f);
+                scale_tmem32(t_o_half + 32, f);
+                if (half == 0) {   // the row sum lives in column 0 of L
                     uint32_t lv;
                     asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(lv) : "r"(t_l) : "memory");
                     tmem_wait_ld();
@@ -542,47 +552,53 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 }
                 tmem_wait_st();
             }
-            // P = e4m3(2^(s - ref + offset)), four keys per 32-bit TMEM column
+            // Pass 2: P = e4m3(2^(s - ref + offset)), four keys per 32-bit TMEM column
             const float sh = kPOffset - ref;
-            uint32_t pw[32];
-            if (lazy) {
-                const float cf = (kPOffset + 7.0f - kFastBias - ref) * 0.03125f;
+            const float cf = (kPOffset + 7.0f - kFastBias - ref) * 0.03125f;
+            uint32_t pw[16];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    pw[c] = p_word_hybrid(s0[4 * c], s0[4 * c + 1], s0[4 * c + 2], s0[4 * c + 3], sh, cf);
-                    pw[8 + c] = p_word_hybrid(s1[4 * c], s1[4 * c + 1], s1[4 * c + 2], s1[4 * c + 3], sh, cf);
-                    pw[16 + c] = p_word_hybrid(s2[4 * c], s2[4 * c + 1], s2[4 * c + 2], s2[4 * c + 3], sh, cf);
-                    pw[24 + c] = p_word_hybrid(s3[4 * c], s3[4 * c + 1], s3[4 * c + 2], s3[4 * c + 3], sh, cf);
+            for (int ch = 0; ch < 2; ++ch) {
+                uint32_t s[32];
+                tmem_ld32(t_s + 32 * ch, s);
+                tmem_wait_ld();
+                if (ch == 1) {
+                    tc_fence_before_sync();
+                    mbar_arrive(bar_s_free(par));   // the score buffer can take tile j + 2 once all 256 threads of this parity are done with it
                 }
-            } else {
+                if (nvalid < 64) {
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    pw[c] = p_word(s0[4 * c], s0[4 * c + 1], s0[4 * c + 2], s0[4 * c + 3], sh);
-                    pw[8 + c] = p_word(s1[4 * c], s1[4 * c + 1], s1[4 * c + 2], s1[4 * c + 3], sh);
-                    pw[16 + c] = p_word(s2[4 * c], s2[4 * c + 1], s2[4 * c + 2], s2[4 * c + 3], sh);
-                    pw[24 + c] = p_word(s3[4 * c], s3[4 * c + 1], s3[4 * c + 2], s3[4 * c + 3], sh);
+                    for (int c = 0; c < 32; ++c) {
+                        if (c + 32 * ch >= nvalid) s[c] = 0xFF800000u;
+                    }
+                }
+                if (lazy) {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) pw[8 * ch + c] = p_word_hybrid(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], sh, cf);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) pw[8 * ch + c] = p_word(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], sh);
                 }
             }
             if (dumping && j == 0) {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) reinterpret_cast<uint32_t*>(p.trace)[32768 + 256 + r * 32 + c] = pw[c];
+                for (int c = 0; c < 16; ++c) reinterpret_cast<uint32_t*>(p.trace)[32768 + 256 + r * 32 + 16 * half + c] = pw[c];
             }
-            stamp(st_trace, g, j, 6);
-            tmem_st32(t_p, pw);
+            stamp(st_trace, par, j, 6);
+            tmem_st16(t_p, pw);
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(bar_p_full(g));
-            stamp(st_trace, g, j, 7);
+            mbar_arrive(bar_p_full(par));
+            stamp(st_trace, par, j, 7);
         }
 
-        // ---- epilogue: O * v_descale / l; group g stores head dims [64 g, 64 g + 64) ----
+        // ---- epilogue: O * v_descale / l; warpgroup wg stores head dims [32 wg, 32 wg + 32) ----
         if (ok && n_tiles > 0) {
             const int last = n_tiles - 1;
-            const int mine = ((last & 1) == static_cast<int>(g)) ? last : last - 1;   // this group's last tile (-1: none)
-            if (mine >= 0) ok = mbar_wait(bar_o_done(g), (mine >> 1) & 1, abort_flag);
-            const int theirs = ((last & 1) == static_cast<int>(g)) ? last - 1 : last;
-            if (ok && theirs >= 0) ok = mbar_wait(bar_o_done(g ^ 1u), (theirs >> 1) & 1, abort_flag);
-            if (ok) ok = wait_ref(last, ref);
+            const int mine = ((last & 1) == static_cast<int>(par)) ? last : last - 1;   // this parity's last tile (-1: none)
+            if (mine >= 0) ok = mbar_wait(bar_o_done(par), (mine >> 1) & 1, abort_flag);
+            const int theirs = ((last & 1) == static_cast<int>(par)) ? last - 1 : last;
+            if (ok && theirs >= 0) ok = mbar_wait(bar_o_done(par ^ 1u), (theirs >> 1) & 1, abort_flag);
+            if (ok) ok = wait_slot(ref_slot(last), last, ref);
         }
         tc_fence_after_sync();
         if (ok && n_tiles > 0) {
@@ -594,24 +610,21 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const float fin = vd / l;   // crates/amdgpu-stage/src/attention/state.rs:79-82
             const uint32_t row = row0 + r;
             const bool row_ok = row < p.S;   // rows past the sequence are computed on clamped scales and not stored (block3.rs:194)
-            const uint32_t t_o = t_o_all + 64 * g;
-            if (tracing && g == 0) {
+            if (tracing && wg == 0) {
                 p.trace[32768 + r] = l;
                 p.trace[32768 + 128 + r] = ref;
             }
-#pragma unroll 1
-            for (int cc = 0; cc < 2; ++cc) {
-                uint32_t o[32];
-                tmem_ld32(t_o + 32 * cc, o);
-                tmem_wait_ld();
-                if (dumping) {
+            uint32_t o[32];
+            tmem_ld32(tmem + kColO + lane_base + 32u * wg, o);
+            tmem_wait_ld();
+            if (dumping) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) p.trace[16384 + r * 128 + 64 * g + 32 * cc + c] = __uint_as_float(o[c]);
-                }
-                if (!row_ok) continue;
+                for (int c = 0; c < 32; ++c) p.trace[16384 + r * 128 + 32 * wg + c] = __uint_as_float(o[c]);
+            }
+            if (row_ok) {
                 if (kSplit) {
                     const size_t prow = static_cast<size_t>(split) * p.rows_total + (static_cast<size_t>(batch) * p.S + row) * p.H + head;
-                    float4* dst = reinterpret_cast<float4*>(p.ohat + prow * 128 + 64 * g + 32 * cc);
+                    float4* dst = reinterpret_cast<float4*>(p.ohat + prow * 128 + 32 * wg);
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
                         dst[c] = make_float4(__uint_as_float(o[4 * c]) * fin, __uint_as_float(o[4 * c + 1]) * fin,
@@ -619,7 +632,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     }
                 } else {
                     uint8_t* orow = p.o + static_cast<size_t>(batch) * p.o_batch_stride + static_cast<size_t>(row) * p.o_row_stride + head * 256u;
-                    uint4* dst = reinterpret_cast<uint4*>(orow + 128 * g + 64 * cc);
+                    uint4* dst = reinterpret_cast<uint4*>(orow + 64 * wg);
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t wv[4];
@@ -631,14 +644,14 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         dst[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
                     }
                 }
-            }
-            if (row_ok && g == 0) {
-                const float lse2 = ref - kPOffset + lg2_approx(l);   // log2 of sum_j 2^(s_j)
-                if (kSplit) {
-                    const size_t prow = static_cast<size_t>(split) * p.rows_total + (static_cast<size_t>(batch) * p.S + row) * p.H + head;
-                    p.lse2[prow] = lse2;
-                } else if (p.lse_nat != nullptr) {
-                    p.lse_nat[(static_cast<size_t>(batch) * p.H + head) * p.S + row] = lse2 * 0.6931471805599453f;
+                if (wg == 0) {
+                    const float lse2 = ref - kPOffset + lg2_approx(l);   // log2 of sum_j 2^(s_j)
+                    if (kSplit) {
+                        const size_t prow = static_cast<size_t>(split) * p.rows_total + (static_cast<size_t>(batch) * p.S + row) * p.H + head;
+                        p.lse2[prow] = lse2;
+                    } else if (p.lse_nat != nullptr) {
+                        p.lse_nat[(static_cast<size_t>(batch) * p.H + head) * p.S + row] = lse2 * 0.6931471805599453f;
+                    }
                 }
             }
         }
@@ -657,20 +670,18 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const AttnParams& p,
                              uint32_t B, bool split, uint32_t rows_per_cta, cudaStream_t stream) {
     (void)rows_per_cta;   // both logical block heights run as 128-row CTAs
-    static bool attr_done[2] = {false, false};
-    cudaError_t e;
-    if (!attr_done[split ? 1 : 0]) {
-        e = split ? cudaFuncSetAttribute(fmha_fwd_mxfp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)
-                  : cudaFuncSetAttribute(fmha_fwd_mxfp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
+    static const Kernel kernels[4] = {fmha_fwd_mxfp8_kernel<false, false>, fmha_fwd_mxfp8_kernel<true, false>,
+                                      fmha_fwd_mxfp8_kernel<false, true>, fmha_fwd_mxfp8_kernel<true, true>};
+    static bool attr_done[4] = {false, false, false, false};
+    const int which = (split ? 1 : 0) + (p.trace != nullptr ? 2 : 0);
+    if (!attr_done[which]) {
+        const cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernels[which]), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
-        attr_done[split ? 1 : 0] = true;
+        attr_done[which] = true;
     }
     dim3 grid((p.S + kRows - 1) / kRows, p.H, B * (split ? p.splits : 1u));
-    if (split) {
-        fmha_fwd_mxfp8_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
-    } else {
-        fmha_fwd_mxfp8_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
-    }
+    kernels[which]<<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
     return cudaGetLastError();
 }
 

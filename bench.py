@@ -295,13 +295,13 @@ def main():
         peak, peak_src = 2.0 * 1590.0, "2 x fallback dense bf16 (1.59 PFLOP/s)"
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
                 "frac_of_nominal_4500": achieved / NOMINAL_MXFP8_TFLOPS, "note": "achieved = 4*B*H*Sq*Skv*128 per launch / mean step time (CUDA events); for kvsplit steps the combine launch is inside the step"}
-    # issue-only ceiling of the MMA shape the kernel uses, measured now
+    # issue-only ceiling of the tensor pipe, measured now: two issuing threads per SM (N = 256 and N = 128 fp8 MMAs, K = 32), no data movement
     try:
         import ctypes as C
         ms = C.c_float(0)
         lib = _abi.load()
-        if lib.fmha_mxfp8_probe_mma_peak(0, 4000, 148, None, C.byref(ms)) == 0 and ms.value > 0:
-            roofline["mma_issue_ceiling_tflops"] = 148 * 4000 * 4 * 2.0 * 128 * 128 * 32 / (ms.value * 1e-3) / 1e12
+        if lib.fmha_mxfp8_probe_mma_peak(8, 4000, 148, None, C.byref(ms)) == 0 and ms.value > 0:
+            roofline["mma_issue_ceiling_tflops"] = 148 * 4000 * 4 * 2.0 * 128 * (256 + 128) * 32 / (ms.value * 1e-3) / 1e12
     except Exception:
         pass
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True,
