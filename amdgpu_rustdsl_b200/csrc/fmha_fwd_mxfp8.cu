@@ -11,19 +11,21 @@
 //   out    : O * v_descale / l as bf16 (state.rs:79-82), or for the split kernel the normalised f32 partial plus a base-2
 //            log-sum-exp per row (block3.rs:291-356).
 //
-// Mapping onto the SM (not a translation of the gfx950 wave layout):
-//   warps 4-11 softmax + epilogue, two warpgroups that take alternate key tiles (warpgroup w owns tiles j = w mod 2), so that one
-//              group's TMEM round trips overlap the other group's arithmetic. Thread r of either group owns query row r = TMEM
-//              lane r: it reads the whole score row with tcgen05.ld and hands the S buffer back at once, takes the row's reference
-//              from the thread that handled the previous tile (one 8-byte shared-memory slot per row), writes P (packed e4m3) to
-//              the group's own P columns with tcgen05.st, and rescales O in TMEM when the reference moves.
-//   warp  0    MMA issuer: one lane issues tcgen05.mma; S = Q K^T is kind::mxf8f6f4.block_scale with both operands in swizzled
-//              shared memory and the E8M0 factors in TMEM (tcgen05.cp); O += P V takes P from TMEM and V (keys x head dim, i.e.
-//              MN-major B) from shared memory; L += P 1 (a 16-column MMA against a tile of e4m3 ones) is the row sum of the
-//              quantised P, which costs no ALU work (the reference sums P with a matrix instruction too, reduce.rs:163-173).
-//              Issue order QK(0) QK(1) | QK(j+2) PV(j) ...: two score tiles are always ahead of the softmax.
-//   warp  1    producer: TMA loads of the Q tile and of the K/V tiles into a ring, plus the 4-byte-per-row scale gathers, which
-//              a TMA box cannot express, written in the 32x16-byte layout tcgen05.cp expects.
+// Mapping onto the SM (not a translation of the gfx950 wave layout), 19 warps:
+//   warp  0    Q K^T issuer: one lane issues S[j % 2] = Q K_j^T as kind::mxf8f6f4.block_scale tcgen05.mma, both operands in swizzled
+//              shared memory, the E8M0 factors copied to TMEM with tcgen05.cp. Two score tiles are always ahead of the softmax.
+//   warp  1    producer: TMA loads of the Q tile and of the K and V tiles into two rings (K is freed after Q K^T, V after P V), plus
+//              the 4-byte-per-row scale gathers, which a TMA box cannot express, written in the 32x16-byte layout tcgen05.cp expects.
+//   warp  2    P V issuer: O += P_j V_j with P from TMEM and V (keys x head dim, i.e. MN-major B) from shared memory. The B operand
+//              is 144 wide: 128 head dims plus 16 columns of a tile of e4m3 ones, so that O[:, 128..143] (= the L columns) holds the
+//              row sums of the *quantised* P at no ALU cost (the reference sums P with a matrix instruction too, reduce.rs:163-173).
+//              A second issuing thread matters: one thread issues an MMA about every 75 clocks whatever its N.
+//   warps 3-18 softmax + epilogue, four warpgroups: warpgroup 2 * half + parity works on key tiles j = parity (mod 2) and on keys
+//              [64 half, 64 half + 64) of them. Thread r of a group owns query row r = TMEM lane r. Per tile it reads its 64 scores
+//              twice with tcgen05.ld (maximum, then conversion: holding them would need more than the 96 registers that 19 warps
+//              leave a thread), exchanges the half-row maximum with the sibling half and the row reference with the group of the
+//              previous tile through 8-byte shared-memory slots {value, tile index}, writes P (packed e4m3) with tcgen05.st, and
+//              rescales its half of O in TMEM on the rare tiles that move the reference.
 // TMEM columns: S0 [0,128) S1 [128,256) O [256,384) L [384,400) P0 [400,432) P1 [432,464) SFQ [464,468) SFK0 [468,472) SFK1 [472,476).
 #include "kernels.h"
 #include "ptx_sm100.cuh"

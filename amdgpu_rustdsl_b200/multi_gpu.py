@@ -81,8 +81,9 @@ def exchange_partials(ohat, lse, ohat_all, lse_all, group=None):
     """The one exchange step of the key-range sharding: all-gather of every rank's partials into local memory (rank-major, which is the
     [splits][rows_total] layout the combine kernel reads)."""
     import torch.distributed as dist
-    dist.all_gather_into_tensor(ohat_all, ohat, group=group)
-    dist.all_gather_into_tensor(lse_all, lse, group=group)
+    # the output as the concatenation along dim 0 (the form every backend accepts; gloo rejects the stacked [world, ...] shape)
+    dist.all_gather_into_tensor(ohat_all.view(-1, ohat.shape[-1]), ohat, group=group)
+    dist.all_gather_into_tensor(lse_all.view(-1), lse, group=group)
 
 
 def fmha_fwd_mxfp8_kv_sharded(q, k_local, v_local, q_scale, k_scale_local, v_scale, out, ws, group=None):
