@@ -34,10 +34,37 @@ WORKLOADS = {  # B, H, HK, Sq, Skv, forced path, splits
 }
 METRIC = "MXFP8 FMHA fwd TFLOP/s (hd128), 4*B*H*Sq*Skv*128 / t"
 NOMINAL_MXFP8_TFLOPS = 4500.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant (attention) kernel, from the ncu capture summarised in
+# profiles/fmha_fwd_mxfp8_kernel_c2.md; only the captured workload has a figure
+NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 25.74e6 + 0.01e6}
 
 
 def flops(B, H, S, SK):
     return 4.0 * B * H * S * SK * 128
+
+
+def synthetic_inputs(B, H, HK, S, SK, seed):
+    """Seeded stand-in for the reference harness's REF_DATA=normal inputs (tests/gpu/ref_host.cpp:214-263), made with torch on the CPU:
+    standard-normal Q (pre-multiplied by log2(e)/sqrt(128)), K and V; Q and K quantised to e4m3 with one E8M0 scale per 32 head-dim
+    elements, V to e4m3 with one f32 descale. Returns uint8 tensors q [B,S,H,128], k, v [B,SK,HK,128], qs [B*S*H*4], ks [B*SK*HK*4] and the
+    V descale."""
+    import math
+    import torch
+    g = torch.Generator().manual_seed(seed)
+
+    def block_quant(x):
+        xb = x.view(*x.shape[:-1], 4, 32)
+        amax = xb.abs().amax(-1).clamp_min(2.0 ** -100)
+        e = torch.floor(torch.log2(amax)) - 8.0          # e4m3 tops out at 1.75 * 2^8
+        q = (xb * torch.exp2(-e).unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+        return q.view(x.shape), (e + 127.0).clamp(0, 254).to(torch.uint8).reshape(-1)
+
+    q, qs = block_quant(torch.randn(B, S, H, 128, generator=g) * (math.log2(math.e) / math.sqrt(128.0)))
+    k, ks = block_quant(torch.randn(B, SK, HK, 128, generator=g))
+    vf = torch.randn(B, SK, HK, 128, generator=g)
+    vd = float(vf.abs().max()) / 448.0
+    v = (vf / vd).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+    return {"q": q, "k": k, "v": v, "qs": qs, "ks": ks}, vd
 
 
 def measured_peaks():
@@ -158,7 +185,6 @@ def main():
     import torch
     import torch.distributed as dist
     from amdgpu_rustdsl_b200 import _abi, device_status, fmha_fwd_mxfp8, multi_gpu
-    from oracle import oracle as O   # input generator + CPU baseline leg only
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -190,28 +216,24 @@ def main():
     nsets = args.sets or max(2, min(16, -(-160 * 2 ** 20 // bytes_per_set)))
     if wl in ("c4", "c5"):
         nsets = args.sets or 1   # one set already exceeds L2
-    gen_B = B
-    if wl == "c4":
-        gen_B = 1   # generate one batch element on the CPU and tile it: 16 x 64 x 4096 rows of Box-Muller would take minutes
-    inp = O.generate("normal", gen_B, Hl, S, SKl, HKl)
-    rep = B // gen_B
-
-    def dev_tile(a, shape):
-        t = torch.from_numpy(a.reshape(shape))
-        return (t.repeat(rep, *([1] * (len(shape) - 1))) if rep > 1 else t)
-
-    host = {"q": dev_tile(inp.q, (gen_B, S, Hl, 128)), "k": dev_tile(inp.k, (gen_B, SKl, HKl, 128)), "v": dev_tile(inp.v, (gen_B, SKl, HKl, 128))}
+    # generate one batch element (and at most 8192 keys) on the CPU and tile it: the arithmetic does not depend on the values repeating
+    gen_B = 1 if wl == "c4" else B
+    gen_SK = min(SKl, 8192)
+    rep, krep = B // gen_B, SKl // gen_SK
+    assert gen_B * rep == B and gen_SK * krep == SKl
+    gen, vdescale = synthetic_inputs(gen_B, Hl, HKl, S, gen_SK, seed=1234 + rank)
+    host = {"q": gen["q"].repeat(rep, 1, 1, 1), "k": gen["k"].repeat(rep, krep, 1, 1), "v": gen["v"].repeat(rep, krep, 1, 1)}
     qs = torch.zeros(B * S * Hl * 4 + 512 * Hl * 4, dtype=torch.uint8)
-    qs[: B * S * Hl * 4] = torch.from_numpy(inp.qs[: gen_B * S * Hl * 4]).repeat(rep)
+    qs[: B * S * Hl * 4] = gen["qs"].repeat(rep)
     ks = torch.zeros(B * SKl * HKl * 4 + 640 * Hl * 4, dtype=torch.uint8)
-    ks[: B * SKl * HKl * 4] = torch.from_numpy(inp.ks[: gen_B * SKl * HKl * 4]).repeat(rep)
+    ks[: B * SKl * HKl * 4] = gen["ks"].view(gen_B, gen_SK * HKl * 4).repeat(rep, krep).reshape(-1)
     host["qs"], host["ks"] = qs, ks
     host = {n: t.contiguous().pin_memory() for n, t in host.items()}
     sets = []
     for _ in range(nsets):
         s = {n: t.to(dev, non_blocking=True) for n, t in host.items()}
         s["vs"] = torch.zeros(1024, dtype=torch.float32, device=dev)
-        s["vs"][0] = inp.vdescale
+        s["vs"][0] = vdescale
         s["out"] = torch.empty(B, S, Hl, 128, dtype=torch.bfloat16, device=dev)
         sets.append(s)
     out_host = torch.empty(B, S, Hl, 128, dtype=torch.bfloat16).pin_memory()
@@ -293,7 +315,9 @@ def main():
         peak, peak_src = 2.0 * float(peaks["bf16_tflops"]), "2 x measured dense bf16 burst (MEASURED_PEAKS.json): fp8 tensor rate is twice bf16"
     else:
         peak, peak_src = 2.0 * 1590.0, "2 x fallback dense bf16 (1.59 PFLOP/s)"
-    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(wl) if world == 1 else None, "traffic_unit": "bytes per launch (ncu, DRAM read + write)",
+                "algorithmic_bytes": B * Hl * S * (128 + 4 + 256) + 2 * B * HKl * SKl * 128 + B * HKl * SKl * 4, "peak_source": peak_src,
                 "frac_of_nominal_4500": achieved / NOMINAL_MXFP8_TFLOPS, "note": "achieved = 4*B*H*Sq*Skv*128 per launch / mean step time (CUDA events); for kvsplit steps the combine launch is inside the step"}
     # issue-only ceiling of the tensor pipe, measured now: two issuing threads per SM (N = 256 and N = 128 fp8 MMAs, K = 32), no data movement
     try:
@@ -305,7 +329,7 @@ def main():
     except Exception:
         pass
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": scaling, "vs_baseline": None, "dtype": "fp8-e4m3 x E8M0 block scales (MXFP8), f32 accumulate, bf16 out", "data": "synthetic (reference harness REF_DATA=normal generator, seeded)",
+            "scaling": scaling, "vs_baseline": None, "dtype": "fp8-e4m3 x E8M0 block scales (MXFP8), f32 accumulate, bf16 out", "data": "synthetic (seeded standard-normal Q/K/V quantised to MXFP8 on the host, the distribution of the reference harness's REF_DATA=normal)",
             "config": {"workload": f"{wl}: B{B} H{H} HK{HK} Sq{S} Skv{SK} hd128, non-causal" + (f", per rank (x{world} ranks)" if scaling == "weak" and world > 1 else ""),
                        "path": ran["path"][0], "splits": ran["path"][1], "l2": f"{nsets} rotating input/output sets of {bytes_per_set / 2**20:.0f} MiB (> 126 MB L2 in total)",
                        "parallelism": "none" if world == 1 else ("batch x head shards, no collective" if wl != "c5" else "key-range shards + NCCL all-gather of partials + combine")},
