@@ -16,6 +16,7 @@ PATH_IDS = {v: k for k, v in PATH_NAMES.items()}
 FLAG_V_BLOCKSCALE = 0x1
 FLAG_EXACT_REBASE = 0x2
 TRACE_BYTES = 4 * (16384 + 16384 + 256 + 4096 + 2048)
+STATIC_SCRATCH_MAX_ROW_SPLITS = 65536   # FMHA_MXFP8_STATIC_SCRATCH_MAX_ROW_SPLITS
 
 ERROR_CLASSES = {1: "GV-HOST-EXTENT", 2: "GV-HOST-KA-RANGE", 3: "GV-HOST-KA-IS", 4: "GV-HOST-GRID", 5: "GV-HOST-SYM", 6: "ARG", 7: "DEVICE"}
 
@@ -113,6 +114,8 @@ def load():
     lib.fmha_mxfp8_dispatch.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.POINTER(C.c_int), C.POINTER(C.c_uint32)]
     lib.fmha_mxfp8_auto.restype = C.c_int
     lib.fmha_mxfp8_auto.argtypes = [C.POINTER(Problem), C.c_int, C.c_uint32, C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_uint32), C.c_char_p, C.c_size_t]
+    lib.fmha_mxfp8_kvsplit_static_scratch.restype = C.c_int
+    lib.fmha_mxfp8_kvsplit_static_scratch.argtypes = [C.POINTER(Problem), C.c_uint32, C.c_void_p, C.c_char_p, C.c_size_t]
     lib.fmha_mxfp8_device_status.restype = C.c_int
     lib.fmha_mxfp8_device_status.argtypes = [C.POINTER(C.c_uint32)]
     lib.fmha_mxfp8_trace_attach.restype = C.c_int
@@ -126,7 +129,7 @@ def load():
 EXPORTS = (
     "fmha_mxfp8_kernel_name", "fmha_mxfp8_kernarg_size", "fmha_mxfp8_workgroup_size", "fmha_mxfp8_validate", "fmha_mxfp8_grid",
     "fmha_mxfp8_launch", "fmha_mxfp8_dispatch", "fmha_mxfp8_auto", "fmha_mxfp8_device_status", "fmha_mxfp8_trace_attach",
-    "fmha_mxfp8_probe_mma_peak",
+    "fmha_mxfp8_probe_mma_peak", "fmha_mxfp8_kvsplit_static_scratch",
 )
 
 

@@ -274,6 +274,23 @@ int fmha_mxfp8_auto(const fmha_mxfp8_problem* prob, int path, uint32_t splits, v
                     char* err, size_t cap);
 
 /*
+ * The kvsplit path (split kernel + combine, same stream) with the partials kept in a fixed array inside the library instead of in
+ * `ws_ohat` / `ws_lse`, which are ignored. This entry has no counterpart in the reference: there the caller always owns the
+ * workspace (tests/gpu/ref_host.cpp:516-569 allocates it per run). It exists for callers that cannot obtain device memory at call
+ * time: their memory is already committed to their own pools, or they run where the CUDA allocator must not be entered because it
+ * synchronises the device. The call allocates nothing and calls no allocating routine.
+ *   - Limit: splits * B * S * H <= FMHA_MXFP8_STATIC_SCRATCH_MAX_ROW_SPLITS (32 MiB of partials + 256 KiB of log-sum-exps per
+ *     device); beyond it the call returns FMHA_MXFP8_E_EXTENT with a message and launches nothing.
+ *   - The first call on a device resolves the array's address (cudaGetSymbolAddress; may load the module): make it at start-up,
+ *     before any stream capture.
+ *   - All calls on a device share the one array: calls that may overlap in time race on it and must be ordered by the caller.
+ *   - Nothing in the array needs clearing: every partial the combine reads is written by the split kernel of the same call.
+ * splits: 2, 4 or 8 (0 = 4). Inputs, output, scale buffers and `flags` are taken from `prob` as in fmha_mxfp8_auto.
+ */
+#define FMHA_MXFP8_STATIC_SCRATCH_MAX_ROW_SPLITS 65536u
+int fmha_mxfp8_kvsplit_static_scratch(const fmha_mxfp8_problem* prob, uint32_t splits, void* stream, char* err, size_t cap);
+
+/*
  * Device status word: 0 when no kernel of this library ever gave up a bounded wait on the current device, else a bit mask of the
  * roles that did. Synchronises the device. No counterpart in the reference (its kernels have no bounded waits); it stands where
  * the reference harness checks hipDeviceSynchronize() after a launch (tests/gpu/ref_host.cpp:400).
