@@ -11,20 +11,22 @@
 //   out    : O * v_descale / l as bf16 (state.rs:79-82), or for the split kernel the normalised f32 partial plus a base-2
 //            log-sum-exp per row (block3.rs:291-356).
 //
-// Mapping onto the SM (not a translation of the gfx950 wave layout), 19 warps:
-//   warp  0    Q K^T issuer: one lane issues S[j % 2] = Q K_j^T as kind::mxf8f6f4.block_scale tcgen05.mma, both operands in swizzled
+// Mapping onto the SM (not a translation of the gfx950 wave layout): a persistent kernel, one CTA of 20 warps per SM, each CTA walking
+// work items (128 query rows of one (batch, head[, split])) with its rings, buffers and barriers running on across items.
+//   warp  0    Q K^T issuer: one lane issues S[g % 2] = Q K_g^T as kind::mxf8f6f4.block_scale tcgen05.mma, both operands in swizzled
 //              shared memory, the E8M0 factors copied to TMEM with tcgen05.cp. Two score tiles are always ahead of the softmax.
-//   warp  1    producer: TMA loads of the Q tile and of the K and V tiles into two rings (K is freed after Q K^T, V after P V), plus
-//              the 4-byte-per-row scale gathers, which a TMA box cannot express, written in the 32x16-byte layout tcgen05.cp expects.
-//   warp  2    P V issuer: O += P_j V_j with P from TMEM and V (keys x head dim, i.e. MN-major B) from shared memory. The B operand
+//   warp  1    Q / K producer: TMA loads of the Q tile (double buffered across items) and of the K ring, plus the 4-byte-per-row scale
+//              gathers, which a TMA box cannot express, written in the 32x16-byte layout tcgen05.cp expects.
+//   warp  2    P V issuer: O += P_g V_g with P from TMEM and V (keys x head dim, i.e. MN-major B) from shared memory. The B operand
 //              is 144 wide: 128 head dims plus 16 columns of a tile of e4m3 ones, so that O[:, 128..143] (= the L columns) holds the
 //              row sums of the *quantised* P at no ALU cost (the reference sums P with a matrix instruction too, reduce.rs:163-173).
 //              A second issuing thread matters: one thread issues an MMA about every 75 clocks whatever its N.
-//   warps 3-18 softmax + epilogue, four warpgroups: warpgroup 2 * half + parity works on key tiles j = parity (mod 2) and on keys
+//   warp  3    V producer: TMA loads of the V ring (K is freed after Q K^T, V after P V, so the two rings run apart).
+//   warps 4-19 softmax + epilogue, four warpgroups: warpgroup 2 * half + parity works on tiles g = parity (mod 2) and on keys
 //              [64 half, 64 half + 64) of them. Thread r of a group owns query row r = TMEM lane r. Per tile it reads its 64 scores
-//              twice with tcgen05.ld (maximum, then conversion: holding them would need more than the 96 registers that 19 warps
+//              twice with tcgen05.ld (maximum, then conversion: holding them would need more than the 96 registers that 20 warps
 //              leave a thread), exchanges the half-row maximum with the sibling half and the row reference with the group of the
-//              previous tile through 8-byte shared-memory slots {value, tile index}, writes P (packed e4m3) with tcgen05.st, and
+//              previous tile through 8-byte shared-memory slots {value, tile counter}, writes P (packed e4m3) with tcgen05.st, and
 //              rescales its half of O in TMEM on the rare tiles that move the reference.
 // TMEM columns: S0 [0,128) S1 [128,256) O [256,384) L [384,400) P0 [400,432) P1 [432,464) SFQ [464,468) SFK0 [468,472) SFK1 [472,476).
 #include "kernels.h"
@@ -41,10 +43,10 @@ namespace {
 constexpr int kRows = 128;          // query rows per CTA tile
 constexpr int kKeys = 128;          // keys per tile
 constexpr int kStages = 5;          // depth of the K ring and of the V ring (freed separately: K after Q K^T, V after P V)
-// The three service warps get the lowest warp ids: the warp schedulers favour older warps, and a service warp that polls behind
-// two arithmetic-dense softmax warps on its scheduler is otherwise only issued when they stall. Softmax = warps 3-18 (a warp's TMEM lane quadrant is warp % 4, so any four consecutive warps cover the 128 rows).
-constexpr int kMmaWarp = 0, kProducerWarp = 1, kPvWarp = 2, kFirstSoftmaxWarp = 3;
-constexpr int kThreads = 32 * (3 + 16);   // 19 warps: five on three of the four schedulers, hence 96 registers per thread
+// The four service warps get the lowest warp ids, one per scheduler (scheduler = warp % 4). Softmax = warps 4-19: a warp's TMEM lane
+// quadrant is warp % 4, so any four consecutive warps cover the 128 rows.
+constexpr int kMmaWarp = 0, kKProducerWarp = 1, kPvWarp = 2, kVProducerWarp = 3, kFirstSoftmaxWarp = 4;
+constexpr int kThreads = 32 * (4 + 16);   // 20 warps, five per scheduler (16 K registers each), hence 96 registers per thread
 constexpr uint32_t kTileBytes = 128 * 128;   // one e4m3 tile
 constexpr uint32_t kSfBytes = 512;           // 128 rows x 4 scale bytes
 
@@ -66,23 +68,25 @@ constexpr float kFollowWindow = 11.0f;
 struct SmemLayout {
     // all tile buffers are 1024-byte aligned (128-byte swizzle atom = 8 rows x 128 B)
     static constexpr uint32_t q = 0;
-    static constexpr uint32_t k = q + kTileBytes;
+    static constexpr uint32_t k = q + 2 * kTileBytes;   // two Q tiles: the next item's is loaded while the current one is in use
     static constexpr uint32_t v = k + kStages * kTileBytes;
     // 32 keys x 128 B of e4m3 1.0 behind the V ring: a second MN-major atom of the P V B operand, of which the MMA uses 16 columns,
     // so that O[:, 128..143] accumulates the row sums of P
     static constexpr uint32_t ones = v + kStages * kTileBytes;
     static constexpr uint32_t sfq = ones + 4096;
-    static constexpr uint32_t sfk = sfq + kSfBytes;
+    static constexpr uint32_t sfk = sfq + 2 * kSfBytes;
     static constexpr uint32_t xref = sfk + kStages * kSfBytes;   // [tile parity 2][half 2][row 128] x {reference bits, tile index}
     static constexpr uint32_t xmax = xref + 2 * 2 * 128 * 8;     // [buffer 2][tile parity 2][half 2][row 128] x {half-row maximum bits, tile index}
     static constexpr uint32_t bars = xmax + 2 * 2 * 2 * 128 * 8;
-    // barriers (8 bytes each): q_full, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], s_free[2], p_full[2], o_done[2]
-    static constexpr uint32_t n_bars = 1 + 4 * kStages + 8;
+    // barriers (8 bytes each): q_full[2], q_empty[2], k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], s_free[2],
+    // p_full[2], o_done[2], o_free
+    static constexpr uint32_t n_bars = 4 + 4 * kStages + 9;
     static constexpr uint32_t tmem_slot = bars + 8 * n_bars;
     static constexpr uint32_t abort_flag = tmem_slot + 4;
     static constexpr uint32_t total = abort_flag + 4;
 };
 constexpr uint32_t kSmemBytes = SmemLayout::total + 1024;   // + slack to align the base to 1024
+static_assert(kSmemBytes <= 227 * 1024, "shared memory budget of one CTA");
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -160,8 +164,47 @@ __device__ __forceinline__ void scale_tmem32(uint32_t taddr, float f) {
     tmem_st32(taddr, o);
 }
 
+// One unit of work of the persistent kernel: 128 query rows of one (batch, head) against the key range of one split.
+struct Item {
+    uint32_t row0, head, batch, split, kv_head, key_lo, key_hi;
+    int n_tiles;
+};
+
+template <bool kSplit>
+__device__ __forceinline__ Item decode_item(uint32_t w, const AttnParams& p) {
+    // w = (z * H + head) * n_qtiles + q tile: neighbouring CTAs work on neighbouring row blocks of one head, whose K / V they share in L2
+    Item it;
+    const uint32_t x = w % p.n_qtiles, yz = w / p.n_qtiles;
+    it.row0 = x * kRows;
+    it.head = yz % p.H;
+    const uint32_t z = yz / p.H;
+    it.batch = z;
+    it.split = 0;
+    if (kSplit) {
+        it.batch = z >> p.split_log2;
+        it.split = z & (p.splits - 1u);
+    }
+    it.kv_head = it.head >> p.gqa_shift;   // crates/amdgpu-stage/src/components.rs:8-17
+    const uint32_t ntiles_total = (p.SK + kKeys - 1) / kKeys;
+    it.key_lo = 0;
+    it.key_hi = p.SK;
+    if (kSplit) {   // tiles [split*tps, min(ntiles, (split+1)*tps)) (components.rs:58-74)
+        const uint32_t tps = (ntiles_total + p.splits - 1) / p.splits;
+        const uint32_t tile_lo = it.split * tps;
+        const uint32_t tile_hi = min(ntiles_total, tile_lo + tps);
+        it.key_lo = tile_lo * kKeys;
+        it.key_hi = min(tile_hi * kKeys, p.SK);
+    }
+    it.n_tiles = (it.key_hi > it.key_lo) ? static_cast<int>((it.key_hi - it.key_lo + kKeys - 1) / kKeys) : 0;
+    return it;
+}
+
 }  // namespace
 
+// Persistent: gridDim.x CTAs (one per SM) walk the work items w = blockIdx.x, blockIdx.x + gridDim.x, ... The K / V rings, the score and P
+// buffers and every barrier run on one tile counter g that keeps counting across items, so the next item's Q, K and V loads and its first
+// two score tiles overlap the current item's last tiles and epilogue; only O is single: P V of an item's first tile waits until the
+// epilogue of the item before has read O out (o_free).
 // kTrace = false compiles every diagnostic (tile dumps, time stamps) out of the tile loop: the production launches use that variant.
 template <bool kSplit, bool kTrace>
 __global__ void __maxnreg__(96)
@@ -179,59 +222,46 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const uint32_t sfq_smem = smem_base + SmemLayout::sfq;
     const uint32_t sfk_smem = smem_base + SmemLayout::sfk;
     const uint32_t bar0 = smem_base + SmemLayout::bars;
-    const uint32_t bar_q_full = bar0;
-    auto bar_k_full = [&](int st) { return bar0 + 8u * (1 + st); };
-    auto bar_k_empty = [&](int st) { return bar0 + 8u * (1 + kStages + st); };
-    auto bar_v_full = [&](int st) { return bar0 + 8u * (1 + 2 * kStages + st); };
-    auto bar_v_empty = [&](int st) { return bar0 + 8u * (1 + 3 * kStages + st); };
-    auto bar_s_full = [&](int b) { return bar0 + 8u * (1 + 4 * kStages + b); };
-    auto bar_s_free = [&](int b) { return bar0 + 8u * (3 + 4 * kStages + b); };
-    auto bar_p_full = [&](int b) { return bar0 + 8u * (5 + 4 * kStages + b); };
-    auto bar_o_done = [&](int b) { return bar0 + 8u * (7 + 4 * kStages + b); };
+    auto bar_q_full = [&](int b) { return bar0 + 8u * b; };
+    auto bar_q_empty = [&](int b) { return bar0 + 8u * (2 + b); };
+    auto bar_k_full = [&](int st) { return bar0 + 8u * (4 + st); };
+    auto bar_k_empty = [&](int st) { return bar0 + 8u * (4 + kStages + st); };
+    auto bar_v_full = [&](int st) { return bar0 + 8u * (4 + 2 * kStages + st); };
+    auto bar_v_empty = [&](int st) { return bar0 + 8u * (4 + 3 * kStages + st); };
+    auto bar_s_full = [&](int b) { return bar0 + 8u * (4 + 4 * kStages + b); };
+    auto bar_s_free = [&](int b) { return bar0 + 8u * (6 + 4 * kStages + b); };
+    auto bar_p_full = [&](int b) { return bar0 + 8u * (8 + 4 * kStages + b); };
+    auto bar_o_done = [&](int b) { return bar0 + 8u * (10 + 4 * kStages + b); };
+    const uint32_t bar_o_free = bar0 + 8u * (12 + 4 * kStages);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + SmemLayout::tmem_slot);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + SmemLayout::abort_flag);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    // ---- which tile: grid = (q tiles of 128 rows, H, B * splits) ----
-    const uint32_t row0 = blockIdx.x * kRows;
-    const uint32_t head = blockIdx.y;
-    uint32_t batch = blockIdx.z, split = 0;
-    if (kSplit) {
-        batch = blockIdx.z >> p.split_log2;
-        split = blockIdx.z & (p.splits - 1u);
-    }
-    const uint32_t kv_head = head >> p.gqa_shift;   // crates/amdgpu-stage/src/components.rs:8-17
-    const uint32_t ntiles_total = (p.SK + kKeys - 1) / kKeys;
-    uint32_t key_lo = 0, key_hi = p.SK;
-    if (kSplit) {   // tiles [split*tps, min(ntiles, (split+1)*tps)) (components.rs:58-74)
-        const uint32_t tps = (ntiles_total + p.splits - 1) / p.splits;
-        const uint32_t tile_lo = split * tps;
-        const uint32_t tile_hi = min(ntiles_total, tile_lo + tps);
-        key_lo = tile_lo * kKeys;
-        key_hi = min(tile_hi * kKeys, p.SK);
-    }
-    const int n_tiles = (key_hi > key_lo) ? static_cast<int>((key_hi - key_lo + kKeys - 1) / kKeys) : 0;
+    const uint32_t n_items = p.n_items, stride = gridDim.x;
     // the recipe is chosen from the whole sequence's tile count, also in a split (block3.rs:180-184)
+    const uint32_t ntiles_total = (p.SK + kKeys - 1) / kKeys;
     const bool lazy = (ntiles_total >= 4) && !(p.flags & 0x2u);
     const float thr = lazy ? kLazyThreshold : -kFollowWindow;
+    const bool cta_traced = kTrace && p.trace != nullptr && blockIdx.x == 0;   // diagnostics cover the first item of CTA 0 = logical block (0,0,0)
 
     // ---- one-time setup ----
     if (threadIdx.x == 0) {
         *abort_flag = 0u;
-        mbar_init(bar_q_full, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_q_full(b), 1);
+            mbar_init(bar_q_empty(b), 1);
+            mbar_init(bar_s_full(b), 1);
+            mbar_init(bar_s_free(b), 2 * kRows);
+            mbar_init(bar_p_full(b), 2 * kRows);
+            mbar_init(bar_o_done(b), 1);
+        }
         for (int st = 0; st < kStages; ++st) {
             mbar_init(bar_k_full(st), 1);
             mbar_init(bar_k_empty(st), 1);
             mbar_init(bar_v_full(st), 1);
             mbar_init(bar_v_empty(st), 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(bar_s_full(b), 1);
-            mbar_init(bar_s_free(b), 2 * kRows);
-            mbar_init(bar_p_full(b), 2 * kRows);
-            mbar_init(bar_o_done(b), 1);
-        }
+        mbar_init(bar_o_free, 4 * kRows);
         fence_mbar_init();
     }
     if (threadIdx.x < 512) {
@@ -244,158 +274,209 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
         tmem_relinquish();
     }
-    if (warp == kProducerWarp && lane == 0) {
+    if (warp == kKProducerWarp && lane == 0) {
         prefetch_tmap(&tm_q);
         prefetch_tmap(&tm_k);
-        prefetch_tmap(&tm_v);
     }
+    if (warp == kVProducerWarp && lane == 0) prefetch_tmap(&tm_v);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == kProducerWarp) {
-        // =========================================================== producer ===========================================================
-        {   // Q scale bytes -> [row % 32][row / 32][4] (the layout tcgen05.cp 32x128b.warpx4 spreads over the four lane quadrants)
-            uint32_t w[4];
+    // The four service roles are single chains of dependent instructions that share their scheduler with four arithmetic-dense softmax
+    // warps, so every instruction costs them several clocks: each role is its own warp, waits with blocking mbarrier waits (its
+    // conditions are conjunctions, never alternatives) and keeps its per-tile instruction count small.
+    if (warp == kKProducerWarp) {
+        // =========================================================== producer: Q and K tiles, Q and K scales ===========================================================
+        // K scales run four tiles ahead of the K tiles in four register sets, each use naming its set statically, so that a tile
+        // never waits for loads issued for the tiles behind it. The scale cursor therefore walks the items on its own.
+        const uint32_t row_step = 32u * p.HK * 4u, tile_step = 4u * row_step;   // bytes between a lane's four keys / between key tiles
+        struct ScaleCursor {
+            const uint8_t* ptr;   // scale word of this lane's first key of the tile
+            int keys_left;        // sequence keys from the tile's first key on (lanes compare against it)
+            int tiles_left;       // of the item
+            uint32_t w;           // the item
+            bool live;
+        };
+        auto enter_item = [&](ScaleCursor& c) {
+            c.live = c.w < n_items;
+            if (!c.live) return;
+            const Item it = decode_item<kSplit>(c.w, p);
+            c.ptr = p.k_descale + static_cast<size_t>(it.batch) * p.ks_batch_stride + (static_cast<size_t>(it.key_lo + lane) * p.HK + it.kv_head) * 4u;
+            c.keys_left = static_cast<int>(p.SK - it.key_lo) - lane;
+            c.tiles_left = it.n_tiles;
+        };
+        auto load_and_advance = [&](ScaleCursor& c, uint32_t (&w)[4]) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                uint32_t r = row0 + lane + 32 * i;
-                r = min(r, p.S - 1u);   // rows past the sequence reuse the last row's scales (block3.rs:110-113)
-                const size_t off = static_cast<size_t>(batch) * p.qs_batch_stride + (static_cast<size_t>(r) * p.H + head) * 4u;
-                w[i] = *reinterpret_cast<const uint32_t*>(p.q_descale + off);
+                w[i] = 0x7F7F7F7Fu;   // keys past the sequence: data is zero-filled by TMA, any finite scale does
+                if (c.live && 32 * i < c.keys_left) w[i] = __ldg(reinterpret_cast<const uint32_t*>(c.ptr + i * row_step));
             }
-            *reinterpret_cast<uint4*>(smem_gen + SmemLayout::sfq + lane * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+            if (!c.live) return;
+            c.ptr += tile_step;
+            c.keys_left -= kKeys;
+            if (--c.tiles_left == 0) {
+                c.w += stride;
+                enter_item(c);
+            }
+        };
+        // Q scale bytes -> [row % 32][row / 32][4] (the layout tcgen05.cp 32x128b.warpx4 spreads over the four lane quadrants)
+        auto load_q_scales = [&](const Item& it, uint32_t (&w)[4]) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t r = it.row0 + lane + 32 * i;
+                r = min(r, p.S - 1u);   // rows past the sequence reuse the last row's scales (block3.rs:110-113)
+                const size_t off = static_cast<size_t>(it.batch) * p.qs_batch_stride + (static_cast<size_t>(r) * p.H + it.head) * 4u;
+                w[i] = __ldg(reinterpret_cast<const uint32_t*>(p.q_descale + off));
+            }
+        };
+        ScaleCursor cs;
+        cs.w = blockIdx.x;
+        enter_item(cs);
+        uint32_t wq[4] = {0u, 0u, 0u, 0u}, w0[4], w1[4], w2[4], w3[4];
+        if (blockIdx.x < n_items) load_q_scales(decode_item<kSplit>(blockIdx.x, p), wq);
+        load_and_advance(cs, w0);
+        load_and_advance(cs, w1);
+        load_and_advance(cs, w2);
+        load_and_advance(cs, w3);
+
+        uint32_t gk = 0, n = 0, ph = 0, q_issued = 0;
+        int st = 0;
+        bool ok = true;
+        for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
+            const Item it = decode_item<kSplit>(w, p);
+            const uint32_t qb = n & 1u;
+            // the Q buffer was last used two items ago
+            if (n >= 2) ok = mbar_wait(bar_q_empty(qb), ((n >> 1) - 1u) & 1u, abort_flag);
+            if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+            *reinterpret_cast<uint4*>(smem_gen + SmemLayout::sfq + qb * kSfBytes + lane * 16) = make_uint4(wq[0], wq[1], wq[2], wq[3]);
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive_expect_tx(bar_q_full, kTileBytes);
-                tma_load_4d(q_smem, &tm_q, bar_q_full, 0, static_cast<int>(head), static_cast<int>(row0), static_cast<int>(batch));
+                mbar_arrive_expect_tx(bar_q_full(qb), kTileBytes);
+                tma_load_4d(q_smem + qb * kTileBytes, &tm_q, bar_q_full(qb), 0, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
             }
-        }
-        // K scale words are fetched two tiles ahead into registers, so their global-load latency never sits on the ring's critical path
-        auto load_k_scales = [&](int j, uint32_t (&w)[4]) {
-            const uint32_t key0 = key_lo + j * kKeys;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t key = key0 + lane + 32 * i;
-                w[i] = 0x7F7F7F7Fu;   // keys past the sequence: data is zero-filled by TMA, any finite scale does
-                if (j < n_tiles && key < p.SK) {
-                    const size_t off = static_cast<size_t>(batch) * p.ks_batch_stride + (static_cast<size_t>(key) * p.HK + kv_head) * 4u;
-                    w[i] = __ldg(reinterpret_cast<const uint32_t*>(p.k_descale + off));
+            ++q_issued;
+            if (w + stride < n_items) load_q_scales(decode_item<kSplit>(w + stride, p), wq);   // the next item's Q scales, a whole item ahead
+            float* k_trace = (cta_traced && n == 0) ? p.trace : nullptr;
+            int key = static_cast<int>(it.key_lo);
+            for (int j = 0; j < it.n_tiles; ++j, key += kKeys) {
+                // the stage is free once Q K^T of the tile that held it is done
+                if (gk >= static_cast<uint32_t>(kStages)) ok = mbar_wait(bar_k_empty(st), ph ^ 1u, abort_flag);
+                if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+                uint4* sf_dst = reinterpret_cast<uint4*>(smem_gen + SmemLayout::sfk + st * kSfBytes + lane * 16);
+                auto put_and_refill = [&](uint32_t (&set)[4]) {
+                    *sf_dst = make_uint4(set[0], set[1], set[2], set[3]);
+                    load_and_advance(cs, set);   // for the tile four ahead
+                };
+                switch (gk & 3u) {
+                    case 0: put_and_refill(w0); break;
+                    case 1: put_and_refill(w1); break;
+                    case 2: put_and_refill(w2); break;
+                    default: put_and_refill(w3); break;
                 }
-            }
-        };
-        uint32_t wa[4], wb[4];
-        load_k_scales(0, wa);
-        load_k_scales(1, wb);
-        // Event loop over the two rings: the next K tile (with its scales) goes out as soon as Q K^T of the tile that held its stage is
-        // done, the next V tile as soon as P V of the tile that held its stage is done; neither waits for the other.
-        int k_next = 0, v_next = 0;
-        bool ok = true;
-        long long t_idle = clock64();
-        while (ok && (k_next < n_tiles || v_next < n_tiles)) {
-            bool progressed = false;
-            if (k_next < n_tiles) {
-                const int j = k_next, st = j % kStages;
-                bool rdy = j < kStages || mbar_test_wait(bar_k_empty(st), ((j / kStages) - 1) & 1);
-                rdy = __shfl_sync(0xFFFFFFFFu, rdy ? 1 : 0, 0) != 0;
-                if (rdy) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) w[i] = (j & 1) ? wb[i] : wa[i];
-                    if (j & 1) load_k_scales(j + 2, wb); else load_k_scales(j + 2, wa);
-                    *reinterpret_cast<uint4*>(smem_gen + SmemLayout::sfk + st * kSfBytes + lane * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        stamp((blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr, 2, j, 6);
-                        mbar_arrive_expect_tx(bar_k_full(st), kTileBytes);
-                        tma_load_4d(k_smem + st * kTileBytes, &tm_k, bar_k_full(st), 0, static_cast<int>(kv_head), static_cast<int>(key_lo + j * kKeys), static_cast<int>(batch));
-                    }
-                    ++k_next;
-                    progressed = true;
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    stamp(k_trace, 2, j, 6);
+                    mbar_arrive_expect_tx(bar_k_full(st), kTileBytes);
+                    tma_load_4d(k_smem + st * kTileBytes, &tm_k, bar_k_full(st), 0, static_cast<int>(it.kv_head), key, static_cast<int>(it.batch));
                 }
-            }
-            if (v_next < n_tiles) {
-                const int j = v_next, st = j % kStages;
-                bool rdy = j < kStages || mbar_test_wait(bar_v_empty(st), ((j / kStages) - 1) & 1);
-                rdy = __shfl_sync(0xFFFFFFFFu, rdy ? 1 : 0, 0) != 0;
-                if (rdy) {
-                    if (lane == 0) {
-                        stamp((blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr, 3, j, 6);
-                        mbar_arrive_expect_tx(bar_v_full(st), kTileBytes);
-                        tma_load_4d(v_smem + st * kTileBytes, &tm_v, bar_v_full(st), 0, static_cast<int>(kv_head), static_cast<int>(key_lo + j * kKeys), static_cast<int>(batch));
-                    }
-                    ++v_next;
-                    progressed = true;
-                }
-            }
-            if (progressed) {
-                t_idle = clock64();
-            } else {
-
-                if (*abort_flag != 0u || clock64() - t_idle > kWaitBudgetCycles) {
-                    *abort_flag = 1u;
-                    ok = false;
-                }
+                ++gk;
+                if (++st == kStages) { st = 0; ph ^= 1u; }
             }
         }
         if (*abort_flag != 0u) {
             // leaving early: let the copies already in flight land before the CTA's shared memory is given back
-            for (int j = max(0, k_next - kStages); j < k_next; ++j) {
+            for (uint32_t g = gk > static_cast<uint32_t>(kStages) ? gk - kStages : 0u; g < gk; ++g) {
                 const long long t0 = clock64();
-                while (!mbar_test_wait(bar_k_full(j % kStages), (j / kStages) & 1) && clock64() - t0 < kWaitBudgetCycles) {}
+                while (!mbar_test_wait(bar_k_full(g % kStages), (g / kStages) & 1u) && clock64() - t0 < kWaitBudgetCycles) {}
             }
-            for (int j = max(0, v_next - kStages); j < v_next; ++j) {
+            for (uint32_t m = q_issued > 2u ? q_issued - 2u : 0u; m < q_issued; ++m) {
                 const long long t0 = clock64();
-                while (!mbar_test_wait(bar_v_full(j % kStages), (j / kStages) & 1) && clock64() - t0 < kWaitBudgetCycles) {}
+                while (!mbar_test_wait(bar_q_full(m & 1u), (m >> 1) & 1u) && clock64() - t0 < kWaitBudgetCycles) {}
             }
         }
+    } else if (warp == kVProducerWarp) {
+        // =========================================================== producer: V tiles ===========================================================
+        if (lane == 0) {
+            uint32_t gv = 0, n = 0, ph = 0;
+            int st = 0;
+            bool ok = true;
+            for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
+                const Item it = decode_item<kSplit>(w, p);
+                float* v_trace = (cta_traced && n == 0) ? p.trace : nullptr;
+                int key = static_cast<int>(it.key_lo);
+                for (int j = 0; ok && j < it.n_tiles; ++j, key += kKeys) {
+                    // the stage is free once P V of the tile that held it is done
+                    if (gv >= static_cast<uint32_t>(kStages)) ok = mbar_wait(bar_v_empty(st), ph ^ 1u, abort_flag);
+                    if (!ok) break;
+                    stamp(v_trace, 3, j, 6);
+                    mbar_arrive_expect_tx(bar_v_full(st), kTileBytes);
+                    tma_load_4d(v_smem + st * kTileBytes, &tm_v, bar_v_full(st), 0, static_cast<int>(it.kv_head), key, static_cast<int>(it.batch));
+                    ++gv;
+                    if (++st == kStages) { st = 0; ph ^= 1u; }
+                }
+            }
+            if (*abort_flag != 0u) {
+                for (uint32_t g = gv > static_cast<uint32_t>(kStages) ? gv - kStages : 0u; g < gv; ++g) {
+                    const long long t0 = clock64();
+                    while (!mbar_test_wait(bar_v_full(g % kStages), (g / kStages) & 1u) && clock64() - t0 < kWaitBudgetCycles) {}
+                }
+            }
+        }
+        __syncwarp();
     } else if (warp == kMmaWarp) {
         // =========================================================== MMA issuer: score tiles ===========================================================
         // One lane runs the role. A tcgen05.mma costs its issuing thread about as long as the tensor pipe needs for a 128 x 128 x 32
         // tile, so Q K^T and P V are issued by two different threads (this warp and kPvWarp): their streams share no operand, and the
-        // pipe interleaves them. Polls are non-blocking and descriptors are prepared once.
+        // pipe interleaves them. Descriptors are prepared once.
         if (lane == 0) {
             const uint32_t idesc_qk = idesc_mxf8_block_scaled(128, 128, 0, 0, 0, 0);
             const uint32_t t_sfq = tmem + kColSfQ;
-            float* mma_trace = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
             // K-major 128-byte-swizzled Q / K tiles: 8-row groups 1024 B apart, 32 head-dim bytes (two 16-byte units) per MMA
             const uint64_t dq0 = make_smem_desc(q_smem, 16, 1024, kSwizzle128B);
             const uint64_t dk0 = make_smem_desc(k_smem, 16, 1024, kSwizzle128B);
             const uint64_t dsf0 = make_smem_desc(sfk_smem, 0, 128, kSwizzleNone);
-
-            bool ok = mbar_wait(bar_q_full, 0, abort_flag);
-            tc_fence_after_sync();
-            if (ok) tmem_cp_sf(t_sfq, make_smem_desc(sfq_smem, 0, 128, kSwizzleNone));
-
-            long long t_idle = clock64();
-            for (int j = 0; ok && j < n_tiles;) {
-                // S[j&1] = Q K(j)^T: needs the K tile and its scales, and the softmax of tile j-2 to have read S[j&1] out
-                const int st = j % kStages;
-                if (mbar_test_wait(bar_k_full(st), (j / kStages) & 1) && (j < 2 || mbar_test_wait(bar_s_free(j & 1), ((j >> 1) - 1) & 1))) {
+            const uint64_t dsfq0 = make_smem_desc(sfq_smem, 0, 128, kSwizzleNone);
+            uint32_t g = 0, n = 0, ph = 0;
+            int st = 0;
+            bool ok = true;
+            for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
+                const int n_tiles = decode_item<kSplit>(w, p).n_tiles;
+                const uint32_t qb = n & 1u;
+                float* mma_trace = (cta_traced && n == 0) ? p.trace : nullptr;
+                ok = mbar_wait(bar_q_full(qb), (n >> 1) & 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after_sync();
+                // issued behind the previous item's MMAs by the same thread, so it cannot overtake their reads of these columns
+                tmem_cp_sf(t_sfq, dsfq0 + static_cast<uint64_t>((qb * kSfBytes) >> 4));
+                const uint64_t dq = dq0 + static_cast<uint64_t>((qb * kTileBytes) >> 4);
+                for (int j = 0; j < n_tiles; ++j) {
+                    // S[g&1] = Q K(j)^T: needs the K tile and its scales, and the softmax of tile g-2 to have read S[g&1] out
+                    ok = mbar_wait(bar_k_full(st), ph, abort_flag);
+                    if (ok && g >= 2) ok = mbar_wait(bar_s_free(g & 1u), ((g >> 1) - 1u) & 1u, abort_flag);
+                    if (!ok) break;
                     tc_fence_after_sync();
                     stamp(mma_trace, 2, j, 2);
-                    const uint32_t t_sfk = tmem + ((j & 1) ? kColSfK1 : kColSfK0);
-                    const uint32_t t_s = tmem + ((j & 1) ? kColS1 : kColS0);
+                    const uint32_t t_sfk = tmem + ((g & 1u) ? kColSfK1 : kColSfK0);
+                    const uint32_t t_s = tmem + ((g & 1u) ? kColS1 : kColS0);
                     tmem_cp_sf(t_sfk, dsf0 + static_cast<uint64_t>((st * kSfBytes) >> 4));
                     const uint64_t dk = dk0 + static_cast<uint64_t>((st * kTileBytes) >> 4);
 #pragma unroll
                     for (int kb = 0; kb < 4; ++kb) {
                         const uint32_t id = idesc_qk | (static_cast<uint32_t>(kb) << 29) | (static_cast<uint32_t>(kb) << 4);
-                        mma_mxf8_ss(t_s, dq0 + 2u * kb, dk + 2u * kb, id, t_sfq + (static_cast<uint32_t>(kb) << 30),
+                        mma_mxf8_ss(t_s, dq + 2u * kb, dk + 2u * kb, id, t_sfq + (static_cast<uint32_t>(kb) << 30),
                                     t_sfk + (static_cast<uint32_t>(kb) << 30), kb > 0 ? 1u : 0u);
                     }
                     stamp(mma_trace, 2, j, 4);
-                    tc_commit(bar_s_full(j & 1));
+                    tc_commit(bar_s_full(g & 1u));
                     tc_commit(bar_k_empty(st));
+                    if (j == n_tiles - 1) tc_commit(bar_q_empty(qb));   // the Q buffer can take the item after next
                     stamp(mma_trace, 2, j, 5);
-                    ++j;
-                    t_idle = clock64();
-                } else if (*abort_flag != 0u || clock64() - t_idle > kWaitBudgetCycles) {
-                    *abort_flag = 1u;
-                    ok = false;
+                    ++g;
+                    if (++st == kStages) { st = 0; ph ^= 1u; }
                 }
             }
         }
@@ -405,16 +486,22 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         if (lane == 0) {
             // P V with N = 144: head dims 0..127 from the V tile, 16 more columns from the tile of ones (O | L are adjacent in TMEM)
             const uint32_t idesc_pv = idesc_f8_dense(128, 144, 0, 1);
-            float* mma_trace = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
+            uint32_t g = 0, n = 0, ph = 0;
+            int st = 0;
             bool ok = true;
-            long long t_idle = clock64();
-            for (int i = 0; ok && i < n_tiles;) {
-                // O (+)= P(i) V(i) with the row sums riding along: P from TMEM (32 columns, 8 per 32 keys), V tile = 128 keys x 128 B, MN-major
-                const int st = i % kStages;
-                if (mbar_test_wait(bar_p_full(i & 1), (i >> 1) & 1) && mbar_test_wait(bar_v_full(st), (i / kStages) & 1)) {
+            for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
+                const int n_tiles = decode_item<kSplit>(w, p).n_tiles;
+                float* mma_trace = (cta_traced && n == 0) ? p.trace : nullptr;
+                // an item's first tile overwrites O and L, which the epilogue of the item before must have read out
+                if (n > 0) ok = mbar_wait(bar_o_free, (n - 1u) & 1u, abort_flag);
+                for (int i = 0; ok && i < n_tiles; ++i) {
+                    // O (+)= P(i) V(i) with the row sums riding along: P from TMEM (32 columns, 8 per 32 keys), V tile = 128 keys x 128 B, MN-major
+                    ok = mbar_wait(bar_v_full(st), ph, abort_flag);
+                    if (ok) ok = mbar_wait(bar_p_full(g & 1u), (g >> 1) & 1u, abort_flag);
+                    if (!ok) break;
                     tc_fence_after_sync();
                     stamp(mma_trace, 3, i, 2);
-                    const uint32_t t_p = tmem + ((i & 1) ? kColP1 : kColP0);
+                    const uint32_t t_p = tmem + ((g & 1u) ? kColP1 : kColP0);
 #pragma unroll
                     for (int kb = 0; kb < 4; ++kb) {
                         // MN-major B: 8-key groups 1024 B apart; the second 128-byte-wide atom (columns 128..) is the tile of ones
@@ -424,20 +511,17 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     }
                     stamp(mma_trace, 3, i, 3);
                     tc_commit(bar_v_empty(st));
-                    tc_commit(bar_o_done(i & 1));
+                    tc_commit(bar_o_done(g & 1u));
                     stamp(mma_trace, 3, i, 4);
-                    ++i;
-                    t_idle = clock64();
-                } else if (*abort_flag != 0u || clock64() - t_idle > kWaitBudgetCycles) {
-                    *abort_flag = 1u;
-                    ok = false;
+                    ++g;
+                    if (++st == kStages) { st = 0; ph ^= 1u; }
                 }
             }
         }
         __syncwarp();
     } else if (warp >= kFirstSoftmaxWarp) {
         // =========================================================== softmax + epilogue ===========================================================
-        // Four warpgroups: wg = 2 * half + parity. Parity = which key tiles (j = parity mod 2) and which S / P buffer; half = which 64 key
+        // Four warpgroups: wg = 2 * half + parity. Parity = which tiles (counter g = parity mod 2) and which S / P buffer; half = which 64 key
         // columns of the tile (and, in the epilogue, which 32 head dims together with the parity). Thread r of a group owns query row r.
         const uint32_t st_id = threadIdx.x - 32u * kFirstSoftmaxWarp;
         const uint32_t wg = st_id >> 7;
@@ -450,212 +534,230 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const uint32_t t_p = tmem + (par ? kColP1 : kColP0) + lane_base + 16u * half;
         const uint32_t t_o_half = tmem + kColO + lane_base + 64u * half;
         const uint32_t t_l = tmem + kColL + lane_base;
-        float ref = -INFINITY;   // the row's reference (log2 units) after the last tile this thread has seen
         bool ok = true;
-        const bool tracing = kTrace && (p.trace != nullptr) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-        const bool dumping = tracing && !(p.flags & 0x4u);   // flag 0x4: time stamps only, no tile dumps
 
-        // bounded poll of an 8-byte {value, tile index} slot
-        auto wait_slot = [&](uint32_t slot, int j, float& out) -> bool {
+        // bounded poll of an 8-byte {value, tile counter} slot
+        auto wait_slot = [&](uint32_t slot, uint32_t g, float& out) -> bool {
             uint2 o = ld_shared_v2(slot);
-            if (o.y != static_cast<uint32_t>(j)) {
+            if (o.y != g) {
                 const long long t0 = clock64();
                 while (true) {
                     o = ld_shared_v2(slot);
-                    if (o.y == static_cast<uint32_t>(j)) break;
+                    if (o.y == g) break;
                     if (*abort_flag != 0u || clock64() - t0 > kWaitBudgetCycles) { *abort_flag = 1u; return false; }
                 }
             }
             out = __uint_as_float(o.x);
             return true;
         };
-        // the reference the row has after tile j: published by both half-row threads that handled tile j, read from the same half
-        auto ref_slot = [&](int j) { return xref + 8u * ((static_cast<uint32_t>(j & 1) * 2u + half) * 128u + r); };
-        // the half-row maximum of tile j: double buffered over this parity's consecutive tiles
-        auto max_slot = [&](int j, uint32_t h) { return xmax + 8u * (((static_cast<uint32_t>((j >> 1) & 1) * 2u + par) * 2u + h) * 128u + r); };
+        // the reference the row has after tile g: published by both half-row threads that handled tile g, read from the same half
+        auto ref_slot = [&](uint32_t g) { return xref + 8u * (((g & 1u) * 2u + half) * 128u + r); };
+        // the half-row maximum of tile g: double buffered over this parity's consecutive tiles
+        auto max_slot = [&](uint32_t g, uint32_t h) { return xmax + 8u * (((((g >> 1) & 1u) * 2u + par) * 2u + h) * 128u + r); };
 
-        for (int j = static_cast<int>(par); j < n_tiles; j += 2) {
-            const int k = j >> 1;   // this parity's tile counter
-            float* st_trace = (tracing && r == 0 && half == 0) ? p.trace : nullptr;
-            stamp(st_trace, par, j, 0);
-            if (!mbar_wait(bar_s_full(par), k & 1, abort_flag)) { ok = false; break; }
-            tc_fence_after_sync();
-            stamp(st_trace, par, j, 1);
-            // Pass 1 over the 64 scores of this half row, 32 at a time: the maximum only. The scores are read again for the conversion
-            // below instead of being kept, which keeps a softmax thread under 96 registers (18 warps share the register file).
-            const int nvalid = static_cast<int>(min(static_cast<uint32_t>(kKeys), key_hi - (key_lo + j * kKeys))) - 64 * static_cast<int>(half);
-            float mt;
+        uint32_t g0 = 0, n = 0;   // tile counter at the item's first tile; ordinal of the item
+        for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
+            // only the tile count and the last tile's valid keys stay live through the tile loop; the item is decoded again for the epilogue
+            int n_tiles, tail_valid;
             {
-                float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+                const Item it = decode_item<kSplit>(w, p);
+                n_tiles = it.n_tiles;
+                tail_valid = static_cast<int>(it.key_hi - it.key_lo) - (n_tiles - 1) * kKeys - 64 * static_cast<int>(half);
+            }
+            const bool tracing = cta_traced && n == 0;
+            const bool dumping = tracing && !(p.flags & 0x4u);   // flag 0x4: time stamps only, no tile dumps
+            float ref = -INFINITY;   // the row's reference (log2 units) after the last tile this thread has seen
+
+            for (int j = static_cast<int>((g0 ^ par) & 1u); j < n_tiles; j += 2) {
+                const uint32_t g = g0 + static_cast<uint32_t>(j);
+                const uint32_t k = g >> 1;   // this parity's tile counter
+                float* st_trace = (tracing && r == 0 && half == 0) ? p.trace : nullptr;
+                stamp(st_trace, par, j, 0);
+                if (!mbar_wait(bar_s_full(par), k & 1u, abort_flag)) ok = false;   // no divergent exit: the votes below keep the warp together
+                tc_fence_after_sync();
+                stamp(st_trace, par, j, 1);
+                // Pass 1 over the 64 scores of this half row, 32 at a time: the maximum only. The scores are read again for the conversion
+                // below instead of being kept, which keeps a softmax thread under 96 registers (20 warps share the register file).
+                const int nvalid = (j == n_tiles - 1) ? tail_valid : 64;   // valid keys of this half row's 64
+                float mt;
+                {
+                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll 1
+                    for (int ch = 0; ch < 2; ++ch) {
+                        uint32_t s[32];
+                        tmem_ld32(t_s + 32 * ch, s);
+                        tmem_wait_ld();
+                        if (nvalid < 64) {   // keys past the range: -inf for the maximum, 0 for P (crates/amdgpu-tile/src/reduce.rs:35-49)
+#pragma unroll
+                            for (int c = 0; c < 32; ++c) {
+                                if (c + 32 * ch >= nvalid) s[c] = 0xFF800000u;
+                            }
+                        }
+                        if (dumping && j == 0) {
+#pragma unroll
+                            for (int c = 0; c < 32; ++c) p.trace[r * 128 + 64 * half + 32 * ch + c] = __uint_as_float(s[c]);
+                        }
+#pragma unroll
+                        for (int c = 0; c < 32; c += 8) {   // four independent chains of three-input maxima
+                            m0 = max3(m0, __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
+                            m1 = max3(m1, __uint_as_float(s[c + 2]), __uint_as_float(s[c + 3]));
+                            m2 = max3(m2, __uint_as_float(s[c + 4]), __uint_as_float(s[c + 5]));
+                            m3 = max3(m3, __uint_as_float(s[c + 6]), __uint_as_float(s[c + 7]));
+                        }
+                    }
+                    mt = fmaxf(max3(m0, m1, m2), m3);
+                }
+                stamp(st_trace, par, j, 2);
+                // exchange the half-row maxima with the thread that holds the other 64 keys of this row
+                st_shared_v2(max_slot(g, half), __float_as_uint(mt), g);
+                stamp(st_trace, par, j, 3);
+                {
+                    float other = mt;
+                    if (!wait_slot(max_slot(g, half ^ 1u), g, other)) ok = false;
+                    mt = fmaxf(mt, other);
+                }
+                // take over the row's reference from the threads that handled the item's previous tile
+                if (ok && j > 0 && !wait_slot(ref_slot(g - 1u), g - 1u, ref)) ok = false;
+                if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+                // the reference moves when this tile's maximum passes it by more than the threshold (negative for short sequences: it then
+                // also follows the tile maximum down, and f > 1 scales O and L up). Both halves of a row see the same mt and ref.
+                const bool move = mt > ref + thr;
+                float f = 1.0f;
+                if (move) {
+                    const float nref = lazy ? ceilf(mt) : mt;
+                    f = ex2_approx(ref - nref);   // 0 on the first tile (ref = -inf); an exact power of two for integer references
+                    ref = nref;
+                }
+                st_shared_v2(ref_slot(g), __float_as_uint(ref), g);
+                stamp(st_trace, par, j, 4);
+                // P V of this parity's previous tile must be done before its P columns are overwritten (and, observed in order, this keeps
+                // the phase parity of the other parity's barrier below unambiguous)
+                if (k > 0 && !mbar_wait(bar_o_done(par), (k - 1u) & 1u, abort_flag)) ok = false;
+                stamp(st_trace, par, j, 5);
+                if (j > 0 && __any_sync(0xFFFFFFFFu, move)) {
+                    // O holds P V of all the item's tiles before j once the other parity's last P V is done; P V of tile j cannot start before this thread's arrive below
+                    if (!mbar_wait(bar_o_done(par ^ 1u), ((g - 1u) >> 1) & 1u, abort_flag)) ok = false;
+                    tc_fence_after_sync();
+                    scale_tmem32(t_o_half, f);
+                    scale_tmem32(t_o_half + 32, f);
+                    if (half == 0) {   // the row sum lives in column 0 of L
+                        uint32_t lv;
+                        asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(lv) : "r"(t_l) : "memory");
+                        tmem_wait_ld();
+                        lv = __float_as_uint(__uint_as_float(lv) * f);
+                        asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(t_l), "r"(lv) : "memory");
+                    }
+                    tmem_wait_st();
+                }
+                // Pass 2: P = e4m3(2^(s - ref + offset)), four keys per 32-bit TMEM column
+                const float sh = kPOffset - ref;
+                const float cf = (kPOffset + 7.0f - kFastBias - ref) * 0.03125f;
+                uint32_t pw[16];
+#pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
                     uint32_t s[32];
                     tmem_ld32(t_s + 32 * ch, s);
                     tmem_wait_ld();
-                    if (nvalid < 64) {   // keys past the range: -inf for the maximum, 0 for P (crates/amdgpu-tile/src/reduce.rs:35-49)
+                    if (ch == 1) {
+                        tc_fence_before_sync();
+                        mbar_arrive(bar_s_free(par));   // the score buffer can take tile g + 2 once all 256 threads of this parity are done with it
+                    }
+                    if (nvalid < 64) {
 #pragma unroll
                         for (int c = 0; c < 32; ++c) {
                             if (c + 32 * ch >= nvalid) s[c] = 0xFF800000u;
                         }
                     }
-                    if (dumping && j == 0) {
+                    if (lazy) {
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) p.trace[r * 128 + 64 * half + 32 * ch + c] = __uint_as_float(s[c]);
-                    }
+                        for (int c = 0; c < 8; ++c) pw[8 * ch + c] = p_word_hybrid(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], sh, cf);
+                    } else {
 #pragma unroll
-                    for (int c = 0; c < 32; c += 8) {   // four independent chains of three-input maxima
-                        m0 = max3(m0, __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
-                        m1 = max3(m1, __uint_as_float(s[c + 2]), __uint_as_float(s[c + 3]));
-                        m2 = max3(m2, __uint_as_float(s[c + 4]), __uint_as_float(s[c + 5]));
-                        m3 = max3(m3, __uint_as_float(s[c + 6]), __uint_as_float(s[c + 7]));
+                        for (int c = 0; c < 8; ++c) pw[8 * ch + c] = p_word(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], sh);
                     }
                 }
-                mt = fmaxf(max3(m0, m1, m2), m3);
-            }
-            stamp(st_trace, par, j, 2);
-            // exchange the half-row maxima with the thread that holds the other 64 keys of this row
-            st_shared_v2(max_slot(j, half), __float_as_uint(mt), static_cast<uint32_t>(j));
-            stamp(st_trace, par, j, 3);
-            {
-                float other = mt;
-                if (!wait_slot(max_slot(j, half ^ 1u), j, other)) ok = false;
-                mt = fmaxf(mt, other);
-            }
-            // take over the row's reference from the threads that handled tile j - 1
-            if (ok && j > 0 && !wait_slot(ref_slot(j - 1), j - 1, ref)) ok = false;
-            if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
-            // the reference moves when this tile's maximum passes it by more than the threshold (negative for short sequences: it then
-            // also follows the tile maximum down, and f > 1 scales O and L up). Both halves of a row see the same mt and ref.
-            const bool move = mt > ref + thr;
-            float f = 1.0f;
-            if (move) {
-                const float nref = lazy ? ceilf(mt) : mt;
-                f = ex2_approx(ref - nref);   // 0 on the first tile (ref = -inf); an exact power of two for integer references
-                ref = nref;
-            }
-            st_shared_v2(ref_slot(j), __float_as_uint(ref), static_cast<uint32_t>(j));
-            stamp(st_trace, par, j, 4);
-            // P V of this parity's previous tile must be done before its P columns are overwritten (and, observed in order, this keeps
-            // the phase parity of the other parity's barrier below unambiguous)
-            if (k > 0 && !mbar_wait(bar_o_done(par), (k - 1) & 1, abort_flag)) { ok = false; break; }
-            stamp(st_trace, par, j, 5);
-            if (j > 0 && __any_sync(0xFFFFFFFFu, move)) {
-                // O holds P V of all tiles before j once the other parity's last P V is done; P V of tile j cannot start before this thread's arrive below
-                if (!mbar_wait(bar_o_done(par ^ 1u), ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
-                tc_fence_after_sync();
-                scale_tmem32(t_o_half, f);
-                scale_tmem32(t_o_half + 32, f);
-                if (half == 0) {   // the row sum lives in column 0 of L
-                    uint32_t lv;
-                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(lv) : "r"(t_l) : "memory");
-                    tmem_wait_ld();
-                    lv = __float_as_uint(__uint_as_float(lv) * f);
-                    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(t_l), "r"(lv) : "memory");
+                if (dumping && j == 0) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) reinterpret_cast<uint32_t*>(p.trace)[32768 + 256 + r * 32 + 16 * half + c] = pw[c];
                 }
+                stamp(st_trace, par, j, 6);
+                tmem_st16(t_p, pw);
                 tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(bar_p_full(par));
+                stamp(st_trace, par, j, 7);
             }
-            // Pass 2: P = e4m3(2^(s - ref + offset)), four keys per 32-bit TMEM column
-            const float sh = kPOffset - ref;
-            const float cf = (kPOffset + 7.0f - kFastBias - ref) * 0.03125f;
-            uint32_t pw[16];
-#pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
-                uint32_t s[32];
-                tmem_ld32(t_s + 32 * ch, s);
-                tmem_wait_ld();
-                if (ch == 1) {
-                    tc_fence_before_sync();
-                    mbar_arrive(bar_s_free(par));   // the score buffer can take tile j + 2 once all 256 threads of this parity are done with it
-                }
-                if (nvalid < 64) {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        if (c + 32 * ch >= nvalid) s[c] = 0xFF800000u;
-                    }
-                }
-                if (lazy) {
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) pw[8 * ch + c] = p_word_hybrid(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], sh, cf);
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) pw[8 * ch + c] = p_word(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], sh);
-                }
-            }
-            if (dumping && j == 0) {
-#pragma unroll
-                for (int c = 0; c < 16; ++c) reinterpret_cast<uint32_t*>(p.trace)[32768 + 256 + r * 32 + 16 * half + c] = pw[c];
-            }
-            stamp(st_trace, par, j, 6);
-            tmem_st16(t_p, pw);
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(bar_p_full(par));
-            stamp(st_trace, par, j, 7);
-        }
+            if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
 
-        // ---- epilogue: O * v_descale / l; warpgroup wg stores head dims [32 wg, 32 wg + 32) ----
-        if (ok && n_tiles > 0) {
-            const int last = n_tiles - 1;
-            const int mine = ((last & 1) == static_cast<int>(par)) ? last : last - 1;   // this parity's last tile (-1: none)
-            if (mine >= 0) ok = mbar_wait(bar_o_done(par), (mine >> 1) & 1, abort_flag);
-            const int theirs = ((last & 1) == static_cast<int>(par)) ? last - 1 : last;
-            if (ok && theirs >= 0) ok = mbar_wait(bar_o_done(par ^ 1u), (theirs >> 1) & 1, abort_flag);
-            if (ok) ok = wait_slot(ref_slot(last), last, ref);
-        }
-        tc_fence_after_sync();
-        if (ok && n_tiles > 0) {
-            uint32_t lv;
-            asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(lv) : "r"(t_l) : "memory");
-            tmem_wait_ld();
-            const float l = __uint_as_float(lv);
-            const float vd = *p.v_descale;
-            const float fin = vd / l;   // crates/amdgpu-stage/src/attention/state.rs:79-82
-            const uint32_t row = row0 + r;
-            const bool row_ok = row < p.S;   // rows past the sequence are computed on clamped scales and not stored (block3.rs:194)
-            if (tracing && wg == 0) {
-                p.trace[32768 + r] = l;
-                p.trace[32768 + 128 + r] = ref;
-            }
-            uint32_t o[32];
-            tmem_ld32(tmem + kColO + lane_base + 32u * wg, o);
-            tmem_wait_ld();
-            if (dumping) {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) p.trace[16384 + r * 128 + 32 * wg + c] = __uint_as_float(o[c]);
-            }
-            if (row_ok) {
-                if (kSplit) {
-                    const size_t prow = static_cast<size_t>(split) * p.rows_total + (static_cast<size_t>(batch) * p.S + row) * p.H + head;
-                    float4* dst = reinterpret_cast<float4*>(p.ohat + prow * 128 + 32 * wg);
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        dst[c] = make_float4(__uint_as_float(o[4 * c]) * fin, __uint_as_float(o[4 * c + 1]) * fin,
-                                             __uint_as_float(o[4 * c + 2]) * fin, __uint_as_float(o[4 * c + 3]) * fin);
-                    }
-                } else {
-                    uint8_t* orow = p.o + static_cast<size_t>(batch) * p.o_batch_stride + static_cast<size_t>(row) * p.o_row_stride + head * 256u;
-                    uint4* dst = reinterpret_cast<uint4*>(orow + 64 * wg);
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t wv[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[8 * c + 2 * e]) * fin, __uint_as_float(o[8 * c + 2 * e + 1]) * fin);
-                            wv[e] = *reinterpret_cast<const uint32_t*>(&b2);
-                        }
-                        dst[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-                    }
+            // ---- epilogue: O * v_descale / l; warpgroup wg stores head dims [32 wg, 32 wg + 32) ----
+            {
+                const uint32_t g_last = g0 + static_cast<uint32_t>(n_tiles) - 1u;
+                // this parity's last tile of the item first (its barrier is observed phase by phase), then the other parity's
+                const uint32_t g_mine = ((g_last & 1u) == par) ? g_last : g_last - 1u;
+                const uint32_t g_theirs = ((g_last & 1u) == par) ? g_last - 1u : g_last;
+                if (n_tiles > (((g_last & 1u) == par) ? 0 : 1)) ok = mbar_wait(bar_o_done(par), (g_mine >> 1) & 1u, abort_flag);
+                if (ok && n_tiles > (((g_last & 1u) == par) ? 1 : 0)) ok = mbar_wait(bar_o_done(par ^ 1u), (g_theirs >> 1) & 1u, abort_flag);
+                if (ok) ok = wait_slot(ref_slot(g_last), g_last, ref);
+                if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+                tc_fence_after_sync();
+                uint32_t lv;
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(lv) : "r"(t_l) : "memory");
+                uint32_t o[32];
+                tmem_ld32(tmem + kColO + lane_base + 32u * wg, o);
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                mbar_arrive(bar_o_free);   // O and L are in registers: the next item's first P V may overwrite them
+                uint32_t w_again;          // opaque copy: keeps the compiler from holding the decoded item in registers across the tile loop
+                asm volatile("mov.u32 %0, %1;" : "=r"(w_again) : "r"(w));
+                const Item it = decode_item<kSplit>(w_again, p);
+                const float l = __uint_as_float(lv);
+                const float vd = *p.v_descale;
+                const float fin = vd / l;   // crates/amdgpu-stage/src/attention/state.rs:79-82
+                const uint32_t row = it.row0 + r;
+                const bool row_ok = row < p.S;   // rows past the sequence are computed on clamped scales and not stored (block3.rs:194)
+                if (tracing && wg == 0) {
+                    p.trace[32768 + r] = l;
+                    p.trace[32768 + 128 + r] = ref;
                 }
-                if (wg == 0) {
-                    const float lse2 = ref - kPOffset + lg2_approx(l);   // log2 of sum_j 2^(s_j)
+                if (dumping) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) p.trace[16384 + r * 128 + 32 * wg + c] = __uint_as_float(o[c]);
+                }
+                if (row_ok) {
                     if (kSplit) {
-                        const size_t prow = static_cast<size_t>(split) * p.rows_total + (static_cast<size_t>(batch) * p.S + row) * p.H + head;
-                        p.lse2[prow] = lse2;
-                    } else if (p.lse_nat != nullptr) {
-                        p.lse_nat[(static_cast<size_t>(batch) * p.H + head) * p.S + row] = lse2 * 0.6931471805599453f;
+                        const size_t prow = static_cast<size_t>(it.split) * p.rows_total + (static_cast<size_t>(it.batch) * p.S + row) * p.H + it.head;
+                        float4* dst = reinterpret_cast<float4*>(p.ohat + prow * 128 + 32 * wg);
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            dst[c] = make_float4(__uint_as_float(o[4 * c]) * fin, __uint_as_float(o[4 * c + 1]) * fin,
+                                                 __uint_as_float(o[4 * c + 2]) * fin, __uint_as_float(o[4 * c + 3]) * fin);
+                        }
+                    } else {
+                        uint8_t* orow = p.o + static_cast<size_t>(it.batch) * p.o_batch_stride + static_cast<size_t>(row) * p.o_row_stride + it.head * 256u;
+                        uint4* dst = reinterpret_cast<uint4*>(orow + 64 * wg);
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t wv[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[8 * c + 2 * e]) * fin, __uint_as_float(o[8 * c + 2 * e + 1]) * fin);
+                                wv[e] = *reinterpret_cast<const uint32_t*>(&b2);
+                            }
+                            dst[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                        }
+                    }
+                    if (wg == 0) {
+                        const float lse2 = ref - kPOffset + lg2_approx(l);   // log2 of sum_j 2^(s_j)
+                        if (kSplit) {
+                            const size_t prow = static_cast<size_t>(it.split) * p.rows_total + (static_cast<size_t>(it.batch) * p.S + row) * p.H + it.head;
+                            p.lse2[prow] = lse2;
+                        } else if (p.lse_nat != nullptr) {
+                            p.lse_nat[(static_cast<size_t>(it.batch) * p.H + it.head) * p.S + row] = lse2 * 0.6931471805599453f;
+                        }
                     }
                 }
             }
+            g0 += static_cast<uint32_t>(n_tiles);
         }
     }
 
@@ -675,15 +777,34 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
     using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
     static const Kernel kernels[4] = {fmha_fwd_mxfp8_kernel<false, false>, fmha_fwd_mxfp8_kernel<true, false>,
                                       fmha_fwd_mxfp8_kernel<false, true>, fmha_fwd_mxfp8_kernel<true, true>};
-    static bool attr_done[4] = {false, false, false, false};
+    constexpr int kMaxDevices = 64;
+    static bool attr_done[kMaxDevices][4] = {};   // the shared-memory attribute is per device
+    static int sm_count[kMaxDevices] = {};
     const int which = (split ? 1 : 0) + (p.trace != nullptr ? 2 : 0);
-    if (!attr_done[which]) {
-        const cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernels[which]), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (!attr_done[dev][which]) {
+        e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernels[which]), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
-        attr_done[which] = true;
+        attr_done[dev][which] = true;
     }
-    dim3 grid((p.S + kRows - 1) / kRows, p.H, B * (split ? p.splits : 1u));
-    kernels[which]<<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
+    if (sm_count[dev] == 0) {
+        int n = 0;
+        e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+        sm_count[dev] = n > 0 ? n : 1;
+    }
+    // Persistent launch: one CTA per SM (a CTA takes all of an SM's tensor memory and nearly all of its shared memory), each walking the
+    // work items blockIdx.x, blockIdx.x + gridDim.x, ...
+    AttnParams q = p;
+    q.n_qtiles = (p.S + kRows - 1) / kRows;
+    const unsigned long long items = 1ull * q.n_qtiles * p.H * B * (split ? p.splits : 1u);
+    if (items == 0 || items > 0xFFFFFFFFull) return cudaErrorInvalidValue;
+    q.n_items = static_cast<uint32_t>(items);
+    const uint32_t ctas = q.n_items < static_cast<uint32_t>(sm_count[dev]) ? q.n_items : static_cast<uint32_t>(sm_count[dev]);
+    kernels[which]<<<dim3(ctas, 1, 1), kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, q);
     return cudaGetLastError();
 }
 

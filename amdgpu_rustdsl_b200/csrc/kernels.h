@@ -24,6 +24,7 @@ struct AttnParams {
     uint32_t qs_batch_stride, ks_batch_stride;  // bytes
     uint32_t splits, split_log2, rows_total;
     uint32_t flags;
+    uint32_t n_qtiles, n_items;   // work decomposition of the persistent kernel, filled in by launch_attention
     // diagnostics
     float* trace;          // may be null
     uint32_t* status;      // device status word
