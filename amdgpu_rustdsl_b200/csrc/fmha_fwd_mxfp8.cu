@@ -11,7 +11,7 @@
 //   out    : O * v_descale / l as bf16 (state.rs:79-82), or for the split kernel the normalised f32 partial plus a base-2
 //            log-sum-exp per row (block3.rs:291-356).
 //
-// Mapping onto the SM (not a translation of the gfx950 wave layout): a persistent kernel, one CTA of 20 warps per SM, each CTA walking
+// Mapping onto the SM (not a translation of the gfx950 wave layout): a persistent kernel, one CTA of 12 warps per SM, each CTA walking
 // work items (128 query rows of one (batch, head[, split])) with its rings, buffers and barriers running on across items.
 //   warp  0    Q K^T issuer: one lane issues S[g % 2] = Q K_g^T as kind::mxf8f6f4.block_scale tcgen05.mma, both operands in swizzled
 //              shared memory, the E8M0 factors copied to TMEM with tcgen05.cp. Two score tiles are always ahead of the softmax.
@@ -22,12 +22,13 @@
 //              row sums of the *quantised* P at no ALU cost (the reference sums P with a matrix instruction too, reduce.rs:163-173).
 //              A second issuing thread matters: one thread issues an MMA about every 75 clocks whatever its N.
 //   warp  3    V producer: TMA loads of the V ring (K is freed after Q K^T, V after P V, so the two rings run apart).
-//   warps 4-19 softmax + epilogue, four warpgroups: warpgroup 2 * half + parity works on tiles g = parity (mod 2) and on keys
-//              [64 half, 64 half + 64) of them. Thread r of a group owns query row r = TMEM lane r. Per tile it reads its 64 scores
-//              twice with tcgen05.ld (maximum, then conversion: holding them would need more than the 96 registers that 20 warps
-//              leave a thread), exchanges the half-row maximum with the sibling half and the row reference with the group of the
-//              previous tile through 8-byte shared-memory slots {value, tile counter}, writes P (packed e4m3) with tcgen05.st, and
-//              rescales its half of O in TMEM on the rare tiles that move the reference.
+//   warps 4-11 softmax + epilogue, two warpgroups (the default layout, FMHA_SOFTMAX_HALVES = 1): warpgroup p works on the tiles with
+//              counter g = p (mod 2). Thread r of a group owns query row r = TMEM lane r: it reads the row's 128 scores with one
+//              tensor-memory round trip and hands the S buffer back at once, takes the row's reference from the group of the previous
+//              tile through an 8-byte shared-memory slot {value, tile counter}, converts in place, writes P (packed e4m3) with
+//              tcgen05.st, and rescales O in TMEM on the rare tiles that move the reference. 12 warps = 168 registers per thread.
+//              The output tile leaves through shared memory and one TMA store per warpgroup.
+//              (FMHA_SOFTMAX_HALVES = 2 is the four-warpgroup layout, half a row per thread in two passes at 96 registers.)
 // TMEM columns: S0 [0,128) S1 [128,256) O [256,384) L [384,400) P0 [400,432) P1 [432,464) SFQ [464,468) SFK0 [468,472) SFK1 [472,476).
 #include "kernels.h"
 #include "ptx_sm100.cuh"
@@ -42,11 +43,20 @@ namespace {
 
 constexpr int kRows = 128;          // query rows per CTA tile
 constexpr int kKeys = 128;          // keys per tile
-constexpr int kStages = 5;          // depth of the K ring and of the V ring (freed separately: K after Q K^T, V after P V)
+constexpr int kStages = 4;          // depth of the K ring and of the V ring (freed separately: K after Q K^T, V after P V)
 // The four service warps get the lowest warp ids, one per scheduler (scheduler = warp % 4). Softmax = warps 4-19: a warp's TMEM lane
 // quadrant is warp % 4, so any four consecutive warps cover the 128 rows.
 constexpr int kMmaWarp = 0, kKProducerWarp = 1, kPvWarp = 2, kVProducerWarp = 3, kFirstSoftmaxWarp = 4;
-constexpr int kThreads = 32 * (4 + 16);   // 20 warps, five per scheduler (16 K registers each), hence 96 registers per thread
+// Softmax layout: kHalves = 1: two warpgroups, a thread owns a whole score row of a tile (128 scores in registers, read once; 12 warps,
+// 168 registers per thread). kHalves = 2: four warpgroups, a thread owns half a row (two passes over tensor memory; 20 warps, 96 registers).
+#ifndef FMHA_SOFTMAX_HALVES
+#define FMHA_SOFTMAX_HALVES 1
+#endif
+constexpr int kHalves = FMHA_SOFTMAX_HALVES;
+constexpr int kCols = 128 / kHalves;                   // score columns per softmax thread
+constexpr int kThreads = 32 * (4 + 8 * kHalves);       // the register file is 16 K registers per scheduler: 3 warps x 168 or 5 warps x 96
+constexpr int kMaxRegs = kHalves == 1 ? 168 : 96;
+constexpr bool kStagedOut = kHalves == 1;   // bf16 output through shared memory and TMA stores (whole-row layout: 64 columns per warpgroup)
 constexpr uint32_t kTileBytes = 128 * 128;   // one e4m3 tile
 constexpr uint32_t kSfBytes = 512;           // 128 rows x 4 scale bytes
 
@@ -73,7 +83,9 @@ struct SmemLayout {
     // 32 keys x 128 B of e4m3 1.0 behind the V ring: a second MN-major atom of the P V B operand, of which the MMA uses 16 columns,
     // so that O[:, 128..143] accumulates the row sums of P
     static constexpr uint32_t ones = v + kStages * kTileBytes;
-    static constexpr uint32_t sfq = ones + 4096;
+    // two 16 KB staging tiles (128 rows x 64 bf16, 128-byte swizzle) for the output's TMA stores, one per warpgroup
+    static constexpr uint32_t ostage = ones + 4096;
+    static constexpr uint32_t sfq = ostage + 2 * 16384;
     static constexpr uint32_t sfk = sfq + 2 * kSfBytes;
     static constexpr uint32_t xref = sfk + kStages * kSfBytes;   // [tile parity 2][half 2][row 128] x {reference bits, tile index}
     static constexpr uint32_t xmax = xref + 2 * 2 * 128 * 8;     // [buffer 2][tile parity 2][half 2][row 128] x {half-row maximum bits, tile index}
@@ -131,8 +143,18 @@ __device__ __forceinline__ uint32_t fast_p_bits(uint32_t s, float c) {
     asm("fma.rn.sat.f32 %0, %1, 0f3D000000, %2;" : "=f"(t) : "f"(__uint_as_float(s)), "f"(c));   // s / 32 + c
     return __float_as_uint(t + 32768.0f);
 }
+// Every kMufuEvery-th P word takes two of its four values from the exp2 unit; all the other values come from the FMA pipe.
+#ifndef FMHA_MUFU_EVERY
+#define FMHA_MUFU_EVERY 1
+#endif
+constexpr int kMufuEvery = FMHA_MUFU_EVERY;
 __device__ __forceinline__ uint32_t p_word_hybrid(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t s3, float sh, float c) {
     const uint32_t lo = cvt_e4m3x2(ex2_approx(__uint_as_float(s0) + sh), ex2_approx(__uint_as_float(s1) + sh));
+    const uint32_t hi = __byte_perm(fast_p_bits(s2, c), fast_p_bits(s3, c), 0x0040);
+    return __byte_perm(lo, hi, 0x5410);
+}
+__device__ __forceinline__ uint32_t p_word_fast(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t s3, float c) {
+    const uint32_t lo = __byte_perm(fast_p_bits(s0, c), fast_p_bits(s1, c), 0x0040);
     const uint32_t hi = __byte_perm(fast_p_bits(s2, c), fast_p_bits(s3, c), 0x0040);
     return __byte_perm(lo, hi, 0x5410);
 }
@@ -207,9 +229,9 @@ __device__ __forceinline__ Item decode_item(uint32_t w, const AttnParams& p) {
 // epilogue of the item before has read O out (o_free).
 // kTrace = false compiles every diagnostic (tile dumps, time stamps) out of the tile loop: the production launches use that variant.
 template <bool kSplit, bool kTrace>
-__global__ void __maxnreg__(96)
+__global__ void __maxnreg__(kMaxRegs)
 fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                      const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const AttnParams p) {
     auto stamp = [](float* trace, int role, int tile, int slot) { stamp_t<kTrace>(trace, role, tile, slot); };
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -251,8 +273,8 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             mbar_init(bar_q_full(b), 1);
             mbar_init(bar_q_empty(b), 1);
             mbar_init(bar_s_full(b), 1);
-            mbar_init(bar_s_free(b), 2 * kRows);
-            mbar_init(bar_p_full(b), 2 * kRows);
+            mbar_init(bar_s_free(b), kHalves * kRows);
+            mbar_init(bar_p_full(b), kHalves * kRows);
             mbar_init(bar_o_done(b), 1);
         }
         for (int st = 0; st < kStages; ++st) {
@@ -261,13 +283,13 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             mbar_init(bar_v_full(st), 1);
             mbar_init(bar_v_empty(st), 1);
         }
-        mbar_init(bar_o_free, 4 * kRows);
+        mbar_init(bar_o_free, 2 * kHalves * kRows);
         fence_mbar_init();
     }
-    if (threadIdx.x < 512) {
-        for (int i = 0; i < 2; ++i) reinterpret_cast<uint32_t*>(smem_gen + SmemLayout::ones)[threadIdx.x + 512 * i] = 0x38383838u;
-        // hand-over slots (512 reference slots, then 1024 maximum slots) start with a tile index no tile has
-        for (int i = 0; i < 3; ++i) reinterpret_cast<uint2*>(smem_gen + SmemLayout::xref)[threadIdx.x + 512 * i] = make_uint2(0u, 0xFFFFFFFFu);
+    if (threadIdx.x < 256) {
+        for (int i = 0; i < 4; ++i) reinterpret_cast<uint32_t*>(smem_gen + SmemLayout::ones)[threadIdx.x + 256 * i] = 0x38383838u;
+        // hand-over slots (512 reference slots, then 1024 maximum slots) start with a tile counter no tile has
+        for (int i = 0; i < 6; ++i) reinterpret_cast<uint2*>(smem_gen + SmemLayout::xref)[threadIdx.x + 256 * i] = make_uint2(0u, 0xFFFFFFFFu);
         fence_proxy_async_smem();
     }
     if (warp == kMmaWarp) {
@@ -359,7 +381,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             }
             ++q_issued;
             if (w + stride < n_items) load_q_scales(decode_item<kSplit>(w + stride, p), wq);   // the next item's Q scales, a whole item ahead
-            float* k_trace = (cta_traced && n == 0) ? p.trace : nullptr;
+            float* k_trace = cta_traced ? p.trace : nullptr;   // stamps are indexed by the running tile counter
             int key = static_cast<int>(it.key_lo);
             for (int j = 0; j < it.n_tiles; ++j, key += kKeys) {
                 // the stage is free once Q K^T of the tile that held it is done
@@ -379,7 +401,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    stamp(k_trace, 2, j, 6);
+                    stamp(k_trace, 2, static_cast<int>(gk), 6);
                     mbar_arrive_expect_tx(bar_k_full(st), kTileBytes);
                     tma_load_4d(k_smem + st * kTileBytes, &tm_k, bar_k_full(st), 0, static_cast<int>(it.kv_head), key, static_cast<int>(it.batch));
                 }
@@ -406,13 +428,13 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             bool ok = true;
             for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
                 const Item it = decode_item<kSplit>(w, p);
-                float* v_trace = (cta_traced && n == 0) ? p.trace : nullptr;
+                float* v_trace = cta_traced ? p.trace : nullptr;
                 int key = static_cast<int>(it.key_lo);
                 for (int j = 0; ok && j < it.n_tiles; ++j, key += kKeys) {
                     // the stage is free once P V of the tile that held it is done
                     if (gv >= static_cast<uint32_t>(kStages)) ok = mbar_wait(bar_v_empty(st), ph ^ 1u, abort_flag);
                     if (!ok) break;
-                    stamp(v_trace, 3, j, 6);
+                    stamp(v_trace, 3, static_cast<int>(gv), 6);
                     mbar_arrive_expect_tx(bar_v_full(st), kTileBytes);
                     tma_load_4d(v_smem + st * kTileBytes, &tm_v, bar_v_full(st), 0, static_cast<int>(it.kv_head), key, static_cast<int>(it.batch));
                     ++gv;
@@ -446,7 +468,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
                 const int n_tiles = decode_item<kSplit>(w, p).n_tiles;
                 const uint32_t qb = n & 1u;
-                float* mma_trace = (cta_traced && n == 0) ? p.trace : nullptr;
+                float* mma_trace = cta_traced ? p.trace : nullptr;
                 ok = mbar_wait(bar_q_full(qb), (n >> 1) & 1u, abort_flag);
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -459,7 +481,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     if (ok && g >= 2) ok = mbar_wait(bar_s_free(g & 1u), ((g >> 1) - 1u) & 1u, abort_flag);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    stamp(mma_trace, 2, j, 2);
+                    stamp(mma_trace, 2, static_cast<int>(g), 2);
                     const uint32_t t_sfk = tmem + ((g & 1u) ? kColSfK1 : kColSfK0);
                     const uint32_t t_s = tmem + ((g & 1u) ? kColS1 : kColS0);
                     tmem_cp_sf(t_sfk, dsf0 + static_cast<uint64_t>((st * kSfBytes) >> 4));
@@ -470,11 +492,11 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         mma_mxf8_ss(t_s, dq + 2u * kb, dk + 2u * kb, id, t_sfq + (static_cast<uint32_t>(kb) << 30),
                                     t_sfk + (static_cast<uint32_t>(kb) << 30), kb > 0 ? 1u : 0u);
                     }
-                    stamp(mma_trace, 2, j, 4);
+                    stamp(mma_trace, 2, static_cast<int>(g), 4);
                     tc_commit(bar_s_full(g & 1u));
                     tc_commit(bar_k_empty(st));
                     if (j == n_tiles - 1) tc_commit(bar_q_empty(qb));   // the Q buffer can take the item after next
-                    stamp(mma_trace, 2, j, 5);
+                    stamp(mma_trace, 2, static_cast<int>(g), 5);
                     ++g;
                     if (++st == kStages) { st = 0; ph ^= 1u; }
                 }
@@ -491,7 +513,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             bool ok = true;
             for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
                 const int n_tiles = decode_item<kSplit>(w, p).n_tiles;
-                float* mma_trace = (cta_traced && n == 0) ? p.trace : nullptr;
+                float* mma_trace = cta_traced ? p.trace : nullptr;
                 // an item's first tile overwrites O and L, which the epilogue of the item before must have read out
                 if (n > 0) ok = mbar_wait(bar_o_free, (n - 1u) & 1u, abort_flag);
                 for (int i = 0; ok && i < n_tiles; ++i) {
@@ -500,7 +522,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     if (ok) ok = mbar_wait(bar_p_full(g & 1u), (g >> 1) & 1u, abort_flag);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    stamp(mma_trace, 3, i, 2);
+                    stamp(mma_trace, 3, static_cast<int>(g), 2);
                     const uint32_t t_p = tmem + ((g & 1u) ? kColP1 : kColP0);
 #pragma unroll
                     for (int kb = 0; kb < 4; ++kb) {
@@ -509,10 +531,10 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         const uint64_t dv = make_smem_desc(v_addr, ones_smem - v_addr, 1024, kSwizzle128B);
                         mma_f8_ts(tmem + kColO, t_p + 8 * kb, dv, idesc_pv, (i > 0 || kb > 0) ? 1u : 0u);
                     }
-                    stamp(mma_trace, 3, i, 3);
+                    stamp(mma_trace, 3, static_cast<int>(g), 3);
                     tc_commit(bar_v_empty(st));
                     tc_commit(bar_o_done(g & 1u));
-                    stamp(mma_trace, 3, i, 4);
+                    stamp(mma_trace, 3, static_cast<int>(g), 4);
                     ++g;
                     if (++st == kStages) { st = 0; ph ^= 1u; }
                 }
@@ -521,8 +543,8 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         __syncwarp();
     } else if (warp >= kFirstSoftmaxWarp) {
         // =========================================================== softmax + epilogue ===========================================================
-        // Four warpgroups: wg = 2 * half + parity. Parity = which tiles (counter g = parity mod 2) and which S / P buffer; half = which 64 key
-        // columns of the tile (and, in the epilogue, which 32 head dims together with the parity). Thread r of a group owns query row r.
+        // 2 * kHalves warpgroups: wg = 2 * half + parity. Parity = which tiles (counter g = parity mod 2) and which S / P buffer; half =
+        // which kCols key columns of the tile. Thread r of a group owns query row r.
         const uint32_t st_id = threadIdx.x - 32u * kFirstSoftmaxWarp;
         const uint32_t wg = st_id >> 7;
         const uint32_t par = wg & 1u, half = wg >> 1;
@@ -530,9 +552,9 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const uint32_t lane_base = (static_cast<uint32_t>(warp & 3) * 32u) << 16;
         const uint32_t xref = smem_base + SmemLayout::xref;   // 8-byte slots, accessed with single 64-bit shared loads / stores
         const uint32_t xmax = smem_base + SmemLayout::xmax;
-        const uint32_t t_s = tmem + (par ? kColS1 : kColS0) + lane_base + 64u * half;
-        const uint32_t t_p = tmem + (par ? kColP1 : kColP0) + lane_base + 16u * half;
-        const uint32_t t_o_half = tmem + kColO + lane_base + 64u * half;
+        const uint32_t t_s = tmem + (par ? kColS1 : kColS0) + lane_base + kCols * half;
+        const uint32_t t_p = tmem + (par ? kColP1 : kColP0) + lane_base + (kCols / 4) * half;
+        const uint32_t t_o_part = tmem + kColO + lane_base + kCols * half;
         const uint32_t t_l = tmem + kColL + lane_base;
         bool ok = true;
 
@@ -550,9 +572,9 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             out = __uint_as_float(o.x);
             return true;
         };
-        // the reference the row has after tile g: published by both half-row threads that handled tile g, read from the same half
+        // the reference the row has after tile g: published by every thread of the row that handled tile g, read from the same half
         auto ref_slot = [&](uint32_t g) { return xref + 8u * (((g & 1u) * 2u + half) * 128u + r); };
-        // the half-row maximum of tile g: double buffered over this parity's consecutive tiles
+        // the half-row maximum of tile g (kHalves = 2): double buffered over this parity's consecutive tiles
         auto max_slot = [&](uint32_t g, uint32_t h) { return xmax + 8u * (((((g >> 1) & 1u) * 2u + par) * 2u + h) * 128u + r); };
 
         uint32_t g0 = 0, n = 0;   // tile counter at the item's first tile; ordinal of the item
@@ -562,7 +584,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             {
                 const Item it = decode_item<kSplit>(w, p);
                 n_tiles = it.n_tiles;
-                tail_valid = static_cast<int>(it.key_hi - it.key_lo) - (n_tiles - 1) * kKeys - 64 * static_cast<int>(half);
+                tail_valid = static_cast<int>(it.key_hi - it.key_lo) - (n_tiles - 1) * kKeys - kCols * static_cast<int>(half);
             }
             const bool tracing = cta_traced && n == 0;
             const bool dumping = tracing && !(p.flags & 0x4u);   // flag 0x4: time stamps only, no tile dumps
@@ -571,23 +593,56 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             for (int j = static_cast<int>((g0 ^ par) & 1u); j < n_tiles; j += 2) {
                 const uint32_t g = g0 + static_cast<uint32_t>(j);
                 const uint32_t k = g >> 1;   // this parity's tile counter
-                float* st_trace = (tracing && r == 0 && half == 0) ? p.trace : nullptr;
-                stamp(st_trace, par, j, 0);
+                float* st_trace = (cta_traced && r == 0 && half == 0) ? p.trace : nullptr;
+                stamp(st_trace, par, static_cast<int>(g), 0);
                 if (!mbar_wait(bar_s_full(par), k & 1u, abort_flag)) ok = false;   // no divergent exit: the votes below keep the warp together
                 tc_fence_after_sync();
-                stamp(st_trace, par, j, 1);
-                // Pass 1 over the 64 scores of this half row, 32 at a time: the maximum only. The scores are read again for the conversion
-                // below instead of being kept, which keeps a softmax thread under 96 registers (20 warps share the register file).
-                const int nvalid = (j == n_tiles - 1) ? tail_valid : 64;   // valid keys of this half row's 64
+                stamp(st_trace, par, static_cast<int>(g), 1);
+                const int nvalid = (j == n_tiles - 1) ? tail_valid : kCols;   // valid keys among this thread's kCols
                 float mt;
+#if FMHA_SOFTMAX_HALVES == 1
+                // All 128 scores of the row in registers with one tensor-memory round trip; the score buffer is handed back at once, so
+                // that Q K^T of tile g + 2 runs under this tile's conversion. The scores are converted in place further down.
+                uint32_t v[128];
                 {
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) tmem_ld32(t_s + 32 * ch, *reinterpret_cast<uint32_t(*)[32]>(&v[32 * ch]));
+                    tmem_wait_ld();
+                    tc_fence_before_sync();
+                    mbar_arrive(bar_s_free(par));
+                    if (nvalid < kCols) {   // keys past the range: -inf for the maximum, 0 for P (crates/amdgpu-tile/src/reduce.rs:35-49)
+#pragma unroll
+                        for (int c = 0; c < 128; ++c) {
+                            if (c >= nvalid) v[c] = 0xFF800000u;
+                        }
+                    }
+                    if (dumping && j == 0) {
+#pragma unroll
+                        for (int c = 0; c < 128; ++c) p.trace[r * 128 + c] = __uint_as_float(v[c]);
+                    }
+                    float m[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) m[i] = -INFINITY;
+#pragma unroll
+                    for (int c = 0; c < 128; c += 16) {   // eight independent chains of three-input maxima
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) m[i] = max3(m[i], __uint_as_float(v[c + 2 * i]), __uint_as_float(v[c + 2 * i + 1]));
+                    }
+                    mt = fmaxf(fmaxf(max3(m[0], m[1], m[2]), max3(m[3], m[4], m[5])), fmaxf(m[6], m[7]));
+                    stamp(st_trace, par, static_cast<int>(g), 2);
+                    stamp(st_trace, par, static_cast<int>(g), 3);
+                }
+#else
+                {
+                    // Pass 1 over the 64 scores of this half row, 32 at a time: the maximum only. The scores are read again for the conversion
+                    // below instead of being kept, which keeps a softmax thread under 96 registers (20 warps share the register file).
                     float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll 1
                     for (int ch = 0; ch < 2; ++ch) {
                         uint32_t s[32];
                         tmem_ld32(t_s + 32 * ch, s);
                         tmem_wait_ld();
-                        if (nvalid < 64) {   // keys past the range: -inf for the maximum, 0 for P (crates/amdgpu-tile/src/reduce.rs:35-49)
+                        if (nvalid < kCols) {
 #pragma unroll
                             for (int c = 0; c < 32; ++c) {
                                 if (c + 32 * ch >= nvalid) s[c] = 0xFF800000u;
@@ -606,21 +661,20 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         }
                     }
                     mt = fmaxf(max3(m0, m1, m2), m3);
-                }
-                stamp(st_trace, par, j, 2);
-                // exchange the half-row maxima with the thread that holds the other 64 keys of this row
-                st_shared_v2(max_slot(g, half), __float_as_uint(mt), g);
-                stamp(st_trace, par, j, 3);
-                {
+                    stamp(st_trace, par, static_cast<int>(g), 2);
+                    // exchange the half-row maxima with the thread that holds the other 64 keys of this row
+                    st_shared_v2(max_slot(g, half), __float_as_uint(mt), g);
+                    stamp(st_trace, par, static_cast<int>(g), 3);
                     float other = mt;
                     if (!wait_slot(max_slot(g, half ^ 1u), g, other)) ok = false;
                     mt = fmaxf(mt, other);
                 }
+#endif
                 // take over the row's reference from the threads that handled the item's previous tile
                 if (ok && j > 0 && !wait_slot(ref_slot(g - 1u), g - 1u, ref)) ok = false;
                 if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
                 // the reference moves when this tile's maximum passes it by more than the threshold (negative for short sequences: it then
-                // also follows the tile maximum down, and f > 1 scales O and L up). Both halves of a row see the same mt and ref.
+                // also follows the tile maximum down, and f > 1 scales O and L up). All threads of a row see the same mt and ref.
                 const bool move = mt > ref + thr;
                 float f = 1.0f;
                 if (move) {
@@ -629,17 +683,17 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     ref = nref;
                 }
                 st_shared_v2(ref_slot(g), __float_as_uint(ref), g);
-                stamp(st_trace, par, j, 4);
+                stamp(st_trace, par, static_cast<int>(g), 4);
                 // P V of this parity's previous tile must be done before its P columns are overwritten (and, observed in order, this keeps
                 // the phase parity of the other parity's barrier below unambiguous)
                 if (k > 0 && !mbar_wait(bar_o_done(par), (k - 1u) & 1u, abort_flag)) ok = false;
-                stamp(st_trace, par, j, 5);
+                stamp(st_trace, par, static_cast<int>(g), 5);
                 if (j > 0 && __any_sync(0xFFFFFFFFu, move)) {
                     // O holds P V of all the item's tiles before j once the other parity's last P V is done; P V of tile j cannot start before this thread's arrive below
                     if (!mbar_wait(bar_o_done(par ^ 1u), ((g - 1u) >> 1) & 1u, abort_flag)) ok = false;
                     tc_fence_after_sync();
-                    scale_tmem32(t_o_half, f);
-                    scale_tmem32(t_o_half + 32, f);
+#pragma unroll 1
+                    for (int c = 0; c < kCols / 32; ++c) scale_tmem32(t_o_part + 32 * c, f);
                     if (half == 0) {   // the row sum lives in column 0 of L
                         uint32_t lv;
                         asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(lv) : "r"(t_l) : "memory");
@@ -649,10 +703,23 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     }
                     tmem_wait_st();
                 }
-                // Pass 2: P = e4m3(2^(s - ref + offset)), four keys per 32-bit TMEM column
+                // P = e4m3(2^(s - ref + offset)), four keys per 32-bit TMEM column
                 const float sh = kPOffset - ref;
                 const float cf = (kPOffset + 7.0f - kFastBias - ref) * 0.03125f;
-                uint32_t pw[16];
+                uint32_t pw[kCols / 4];
+#if FMHA_SOFTMAX_HALVES == 1
+                if (lazy) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        pw[c] = kMufuEvery == 0 ? p_word(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3], sh)
+                                : (c % (kMufuEvery ? kMufuEvery : 1) == 0) ? p_word_hybrid(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3], sh, cf)
+                                                                           : p_word_fast(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3], cf);
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) pw[c] = p_word(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3], sh);
+                }
+#else
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
                     uint32_t s[32];
@@ -662,7 +729,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         tc_fence_before_sync();
                         mbar_arrive(bar_s_free(par));   // the score buffer can take tile g + 2 once all 256 threads of this parity are done with it
                     }
-                    if (nvalid < 64) {
+                    if (nvalid < kCols) {
 #pragma unroll
                         for (int c = 0; c < 32; ++c) {
                             if (c + 32 * ch >= nvalid) s[c] = 0xFF800000u;
@@ -670,48 +737,65 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     }
                     if (lazy) {
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) pw[8 * ch + c] = p_word_hybrid(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], sh, cf);
+                        for (int c = 0; c < 8; ++c) {
+                            pw[8 * ch + c] = (c % kMufuEvery == 0) ? p_word_hybrid(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], sh, cf)
+                                                                   : p_word_fast(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], cf);
+                        }
                     } else {
 #pragma unroll
                         for (int c = 0; c < 8; ++c) pw[8 * ch + c] = p_word(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], sh);
                     }
                 }
+#endif
                 if (dumping && j == 0) {
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) reinterpret_cast<uint32_t*>(p.trace)[32768 + 256 + r * 32 + 16 * half + c] = pw[c];
+                    for (int c = 0; c < kCols / 4; ++c) reinterpret_cast<uint32_t*>(p.trace)[32768 + 256 + r * 32 + (kCols / 4) * half + c] = pw[c];
                 }
-                stamp(st_trace, par, j, 6);
+                stamp(st_trace, par, static_cast<int>(g), 6);
+#if FMHA_SOFTMAX_HALVES == 1
+                tmem_st32(t_p, pw);
+#else
                 tmem_st16(t_p, pw);
+#endif
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(bar_p_full(par));
-                stamp(st_trace, par, j, 7);
+                stamp(st_trace, par, static_cast<int>(g), 7);
             }
             if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
 
-            // ---- epilogue: O * v_descale / l; warpgroup wg stores head dims [32 wg, 32 wg + 32) ----
+            // ---- epilogue: O * v_descale / l; warpgroup wg stores head dims [kOutCols wg, kOutCols wg + kOutCols) ----
             {
+                constexpr int kOutCols = 128 / (2 * kHalves);
+                const float vd = __ldg(p.v_descale);   // issued ahead of the waits below
+                float* ep_trace = (cta_traced && r == 0 && half == 0) ? p.trace : nullptr;   // epilogue stamps: tile index 24 + item ordinal
+                stamp(ep_trace, par, 24 + static_cast<int>(n), 0);
                 const uint32_t g_last = g0 + static_cast<uint32_t>(n_tiles) - 1u;
                 // this parity's last tile of the item first (its barrier is observed phase by phase), then the other parity's
                 const uint32_t g_mine = ((g_last & 1u) == par) ? g_last : g_last - 1u;
                 const uint32_t g_theirs = ((g_last & 1u) == par) ? g_last - 1u : g_last;
                 if (n_tiles > (((g_last & 1u) == par) ? 0 : 1)) ok = mbar_wait(bar_o_done(par), (g_mine >> 1) & 1u, abort_flag);
+                stamp(ep_trace, par, 24 + static_cast<int>(n), 1);
                 if (ok && n_tiles > (((g_last & 1u) == par) ? 1 : 0)) ok = mbar_wait(bar_o_done(par ^ 1u), (g_theirs >> 1) & 1u, abort_flag);
+                stamp(ep_trace, par, 24 + static_cast<int>(n), 2);
                 if (ok) ok = wait_slot(ref_slot(g_last), g_last, ref);
                 if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+                stamp(ep_trace, par, 24 + static_cast<int>(n), 3);
                 tc_fence_after_sync();
                 uint32_t lv;
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(lv) : "r"(t_l) : "memory");
-                uint32_t o[32];
-                tmem_ld32(tmem + kColO + lane_base + 32u * wg, o);
+                uint32_t o[kOutCols];
+#pragma unroll
+                for (int c = 0; c < kOutCols / 32; ++c) tmem_ld32(tmem + kColO + lane_base + kOutCols * wg + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&o[32 * c]));
                 tmem_wait_ld();
                 tc_fence_before_sync();
                 mbar_arrive(bar_o_free);   // O and L are in registers: the next item's first P V may overwrite them
+                stamp(ep_trace, par, 24 + static_cast<int>(n), 4);
                 uint32_t w_again;          // opaque copy: keeps the compiler from holding the decoded item in registers across the tile loop
                 asm volatile("mov.u32 %0, %1;" : "=r"(w_again) : "r"(w));
                 const Item it = decode_item<kSplit>(w_again, p);
+                stamp(ep_trace, par, 24 + static_cast<int>(n), 5);
                 const float l = __uint_as_float(lv);
-                const float vd = *p.v_descale;
                 const float fin = vd / l;   // crates/amdgpu-stage/src/attention/state.rs:79-82
                 const uint32_t row = it.row0 + r;
                 const bool row_ok = row < p.S;   // rows past the sequence are computed on clamped scales and not stored (block3.rs:194)
@@ -721,22 +805,50 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 }
                 if (dumping) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) p.trace[16384 + r * 128 + 32 * wg + c] = __uint_as_float(o[c]);
+                    for (int c = 0; c < kOutCols; ++c) p.trace[16384 + r * 128 + kOutCols * wg + c] = __uint_as_float(o[c]);
+                }
+                if (kStagedOut && !kSplit) {
+                    // A thread owns a row, so direct stores would touch 32 different lines per instruction. The warpgroup's 128 x 64 bf16
+                    // tile goes through shared memory (128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8)) and out with
+                    // one TMA store, which also leaves out the rows past the sequence.
+                    const uint32_t stg = smem_base + SmemLayout::ostage + wg * 16384u;
+                    const bool issuer = (st_id & 127u) == 0u;
+                    if (n > 0) {   // the previous item's store must have read the staging tile out
+                        if (issuer) bulk_wait_group_read0();
+                        named_bar_sync(1u + wg, 128u);
+                    }
+#pragma unroll
+                    for (int c = 0; c < kOutCols / 8; ++c) {
+                        uint32_t wv[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[8 * c + 2 * e]) * fin, __uint_as_float(o[8 * c + 2 * e + 1]) * fin);
+                            wv[e] = *reinterpret_cast<const uint32_t*>(&b2);
+                        }
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stg + r * 128u + ((static_cast<uint32_t>(c) ^ (r & 7u)) << 4)),
+                                     "r"(wv[0]), "r"(wv[1]), "r"(wv[2]), "r"(wv[3]) : "memory");
+                    }
+                    fence_proxy_async_smem();
+                    named_bar_sync(1u + wg, 128u);
+                    if (issuer) {
+                        tma_store_4d(&tm_o, stg, static_cast<int>(kOutCols * wg), static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
+                        bulk_commit_group();
+                    }
                 }
                 if (row_ok) {
                     if (kSplit) {
                         const size_t prow = static_cast<size_t>(it.split) * p.rows_total + (static_cast<size_t>(it.batch) * p.S + row) * p.H + it.head;
-                        float4* dst = reinterpret_cast<float4*>(p.ohat + prow * 128 + 32 * wg);
+                        float4* dst = reinterpret_cast<float4*>(p.ohat + prow * 128 + kOutCols * wg);
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) {
+                        for (int c = 0; c < kOutCols / 4; ++c) {
                             dst[c] = make_float4(__uint_as_float(o[4 * c]) * fin, __uint_as_float(o[4 * c + 1]) * fin,
                                                  __uint_as_float(o[4 * c + 2]) * fin, __uint_as_float(o[4 * c + 3]) * fin);
                         }
-                    } else {
+                    } else if (!kStagedOut) {
                         uint8_t* orow = p.o + static_cast<size_t>(it.batch) * p.o_batch_stride + static_cast<size_t>(row) * p.o_row_stride + it.head * 256u;
-                        uint4* dst = reinterpret_cast<uint4*>(orow + 64 * wg);
+                        uint4* dst = reinterpret_cast<uint4*>(orow + 2 * kOutCols * wg);
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) {
+                        for (int c = 0; c < kOutCols / 8; ++c) {
                             uint32_t wv[4];
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
@@ -757,8 +869,10 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     }
                 }
             }
+            stamp((cta_traced && r == 0 && half == 0) ? p.trace : nullptr, par, 24 + static_cast<int>(n), 6);
             g0 += static_cast<uint32_t>(n_tiles);
         }
+        if (kStagedOut && !kSplit && (st_id & 127u) == 0u) bulk_wait_group0();   // the output stores of this thread are done before the CTA ends
     }
 
     // ---- teardown ----
@@ -771,10 +885,10 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     }
 }
 
-cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const AttnParams& p,
+cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnParams& p,
                              uint32_t B, bool split, uint32_t rows_per_cta, cudaStream_t stream) {
     (void)rows_per_cta;   // both logical block heights run as 128-row CTAs
-    using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
+    using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
     static const Kernel kernels[4] = {fmha_fwd_mxfp8_kernel<false, false>, fmha_fwd_mxfp8_kernel<true, false>,
                                       fmha_fwd_mxfp8_kernel<false, true>, fmha_fwd_mxfp8_kernel<true, true>};
     constexpr int kMaxDevices = 64;
@@ -804,7 +918,7 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
     if (items == 0 || items > 0xFFFFFFFFull) return cudaErrorInvalidValue;
     q.n_items = static_cast<uint32_t>(items);
     const uint32_t ctas = q.n_items < static_cast<uint32_t>(sm_count[dev]) ? q.n_items : static_cast<uint32_t>(sm_count[dev]);
-    kernels[which]<<<dim3(ctas, 1, 1), kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, q);
+    kernels[which]<<<dim3(ctas, 1, 1), kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, q);
     return cudaGetLastError();
 }
 

@@ -165,6 +165,21 @@ int make_tile_map(CUtensorMap* m, const void* base, uint64_t seq, uint64_t heads
     return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r);
 }
 
+// The bf16 output [batch, seq, heads, 128] as a 4-D map (head dim, head, row, batch) with a 128-row x 64-column box, 128-byte swizzle:
+// the shape of one warpgroup's TMA store. Rows past `seq` are not written.
+int make_out_map(CUtensorMap* m, void* base, uint64_t seq, uint64_t heads, uint64_t batches, uint64_t head_stride, uint64_t row_stride,
+                 uint64_t batch_stride) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return -static_cast<int>(cudaErrorSymbolNotFound);
+    const cuuint64_t dims[4] = {128, heads, seq, batches};
+    const cuuint64_t strides[3] = {head_stride, row_stride, batch_stride == 0 ? row_stride * seq : batch_stride};
+    const cuuint32_t box[4] = {64, 1, 128, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r);
+}
+
 uint32_t log2_u32(uint32_t x) {
     uint32_t l = 0;
     while ((1u << l) < x) ++l;
@@ -220,7 +235,12 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
     if (r) return r;
     r = make_tile_map(&tv, a->ptr_v, p.SK, p.HK, B, a->s_v_Hs, a->s_v_Seqs, a->s_v_Bs);
     if (r) return r;
-    const cudaError_t e = fmha::launch_attention(tq, tk, tv, p, B, split, kernel == FMHA_MXFP8_T128 ? 128u : 256u, stream);
+    CUtensorMap to = tq;   // the split kernel writes f32 partials with plain stores and never looks at this map
+    if (!split) {
+        r = make_out_map(&to, a->ptr_o, p.S, p.H, B, a->s_o_Hs, a->s_o_Seqs, a->s_o_Bs);
+        if (r) return r;
+    }
+    const cudaError_t e = fmha::launch_attention(tq, tk, tv, to, p, B, split, kernel == FMHA_MXFP8_T128 ? 128u : 256u, stream);
     return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }
 

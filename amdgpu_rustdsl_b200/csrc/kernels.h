@@ -31,7 +31,8 @@ struct AttnParams {
 };
 
 // rows_per_cta is 128 (t128) or 256 (vs128 / kvsplit): the logical block height of the reference's grids.
-cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const AttnParams& p,
+// tm_o: the bf16 output as a 4-D map with a 128-row x 64-column box (unsplit kernels; ignored by the split kernel)
+cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnParams& p,
                              uint32_t B, bool split, uint32_t rows_per_cta, cudaStream_t stream);
 
 cudaError_t launch_combine(const float* ohat, const float* lse2, uint8_t* out, uint32_t rows_total, uint32_t splits, cudaStream_t stream);
