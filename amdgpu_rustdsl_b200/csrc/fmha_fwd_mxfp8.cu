@@ -267,10 +267,11 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const bool cta_traced = kTrace && p.trace != nullptr && blockIdx.x == 0;   // diagnostics cover the first item of CTA 0 = logical block (0,0,0)
 
     // ---- one-time setup ----
+    if (threadIdx.x == 0) stamp(cta_traced ? p.trace : nullptr, 2, 30, 0);   // kernel entry
     if (threadIdx.x == 0) {
         *abort_flag = 0u;
         for (int b = 0; b < 2; ++b) {
-            mbar_init(bar_q_full(b), 1);
+            mbar_init(bar_q_full(b), 2);   // the TMA's expect-tx arrive + the arrive that follows the scale bytes
             mbar_init(bar_q_empty(b), 1);
             mbar_init(bar_s_full(b), 1);
             mbar_init(bar_s_free(b), kHalves * kRows);
@@ -278,7 +279,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             mbar_init(bar_o_done(b), 1);
         }
         for (int st = 0; st < kStages; ++st) {
-            mbar_init(bar_k_full(st), 1);
+            mbar_init(bar_k_full(st), 2);
             mbar_init(bar_k_empty(st), 1);
             mbar_init(bar_v_full(st), 1);
             mbar_init(bar_v_empty(st), 1);
@@ -305,6 +306,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    if (threadIdx.x == 0) stamp(cta_traced ? p.trace : nullptr, 2, 30, 2);   // setup done
 
     // The four service roles are single chains of dependent instructions that share their scheduler with four arithmetic-dense softmax
     // warps, so every instruction costs them several clocks: each role is its own warp, waits with blocking mbarrier waits (its
@@ -353,6 +355,15 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 w[i] = __ldg(reinterpret_cast<const uint32_t*>(p.q_descale + off));
             }
         };
+        // The CTA's first two copies (Q tile and first K tile of its first item) go out before anything else of this role's set-up.
+        if (lane == 0 && blockIdx.x < n_items) {
+            const Item it = decode_item<kSplit>(blockIdx.x, p);
+            mbar_arrive_expect_tx(bar_q_full(0), kTileBytes);
+            tma_load_4d(q_smem, &tm_q, bar_q_full(0), 0, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
+            stamp(cta_traced ? p.trace : nullptr, 2, 0, 6);
+            mbar_arrive_expect_tx(bar_k_full(0), kTileBytes);
+            tma_load_4d(k_smem, &tm_k, bar_k_full(0), 0, static_cast<int>(it.kv_head), static_cast<int>(it.key_lo), static_cast<int>(it.batch));
+        }
         ScaleCursor cs;
         cs.w = blockIdx.x;
         enter_item(cs);
@@ -372,13 +383,15 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             // the Q buffer was last used two items ago
             if (n >= 2) ok = mbar_wait(bar_q_empty(qb), ((n >> 1) - 1u) & 1u, abort_flag);
             if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
-            *reinterpret_cast<uint4*>(smem_gen + SmemLayout::sfq + qb * kSfBytes + lane * 16) = make_uint4(wq[0], wq[1], wq[2], wq[3]);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
+            // the tile copy goes out first: it does not depend on the scale bytes, whose global loads may still be in flight
+            if (lane == 0 && n > 0) {
                 mbar_arrive_expect_tx(bar_q_full(qb), kTileBytes);
                 tma_load_4d(q_smem + qb * kTileBytes, &tm_q, bar_q_full(qb), 0, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
             }
+            *reinterpret_cast<uint4*>(smem_gen + SmemLayout::sfq + qb * kSfBytes + lane * 16) = make_uint4(wq[0], wq[1], wq[2], wq[3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_q_full(qb));
             ++q_issued;
             if (w + stride < n_items) load_q_scales(decode_item<kSplit>(w + stride, p), wq);   // the next item's Q scales, a whole item ahead
             float* k_trace = cta_traced ? p.trace : nullptr;   // stamps are indexed by the running tile counter
@@ -387,6 +400,11 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 // the stage is free once Q K^T of the tile that held it is done
                 if (gk >= static_cast<uint32_t>(kStages)) ok = mbar_wait(bar_k_empty(st), ph ^ 1u, abort_flag);
                 if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+                if (lane == 0 && gk > 0) {
+                    stamp(k_trace, 2, static_cast<int>(gk), 6);
+                    mbar_arrive_expect_tx(bar_k_full(st), kTileBytes);
+                    tma_load_4d(k_smem + st * kTileBytes, &tm_k, bar_k_full(st), 0, static_cast<int>(it.kv_head), key, static_cast<int>(it.batch));
+                }
                 uint4* sf_dst = reinterpret_cast<uint4*>(smem_gen + SmemLayout::sfk + st * kSfBytes + lane * 16);
                 auto put_and_refill = [&](uint32_t (&set)[4]) {
                     *sf_dst = make_uint4(set[0], set[1], set[2], set[3]);
@@ -400,11 +418,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) {
-                    stamp(k_trace, 2, static_cast<int>(gk), 6);
-                    mbar_arrive_expect_tx(bar_k_full(st), kTileBytes);
-                    tma_load_4d(k_smem + st * kTileBytes, &tm_k, bar_k_full(st), 0, static_cast<int>(it.kv_head), key, static_cast<int>(it.batch));
-                }
+                if (lane == 0) mbar_arrive(bar_k_full(st));
                 ++gk;
                 if (++st == kStages) { st = 0; ph ^= 1u; }
             }
@@ -872,12 +886,13 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             stamp((cta_traced && r == 0 && half == 0) ? p.trace : nullptr, par, 24 + static_cast<int>(n), 6);
             g0 += static_cast<uint32_t>(n_tiles);
         }
-        if (kStagedOut && !kSplit && (st_id & 127u) == 0u) bulk_wait_group0();   // the output stores of this thread are done before the CTA ends
+        if (kStagedOut && !kSplit && (st_id & 127u) == 0u) bulk_wait_group_read0();   // the staging tiles have been read out before the CTA gives its shared memory back
     }
 
     // ---- teardown ----
     tc_fence_before_sync();
     __syncthreads();
+    if (threadIdx.x == 0) stamp(cta_traced ? p.trace : nullptr, 2, 30, 1);   // all roles done
     if (threadIdx.x == 0 && *abort_flag != 0u) atomicOr(p.status, 1u);
     if (warp == kMmaWarp) {
         tc_fence_after_sync();
