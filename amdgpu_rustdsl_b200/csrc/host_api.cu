@@ -208,6 +208,7 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
     p.qs_batch_stride = a->s_descale_q_Bs;
     p.ks_batch_stride = a->s_descale_k_Bs;
     p.flags = a->ext_flags;
+    if (p.flags & FMHA_MXFP8_FLAG_V_BLOCKSCALE) return FMHA_MXFP8_E_ARG;   // per-32-key V scales are declared in the ABI but no kernel implements them
     p.v_blockscale = (p.flags & FMHA_MXFP8_FLAG_V_BLOCKSCALE) ? static_cast<const uint8_t*>(a->ext_ptr_v_blockscale) : nullptr;
     p.lse_nat = split ? nullptr : static_cast<float*>(a->ext_ptr_lse);
     p.trace = g_trace;

@@ -129,3 +129,16 @@ def test_python_entry_rejects_bad_shapes_like_the_reference():
     q = torch.zeros(1, 4, 2, 64, dtype=torch.uint8)
     with pytest.raises(ValueError):
         fmha_fwd_mxfp8(q, q, q, q, q, q, q)   # head dim 64
+
+
+def test_launch_refuses_the_unimplemented_v_block_scales(abi):
+    """Per-32-key V scales are declared in the pad bytes of the argument block (ext_flags bit 0) but no kernel implements them: the launch
+    refuses such a block before it touches the device instead of ignoring the flag."""
+    lib = abi.load()
+    for kernel in (0, 1, 2):
+        args, _, grid, _ = CC.materialize({"kernel": kernel, "B": 1, "H": 2, "HK": 2, "S": 256, "SK": 512, "splits": 2, "mut": []})
+        buf = bytearray(args)
+        buf[0x058:0x05C] = (abi.FLAG_V_BLOCKSCALE).to_bytes(4, "little")
+        g = abi.grid3(*grid)
+        raw = (C.c_char * len(buf)).from_buffer(buf)
+        assert lib.fmha_mxfp8_launch(kernel, raw, g, None) == 6   # FMHA_MXFP8_E_ARG
