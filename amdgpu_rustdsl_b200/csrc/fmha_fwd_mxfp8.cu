@@ -609,11 +609,12 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 const uint32_t k = g >> 1;   // this parity's tile counter
                 float* st_trace = (cta_traced && r == 0 && half == 0) ? p.trace : nullptr;
                 stamp(st_trace, par, static_cast<int>(g), 0);
-                if (!mbar_wait(bar_s_full(par), k & 1u, abort_flag)) ok = false;   // no divergent exit: the votes below keep the warp together
+                if (!mbar_wait(bar_s_full(par), k & 1u, abort_flag)) ok = false;   // no divergent exit: a failed wait only clears `ok`, the vote after the tile loop ends the role
                 tc_fence_after_sync();
                 stamp(st_trace, par, static_cast<int>(g), 1);
                 const int nvalid = (j == n_tiles - 1) ? tail_valid : kCols;   // valid keys among this thread's kCols
                 float mt;
+                bool pv_seen = false;   // P V of this parity's previous tile is known to be done
 #if FMHA_SOFTMAX_HALVES == 1
                 // All 128 scores of the row in registers with one tensor-memory round trip; the score buffer is handed back at once, so
                 // that Q K^T of tile g + 2 runs under this tile's conversion. The scores are converted in place further down.
@@ -621,6 +622,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 {
 #pragma unroll
                     for (int ch = 0; ch < 4; ++ch) tmem_ld32(t_s + 32 * ch, *reinterpret_cast<uint32_t(*)[32]>(&v[32 * ch]));
+                    pv_seen = k == 0 || mbar_test_wait(bar_o_done(par), (k - 1u) & 1u);   // probed under the tensor-memory round trip
                     tmem_wait_ld();
                     tc_fence_before_sync();
                     mbar_arrive(bar_s_free(par));
@@ -686,7 +688,6 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #endif
                 // take over the row's reference from the threads that handled the item's previous tile
                 if (ok && j > 0 && !wait_slot(ref_slot(g - 1u), g - 1u, ref)) ok = false;
-                if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
                 // the reference moves when this tile's maximum passes it by more than the threshold (negative for short sequences: it then
                 // also follows the tile maximum down, and f > 1 scales O and L up). All threads of a row see the same mt and ref.
                 const bool move = mt > ref + thr;
@@ -700,7 +701,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 stamp(st_trace, par, static_cast<int>(g), 4);
                 // P V of this parity's previous tile must be done before its P columns are overwritten (and, observed in order, this keeps
                 // the phase parity of the other parity's barrier below unambiguous)
-                if (k > 0 && !mbar_wait(bar_o_done(par), (k - 1u) & 1u, abort_flag)) ok = false;
+                if (!pv_seen && k > 0 && !mbar_wait(bar_o_done(par), (k - 1u) & 1u, abort_flag)) ok = false;
                 stamp(st_trace, par, static_cast<int>(g), 5);
                 if (j > 0 && __any_sync(0xFFFFFFFFu, move)) {
                     // O holds P V of all the item's tiles before j once the other parity's last P V is done; P V of tile j cannot start before this thread's arrive below
