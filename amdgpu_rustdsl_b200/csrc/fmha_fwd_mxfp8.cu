@@ -266,6 +266,9 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const float thr = lazy ? kLazyThreshold : -kFollowWindow;
     const bool cta_traced = kTrace && p.trace != nullptr && blockIdx.x == 0;   // diagnostics cover the first item of CTA 0 = logical block (0,0,0)
 
+    // Programmatic dependent launch: the next launch in the stream (if it asks for it, as this library's own launches do) may be
+    // scheduled while this grid runs; its CTAs become resident as ours exit and do their set-up, then wait below for this grid's end.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // ---- one-time setup ----
     if (threadIdx.x == 0) stamp(cta_traced ? p.trace : nullptr, 2, 30, 0);   // kernel entry
     if (threadIdx.x == 0) {
@@ -306,6 +309,8 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    // nothing above touches global memory; everything below may read what the previous grid in the stream wrote
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) stamp(cta_traced ? p.trace : nullptr, 2, 30, 2);   // setup done
 
     // The four service roles are single chains of dependent instructions that share their scheduler with four arithmetic-dense softmax
@@ -934,8 +939,17 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
     if (items == 0 || items > 0xFFFFFFFFull) return cudaErrorInvalidValue;
     q.n_items = static_cast<uint32_t>(items);
     const uint32_t ctas = q.n_items < static_cast<uint32_t>(sm_count[dev]) ? q.n_items : static_cast<uint32_t>(sm_count[dev]);
-    kernels[which]<<<dim3(ctas, 1, 1), kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, q);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // overlap this grid's launch and set-up with the tail of the grid before it
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernels[which], tm_q, tm_k, tm_v, tm_o, q);
 }
 
 }  // namespace fmha
