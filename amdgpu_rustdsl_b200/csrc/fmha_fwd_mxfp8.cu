@@ -228,7 +228,7 @@ __device__ __forceinline__ Item decode_item(uint32_t w, const AttnParams& p) {
 // two score tiles overlap the current item's last tiles and epilogue; only O is single: P V of an item's first tile waits until the
 // epilogue of the item before has read O out (o_free).
 // kTrace = false compiles every diagnostic (tile dumps, time stamps) out of the tile loop: the production launches use that variant.
-template <bool kSplit, bool kTrace>
+template <bool kSplit, bool kTrace, bool kLazy>
 __global__ void __maxnreg__(kMaxRegs)
 fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const AttnParams p) {
@@ -260,10 +260,9 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t n_items = p.n_items, stride = gridDim.x;
-    // the recipe is chosen from the whole sequence's tile count, also in a split (block3.rs:180-184)
-    const uint32_t ntiles_total = (p.SK + kKeys - 1) / kKeys;
-    const bool lazy = (ntiles_total >= 4) && !(p.flags & 0x2u);
-    const float thr = lazy ? kLazyThreshold : -kFollowWindow;
+    // kLazy: the long-sequence recipe, chosen by the launcher from the whole sequence's tile count, also in a split (block3.rs:180-184)
+    constexpr bool lazy = kLazy;
+    constexpr float thr = lazy ? kLazyThreshold : -kFollowWindow;
     const bool cta_traced = kTrace && p.trace != nullptr && blockIdx.x == 0;   // diagnostics cover the first item of CTA 0 = logical block (0,0,0)
 
     // Programmatic dependent launch: the next launch in the stream (if it asks for it, as this library's own launches do) may be
@@ -631,7 +630,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     tmem_wait_ld();
                     tc_fence_before_sync();
                     mbar_arrive(bar_s_free(par));
-                    if (nvalid < kCols) {   // keys past the range: -inf for the maximum, 0 for P (crates/amdgpu-tile/src/reduce.rs:35-49)
+                    if (__builtin_expect(nvalid < kCols, 0)) {   // keys past the range: -inf for the maximum, 0 for P (crates/amdgpu-tile/src/reduce.rs:35-49)
 #pragma unroll
                         for (int c = 0; c < 128; ++c) {
                             if (c >= nvalid) v[c] = 0xFF800000u;
@@ -663,7 +662,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         uint32_t s[32];
                         tmem_ld32(t_s + 32 * ch, s);
                         tmem_wait_ld();
-                        if (nvalid < kCols) {
+                        if (__builtin_expect(nvalid < kCols, 0)) {
 #pragma unroll
                             for (int c = 0; c < 32; ++c) {
                                 if (c + 32 * ch >= nvalid) s[c] = 0xFF800000u;
@@ -708,7 +707,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 // the phase parity of the other parity's barrier below unambiguous)
                 if (!pv_seen && k > 0 && !mbar_wait(bar_o_done(par), (k - 1u) & 1u, abort_flag)) ok = false;
                 stamp(st_trace, par, static_cast<int>(g), 5);
-                if (j > 0 && __any_sync(0xFFFFFFFFu, move)) {
+                if (__builtin_expect(j > 0 && __any_sync(0xFFFFFFFFu, move), 0)) {
                     // O holds P V of all the item's tiles before j once the other parity's last P V is done; P V of tile j cannot start before this thread's arrive below
                     if (!mbar_wait(bar_o_done(par ^ 1u), ((g - 1u) >> 1) & 1u, abort_flag)) ok = false;
                     tc_fence_after_sync();
@@ -749,7 +748,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         tc_fence_before_sync();
                         mbar_arrive(bar_s_free(par));   // the score buffer can take tile g + 2 once all 256 threads of this parity are done with it
                     }
-                    if (nvalid < kCols) {
+                    if (__builtin_expect(nvalid < kCols, 0)) {
 #pragma unroll
                         for (int c = 0; c < 32; ++c) {
                             if (c + 32 * ch >= nvalid) s[c] = 0xFF800000u;
@@ -910,12 +909,17 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
                              uint32_t B, bool split, uint32_t rows_per_cta, cudaStream_t stream) {
     (void)rows_per_cta;   // both logical block heights run as 128-row CTAs
     using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
-    static const Kernel kernels[4] = {fmha_fwd_mxfp8_kernel<false, false>, fmha_fwd_mxfp8_kernel<true, false>,
-                                      fmha_fwd_mxfp8_kernel<false, true>, fmha_fwd_mxfp8_kernel<true, true>};
+    static const Kernel kernels[8] = {fmha_fwd_mxfp8_kernel<false, false, false>, fmha_fwd_mxfp8_kernel<true, false, false>,
+                                      fmha_fwd_mxfp8_kernel<false, true, false>,  fmha_fwd_mxfp8_kernel<true, true, false>,
+                                      fmha_fwd_mxfp8_kernel<false, false, true>,  fmha_fwd_mxfp8_kernel<true, false, true>,
+                                      fmha_fwd_mxfp8_kernel<false, true, true>,   fmha_fwd_mxfp8_kernel<true, true, true>};
     constexpr int kMaxDevices = 64;
-    static bool attr_done[kMaxDevices][4] = {};   // the shared-memory attribute is per device
+    static bool attr_done[kMaxDevices][8] = {};   // the shared-memory attribute is per device
     static int sm_count[kMaxDevices] = {};
-    const int which = (split ? 1 : 0) + (p.trace != nullptr ? 2 : 0);
+    // the long-sequence recipe from 4 key tiles of the whole sequence on (crates/amdgpu-stage/src/attention/state.rs:73-77), unless the
+    // caller asks for the exact one; each recipe is its own instantiation, which halves the code of the tile loop
+    const bool lazy_recipe = (p.SK + kKeys - 1) / kKeys >= 4 && !(p.flags & 0x2u);
+    const int which = (split ? 1 : 0) + (p.trace != nullptr ? 2 : 0) + (lazy_recipe ? 4 : 0);
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
