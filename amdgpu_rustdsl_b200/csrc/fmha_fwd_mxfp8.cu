@@ -826,6 +826,32 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
                     for (int c = 0; c < kOutCols; ++c) p.trace[16384 + r * 128 + kOutCols * wg + c] = __uint_as_float(o[c]);
                 }
+                if (kStagedOut && kSplit) {
+                    // The split kernel's f32 partial goes the same way as the bf16 output below: the warpgroup's 128 x 64 f32 tile in two
+                    // halves of 32 columns (128 bytes per row) through its 16 KB staging tile, one TMA store each.
+                    const uint32_t stg = smem_base + SmemLayout::ostage + wg * 16384u;
+                    const bool issuer = (st_id & 127u) == 0u;
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        if (n > 0 || hh > 0) {   // the previous store must have read the staging tile out
+                            if (issuer) bulk_wait_group_read0();
+                            named_bar_sync(1u + wg, 128u);
+                        }
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stg + r * 128u + ((static_cast<uint32_t>(c) ^ (r & 7u)) << 4)),
+                                         "f"(__uint_as_float(o[32 * hh + 4 * c]) * fin), "f"(__uint_as_float(o[32 * hh + 4 * c + 1]) * fin),
+                                         "f"(__uint_as_float(o[32 * hh + 4 * c + 2]) * fin), "f"(__uint_as_float(o[32 * hh + 4 * c + 3]) * fin) : "memory");
+                        }
+                        fence_proxy_async_smem();
+                        named_bar_sync(1u + wg, 128u);
+                        if (issuer) {
+                            tma_store_5d(&tm_o, stg, static_cast<int>(kOutCols * wg + 32 * hh), static_cast<int>(it.head), static_cast<int>(it.row0),
+                                         static_cast<int>(it.batch), static_cast<int>(it.split));
+                            bulk_commit_group();
+                        }
+                    }
+                }
                 if (kStagedOut && !kSplit) {
                     // A thread owns a row, so direct stores would touch 32 different lines per instruction. The warpgroup's 128 x 64 bf16
                     // tile goes through shared memory (128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8)) and out with
@@ -855,7 +881,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     }
                 }
                 if (row_ok) {
-                    if (kSplit) {
+                    if (kSplit && !kStagedOut) {
                         const size_t prow = static_cast<size_t>(it.split) * p.rows_total + (static_cast<size_t>(it.batch) * p.S + row) * p.H + it.head;
                         float4* dst = reinterpret_cast<float4*>(p.ohat + prow * 128 + kOutCols * wg);
 #pragma unroll
@@ -891,7 +917,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             stamp((cta_traced && r == 0 && half == 0) ? p.trace : nullptr, par, 24 + static_cast<int>(n), 6);
             g0 += static_cast<uint32_t>(n_tiles);
         }
-        if (kStagedOut && !kSplit && (st_id & 127u) == 0u) bulk_wait_group_read0();   // the staging tiles have been read out before the CTA gives its shared memory back
+        if (kStagedOut && (st_id & 127u) == 0u) bulk_wait_group_read0();   // the staging tiles have been read out before the CTA gives its shared memory back
     }
 
     // ---- teardown ----

@@ -180,6 +180,20 @@ int make_out_map(CUtensorMap* m, void* base, uint64_t seq, uint64_t heads, uint6
     return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r);
 }
 
+// The split kernel's f32 partials [splits][B*S*H rows][128] as a 5-D map (head dim, head, row, batch, split) with a 128-row x 32-column
+// box (128 bytes), 128-byte swizzle: half of one warpgroup's share of a partial tile.
+int make_partial_map(CUtensorMap* m, void* base, uint64_t seq, uint64_t heads, uint64_t batches, uint64_t splits) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return -static_cast<int>(cudaErrorSymbolNotFound);
+    const cuuint64_t dims[5] = {128, heads, seq, batches, splits};
+    const cuuint64_t strides[4] = {512, heads * 512, seq * heads * 512, batches * seq * heads * 512};
+    const cuuint32_t box[5] = {32, 1, 128, 1, 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r);
+}
+
 uint32_t log2_u32(uint32_t x) {
     uint32_t l = 0;
     while ((1u << l) < x) ++l;
@@ -236,11 +250,14 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
     if (r) return r;
     r = make_tile_map(&tv, a->ptr_v, p.SK, p.HK, B, a->s_v_Hs, a->s_v_Seqs, a->s_v_Bs);
     if (r) return r;
-    CUtensorMap to = tq;   // the split kernel writes f32 partials with plain stores and never looks at this map
+    CUtensorMap to;   // the output of the kernel's TMA stores: bf16 O, or the split kernel's f32 partials
     if (!split) {
         r = make_out_map(&to, a->ptr_o, p.S, p.H, B, a->s_o_Hs, a->s_o_Seqs, a->s_o_Bs);
-        if (r) return r;
+    } else {
+        if (static_cast<uint64_t>(p.rows_total) != static_cast<uint64_t>(B) * p.S * p.H) return FMHA_MXFP8_E_KA_IS;
+        r = make_partial_map(&to, p.ohat, p.S, p.H, B, p.splits);
     }
+    if (r) return r;
     const cudaError_t e = fmha::launch_attention(tq, tk, tv, to, p, B, split, kernel == FMHA_MXFP8_T128 ? 128u : 256u, stream);
     return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }
