@@ -7,8 +7,8 @@ The reference has no multi-GPU code; the two shardings below follow from the str
     No collective.
   * by key range: the KV-split algebra with "split = rank" (crates/amdgpu-stage/src/components.rs:58-74,
     crates/amdgpu-tile/src/epilogue.rs:117-146): every rank runs the split kernel over its local keys for all queries, the f32
-    partials (O, base-2 LSE) are exchanged once (all-gather: NCCL on GPUs, gloo in the CPU tests) into local memory, and the
-    combine kernel merges them with splits = world.
+    partials (O, base-2 LSE) are exchanged once into local memory (an all-to-all of row slices, or an all-gather of whole partials: NCCL on GPUs, gloo in the
+    CPU tests), and the combine kernel merges them with splits = world.
 `torch.distributed` is the plumbing; the kernels are the library's.
 """
 from __future__ import annotations
@@ -86,11 +86,48 @@ def exchange_partials(ohat, lse, ohat_all, lse_all, group=None):
     dist.all_gather_into_tensor(lse_all.view(-1), lse, group=group)
 
 
+def exchange_row_slices(ohat, lse, ohat_recv, lse_recv, group=None):
+    """The cheaper exchange of the key-range sharding: an all-to-all in which rank j receives, from every rank, only the partials of its
+    own 1/world slice of the rows: ohat [rows_total,128] -> ohat_recv [world, rows_total/world, 128] (rank-major = the [splits][rows]
+    layout the combine kernel reads), likewise the LSEs. (world-1)/world of one partial crosses the links per rank instead of world-1."""
+    import torch.distributed as dist
+    dist.all_to_all_single(ohat_recv.view(-1, ohat.shape[-1]), ohat, group=group)
+    dist.all_to_all_single(lse_recv.view(-1), lse, group=group)
+
+
+def gather_output_slices(out, out_slice, group=None):
+    """Every rank's combined bf16 row slice -> the whole output on every rank."""
+    import torch.distributed as dist
+    dist.all_gather_into_tensor(out.view(-1, out.shape[-1]), out_slice.view(-1, out.shape[-1]), group=group)
+
+
+def kv_sharded_workspace(rows_total: int, world: int, device, sliced: bool = True):
+    """Workspaces of `fmha_fwd_mxfp8_kv_sharded` for `rows_total` = B*S*H rows: the local partial, and either the row-slice buffers of the
+    all-to-all form (rows_total divisible by world) or the gathered partials of the all-gather form."""
+    import torch
+    ws = {"ohat": torch.empty(rows_total, D, dtype=torch.float32, device=device), "lse": torch.empty(rows_total, dtype=torch.float32, device=device)}
+    if sliced and rows_total % world == 0:
+        n = rows_total // world
+        ws["ohat_recv"] = torch.empty(world, n, D, dtype=torch.float32, device=device)
+        ws["lse_recv"] = torch.empty(world, n, dtype=torch.float32, device=device)
+        ws["out_slice"] = torch.empty(n, D, dtype=torch.bfloat16, device=device)
+    else:
+        ws["ohat_all"] = torch.empty(world, rows_total, D, dtype=torch.float32, device=device)
+        ws["lse_all"] = torch.empty(world, rows_total, dtype=torch.float32, device=device)
+    return ws
+
+
 def fmha_fwd_mxfp8_kv_sharded(q, k_local, v_local, q_scale, k_scale_local, v_scale, out, ws, group=None):
-    """Key-range-sharded forward on every rank of `group`: local partials -> all-gather -> combine. `ws` holds the caller's workspaces
-    {"ohat": f32 [rows_total,128], "lse": f32 [rows_total], "ohat_all": f32 [world,rows_total,128], "lse_all": f32 [world,rows_total]}."""
+    """Key-range-sharded forward on every rank of `group`. `ws` from `kv_sharded_workspace`. With row-slice buffers: local partials ->
+    all-to-all of row slices -> combine of the own slice -> all-gather of the bf16 slices; else: local partials -> all-gather of the
+    partials -> combine of all rows."""
     import torch.distributed as dist
     world = dist.get_world_size(group)
     local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ws["ohat"], ws["lse"])
+    if "ohat_recv" in ws:
+        exchange_row_slices(ws["ohat"], ws["lse"], ws["ohat_recv"], ws["lse_recv"], group)
+        combine_gathered(ws["ohat_recv"], ws["lse_recv"], ws["out_slice"], world)
+        gather_output_slices(out, ws["out_slice"], group)
+        return
     exchange_partials(ws["ohat"], ws["lse"], ws["ohat_all"], ws["lse_all"], group)
     combine_gathered(ws["ohat_all"], ws["lse_all"], out, world)

@@ -240,8 +240,7 @@ def main():
     rows_total = B * S * Hl
     ws = None
     if wl == "c5":
-        ws = {"ohat": torch.empty(rows_total, 128, dtype=torch.float32, device=dev), "lse": torch.empty(rows_total, dtype=torch.float32, device=dev),
-              "ohat_all": torch.empty(world, rows_total, 128, dtype=torch.float32, device=dev), "lse_all": torch.empty(world, rows_total, dtype=torch.float32, device=dev)}
+        ws = multi_gpu.kv_sharded_workspace(rows_total, world, dev)
     torch.cuda.synchronize()
 
     launches_per_step = 1
@@ -253,7 +252,7 @@ def main():
                 multi_gpu.fmha_fwd_mxfp8_kv_sharded(s["q"], s["k"], s["v"], s["qs"], s["ks"], s["vs"], s["out"], ws)
             else:
                 multi_gpu.local_partials(s["q"], s["k"], s["v"], s["qs"], s["ks"], s["vs"], ws["ohat"], ws["lse"], check=False)
-                multi_gpu.combine_gathered(ws["ohat"], ws["lse"], s["out"], 1, check=False)
+                multi_gpu.combine_gathered(ws["ohat"].view(1, rows_total, 128), ws["lse"].view(1, rows_total), s["out"], 1, check=False)
             ran["path"] = ("kvshard", world)
         else:
             ran["path"] = fmha_fwd_mxfp8(s["q"], s["k"], s["v"], s["qs"], s["ks"], s["vs"], s["out"], path=path, splits=splits)
@@ -332,7 +331,7 @@ def main():
             "scaling": scaling, "vs_baseline": None, "dtype": "fp8-e4m3 x E8M0 block scales (MXFP8), f32 accumulate, bf16 out", "data": "synthetic (seeded standard-normal Q/K/V quantised to MXFP8 on the host, the distribution of the reference harness's REF_DATA=normal)",
             "config": {"workload": f"{wl}: B{B} H{H} HK{HK} Sq{S} Skv{SK} hd128, non-causal" + (f", per rank (x{world} ranks)" if scaling == "weak" and world > 1 else ""),
                        "path": ran["path"][0], "splits": ran["path"][1], "l2": f"{nsets} rotating input/output sets of {bytes_per_set / 2**20:.0f} MiB (> 126 MB L2 in total)",
-                       "parallelism": "none" if world == 1 else ("batch x head shards, no collective" if wl != "c5" else "key-range shards + NCCL all-gather of partials + combine")},
+                       "parallelism": "none" if world == 1 else ("batch x head shards, no collective" if wl != "c5" else "key-range shards + NCCL all-to-all of partial row slices + combine + all-gather of the bf16 slices")},
             "roofline": roofline, "gpu_launches": K * launches_per_step, "device_status": status,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": Ke, "ms_per_step": ms_e2e / Ke},
             "clocks": clocks}

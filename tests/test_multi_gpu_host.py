@@ -86,6 +86,15 @@ def _rank_kv(rank, world, port, shape, q_out):
         # rank-major layout = [splits][rows_total], what the combine reads
         assert torch.equal(ohat_all[rank], t_ohat) and torch.equal(lse_all[rank], t_lse)
         out = orc.combine_f32(ohat_all.numpy(), lse_all.numpy(), rows_total, world)
+        # the all-to-all form: this rank receives and combines only its own slice of the rows, then the bf16 slices are gathered
+        n = rows_total // world
+        ohat_recv, lse_recv = torch.empty(world, n, 128), torch.empty(world, n)
+        multi_gpu.exchange_row_slices(t_ohat, t_lse, ohat_recv, lse_recv)
+        assert torch.equal(ohat_recv[rank], t_ohat[rank * n:(rank + 1) * n]) and torch.equal(lse_recv[rank], t_lse[rank * n:(rank + 1) * n])
+        mine = orc.combine_f32(ohat_recv.numpy(), lse_recv.numpy(), n, world)
+        out_sliced = torch.empty(rows_total, 128)   # gloo has no 16-bit integer gather: the bf16 values as f32
+        multi_gpu.gather_output_slices(out_sliced, torch.from_numpy(orc.bf16_to_f32(mine)))
+        assert np.array_equal(out_sliced.numpy(), orc.bf16_to_f32(out))      # both exchange forms give the same values
         ref = orc.reference(inp, S)
         st = orc.compare(inp, out.reshape(B, S, H, 128), ref, S)
         q_out.put((rank, st.bad, st.mean_err, st.worst_err, out.tobytes()))
