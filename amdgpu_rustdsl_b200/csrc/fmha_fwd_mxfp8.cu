@@ -34,6 +34,8 @@
 #include "ptx_sm100.cuh"
 
 #include <cuda_bf16.h>
+
+#include <type_traits>
 #include <cuda_fp8.h>
 
 namespace fmha {
@@ -608,7 +610,11 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const bool dumping = tracing && !(p.flags & 0x4u);   // flag 0x4: time stamps only, no tile dumps
             float ref = -INFINITY;   // the row's reference (log2 units) after the last tile this thread has seen
 
-            for (int j = static_cast<int>((g0 ^ par) & 1u); j < n_tiles; j += 2) {
+            // The tile body exists twice: the copy in the loop has no code for keys past the range; an item's ragged last tile, if this parity
+            // owns it, runs through a second copy placed behind the loop (instruction fetch is scarce enough with all SMs busy that even
+            // never-executed masking code inside the loop costs 3-4 %).
+            auto tile = [&](int j, auto masked_c) {
+                constexpr bool kMasked = decltype(masked_c)::value;
                 const uint32_t g = g0 + static_cast<uint32_t>(j);
                 const uint32_t k = g >> 1;   // this parity's tile counter
                 float* st_trace = (cta_traced && r == 0 && half == 0) ? p.trace : nullptr;
@@ -616,7 +622,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 if (!mbar_wait(bar_s_full(par), k & 1u, abort_flag)) ok = false;   // no divergent exit: a failed wait only clears `ok`, the vote after the tile loop ends the role
                 tc_fence_after_sync();
                 stamp(st_trace, par, static_cast<int>(g), 1);
-                const int nvalid = (j == n_tiles - 1) ? tail_valid : kCols;   // valid keys among this thread's kCols
+                const int nvalid = kMasked ? tail_valid : kCols;   // valid keys among this thread's kCols
                 float mt;
                 bool pv_seen = false;   // P V of this parity's previous tile is known to be done
 #if FMHA_SOFTMAX_HALVES == 1
@@ -630,7 +636,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     tmem_wait_ld();
                     tc_fence_before_sync();
                     mbar_arrive(bar_s_free(par));
-                    if (__builtin_expect(nvalid < kCols, 0)) {   // keys past the range: -inf for the maximum, 0 for P (crates/amdgpu-tile/src/reduce.rs:35-49)
+                    if (kMasked) {   // keys past the range: -inf for the maximum, 0 for P (crates/amdgpu-tile/src/reduce.rs:35-49)
 #pragma unroll
                         for (int c = 0; c < 128; ++c) {
                             if (c >= nvalid) v[c] = 0xFF800000u;
@@ -662,7 +668,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         uint32_t s[32];
                         tmem_ld32(t_s + 32 * ch, s);
                         tmem_wait_ld();
-                        if (__builtin_expect(nvalid < kCols, 0)) {
+                        if (kMasked) {
 #pragma unroll
                             for (int c = 0; c < 32; ++c) {
                                 if (c + 32 * ch >= nvalid) s[c] = 0xFF800000u;
@@ -748,7 +754,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         tc_fence_before_sync();
                         mbar_arrive(bar_s_free(par));   // the score buffer can take tile g + 2 once all 256 threads of this parity are done with it
                     }
-                    if (__builtin_expect(nvalid < kCols, 0)) {
+                    if (kMasked) {
 #pragma unroll
                         for (int c = 0; c < 32; ++c) {
                             if (c + 32 * ch >= nvalid) s[c] = 0xFF800000u;
@@ -780,7 +786,11 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 tc_fence_before_sync();
                 mbar_arrive(bar_p_full(par));
                 stamp(st_trace, par, static_cast<int>(g), 7);
-            }
+            };
+            const bool ragged = tail_valid < kCols;
+            const int j_full = ragged ? n_tiles - 1 : n_tiles;   // tiles [0, j_full) have all their keys
+            for (int j = static_cast<int>((g0 ^ par) & 1u); j < j_full; j += 2) tile(j, std::false_type{});
+            if (ragged && ((g0 + static_cast<uint32_t>(n_tiles) - 1u) & 1u) == par) tile(n_tiles - 1, std::true_type{});
             if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
 
             // ---- epilogue: O * v_descale / l; warpgroup wg stores head dims [kOutCols wg, kOutCols wg + kOutCols) ----

@@ -445,7 +445,7 @@ int fmha_mxfp8_trace_attach(void* dev_buf, size_t bytes) {
 }
 
 int fmha_mxfp8_probe_mma_peak(int variant, int iters, int ctas, void* stream, float* ms) {
-    if (variant < 0 || variant > 8 || iters < 1 || ctas < 1 || !ms) return FMHA_MXFP8_E_ARG;
+    if (variant < 0 || variant > 12 || iters < 1 || ctas < 1 || !ms) return FMHA_MXFP8_E_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint32_t* status = fmha::device_status_word();
     if (!status) return -static_cast<int>(cudaErrorInvalidSymbol);

@@ -54,6 +54,46 @@ __global__ void __launch_bounds__(128, 1) mma_probe_kernel(int variant, int iter
         const uint32_t id_bs = idesc_mxf8_block_scaled(128, 128, 0, 0, 0, 0);
         const uint32_t id_bs_mn = idesc_mxf8_block_scaled(128, 128, 0, 1, 0, 0);
         const uint32_t id_f8_mn = idesc_f8_dense(128, 128, 0, 1);
+        if (variant >= 9 && variant <= 12) {
+            // Tight loops with every descriptor prepared up front, to separate the hardware's cost per instruction from loop overhead:
+            // 9 = four dependent MMAs per tile, tiles alternate between two accumulators (what the kernels' Q K^T stream does);
+            // 10 = the same work with the two accumulators interleaved MMA by MMA (two independent chains in flight);
+            // 11 = one accumulator throughout (one long dependent chain, what the P V stream is); 12 = like 9 with N = 144 from tensor memory.
+            uint64_t da[4], db[4], dv[4];
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
+                da[kb] = make_smem_desc(a_smem + kb * 32, 16, 1024, kSwizzle128B);
+                db[kb] = make_smem_desc(b_smem + kb * 32, 16, 1024, kSwizzle128B);
+                dv[kb] = make_smem_desc(b_smem + (kb & 1) * 4096, 1024, 1024, kSwizzle128B);
+            }
+            const uint32_t id = idesc_f8_dense(128, 128, 0, 0), id_pv = idesc_f8_dense(128, 144, 0, 1);
+            if (variant == 9) {
+                for (int it = 0; it < iters; it += 2) {
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) mma_f8_ss(tmem, da[kb], db[kb], id, kb > 0);
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) mma_f8_ss(tmem + 128, da[kb], db[kb], id, kb > 0);
+                }
+            } else if (variant == 10) {
+                for (int it = 0; it < iters; it += 2) {
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) {
+                        mma_f8_ss(tmem, da[kb], db[kb], id, kb > 0);
+                        mma_f8_ss(tmem + 128, da[kb], db[kb], id, kb > 0);
+                    }
+                }
+            } else if (variant == 11) {
+                for (int it = 0; it < iters; ++it) {
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) mma_f8_ss(tmem, da[kb], db[kb], id, 1u);
+                }
+            } else {
+                for (int it = 0; it < iters; ++it) {
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) mma_f8_ts(tmem, tmem + 256 + 8 * kb, dv[kb], id_pv, 1u);
+                }
+            }
+        } else
         for (int it = 0; it < iters; ++it) {
             const uint32_t d = tmem + ((it & 1) ? 128u : 0u);
 #pragma unroll
