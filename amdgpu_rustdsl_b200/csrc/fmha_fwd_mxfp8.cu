@@ -20,15 +20,15 @@
 //   warp  2    P V issuer: O += P_g V_g with P from TMEM and V (keys x head dim, i.e. MN-major B) from shared memory. The B operand
 //              is 144 wide: 128 head dims plus 16 columns of a tile of e4m3 ones, so that O[:, 128..143] (= the L columns) holds the
 //              row sums of the *quantised* P at no ALU cost (the reference sums P with a matrix instruction too, reduce.rs:163-173).
-//              A second issuing thread matters: one thread issues an MMA about every 75 clocks whatever its N.
+//              It has a thread of its own: the tensor pipe takes MMAs from one thread at its full rate, but a thread that shares its
+//              scheduler with softmax warps only gets an instruction in every few clocks.
 //   warp  3    V producer: TMA loads of the V ring (K is freed after Q K^T, V after P V, so the two rings run apart).
-//   warps 4-11 softmax + epilogue, two warpgroups (the default layout, FMHA_SOFTMAX_HALVES = 1): warpgroup p works on the tiles with
+//   warps 4-11 softmax + epilogue, two warpgroups: warpgroup p works on the tiles with
 //              counter g = p (mod 2). Thread r of a group owns query row r = TMEM lane r: it reads the row's 128 scores with one
 //              tensor-memory round trip and hands the S buffer back at once, takes the row's reference from the group of the previous
 //              tile through an 8-byte shared-memory slot {value, tile counter}, converts in place, writes P (packed e4m3) with
 //              tcgen05.st, and rescales O in TMEM on the rare tiles that move the reference. 12 warps = 168 registers per thread.
 //              The output tile leaves through shared memory and one TMA store per warpgroup.
-//              (FMHA_SOFTMAX_HALVES = 2 is the four-warpgroup layout, half a row per thread in two passes at 96 registers.)
 // TMEM columns: S0 [0,128) S1 [128,256) O [256,384) L [384,400) P0 [400,432) P1 [432,464) SFQ [464,468) SFK0 [468,472) SFK1 [472,476).
 #include "kernels.h"
 #include "ptx_sm100.cuh"
@@ -49,16 +49,11 @@ constexpr int kStages = 4;          // depth of the K ring and of the V ring (fr
 // The four service warps get the lowest warp ids, one per scheduler (scheduler = warp % 4). Softmax = warps 4-19: a warp's TMEM lane
 // quadrant is warp % 4, so any four consecutive warps cover the 128 rows.
 constexpr int kMmaWarp = 0, kKProducerWarp = 1, kPvWarp = 2, kVProducerWarp = 3, kFirstSoftmaxWarp = 4;
-// Softmax layout: kHalves = 1: two warpgroups, a thread owns a whole score row of a tile (128 scores in registers, read once; 12 warps,
-// 168 registers per thread). kHalves = 2: four warpgroups, a thread owns half a row (two passes over tensor memory; 20 warps, 96 registers).
-#ifndef FMHA_SOFTMAX_HALVES
-#define FMHA_SOFTMAX_HALVES 1
-#endif
-constexpr int kHalves = FMHA_SOFTMAX_HALVES;
-constexpr int kCols = 128 / kHalves;                   // score columns per softmax thread
-constexpr int kThreads = 32 * (4 + 8 * kHalves);       // the register file is 16 K registers per scheduler: 3 warps x 168 or 5 warps x 96
-constexpr int kMaxRegs = kHalves == 1 ? 168 : 96;
-constexpr bool kStagedOut = kHalves == 1;   // bf16 output through shared memory and TMA stores (whole-row layout: 64 columns per warpgroup)
+// A softmax thread owns a whole score row of a tile: 128 scores in registers, read from tensor memory once. 4 service + 8 softmax warps;
+// the register file is 16 K registers per scheduler, so three warps per scheduler get 168 registers each.
+constexpr int kCols = 128;                  // score columns per softmax thread
+constexpr int kThreads = 32 * (4 + 8);
+constexpr int kMaxRegs = 168;
 constexpr uint32_t kTileBytes = 128 * 128;   // one e4m3 tile
 constexpr uint32_t kSfBytes = 512;           // 128 rows x 4 scale bytes
 
@@ -89,9 +84,8 @@ struct SmemLayout {
     static constexpr uint32_t ostage = ones + 4096;
     static constexpr uint32_t sfq = ostage + 2 * 16384;
     static constexpr uint32_t sfk = sfq + 2 * kSfBytes;
-    static constexpr uint32_t xref = sfk + kStages * kSfBytes;   // [tile parity 2][half 2][row 128] x {reference bits, tile index}
-    static constexpr uint32_t xmax = xref + 2 * 2 * 128 * 8;     // [buffer 2][tile parity 2][half 2][row 128] x {half-row maximum bits, tile index}
-    static constexpr uint32_t bars = xmax + 2 * 2 * 2 * 128 * 8;
+    static constexpr uint32_t xref = sfk + kStages * kSfBytes;   // [tile parity 2][row 128] x {reference bits, tile counter}
+    static constexpr uint32_t bars = xref + 2 * 128 * 8;
     // barriers (8 bytes each): q_full[2], q_empty[2], k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], s_free[2],
     // p_full[2], o_done[2], o_free
     static constexpr uint32_t n_bars = 4 + 4 * kStages + 9;
@@ -278,8 +272,8 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             mbar_init(bar_q_full(b), 2);   // the TMA's expect-tx arrive + the arrive that follows the scale bytes
             mbar_init(bar_q_empty(b), 1);
             mbar_init(bar_s_full(b), 1);
-            mbar_init(bar_s_free(b), kHalves * kRows);
-            mbar_init(bar_p_full(b), kHalves * kRows);
+            mbar_init(bar_s_free(b), kRows);
+            mbar_init(bar_p_full(b), kRows);
             mbar_init(bar_o_done(b), 1);
         }
         for (int st = 0; st < kStages; ++st) {
@@ -288,13 +282,13 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             mbar_init(bar_v_full(st), 1);
             mbar_init(bar_v_empty(st), 1);
         }
-        mbar_init(bar_o_free, 2 * kHalves * kRows);
+        mbar_init(bar_o_free, 2 * kRows);
         fence_mbar_init();
     }
     if (threadIdx.x < 256) {
         for (int i = 0; i < 4; ++i) reinterpret_cast<uint32_t*>(smem_gen + SmemLayout::ones)[threadIdx.x + 256 * i] = 0x38383838u;
-        // hand-over slots (512 reference slots, then 1024 maximum slots) start with a tile counter no tile has
-        for (int i = 0; i < 6; ++i) reinterpret_cast<uint2*>(smem_gen + SmemLayout::xref)[threadIdx.x + 256 * i] = make_uint2(0u, 0xFFFFFFFFu);
+        // the 256 reference hand-over slots start with a tile counter no tile has
+        reinterpret_cast<uint2*>(smem_gen + SmemLayout::xref)[threadIdx.x] = make_uint2(0u, 0xFFFFFFFFu);
         fence_proxy_async_smem();
     }
     if (warp == kMmaWarp) {
@@ -471,9 +465,8 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         __syncwarp();
     } else if (warp == kMmaWarp) {
         // =========================================================== MMA issuer: score tiles ===========================================================
-        // One lane runs the role. A tcgen05.mma costs its issuing thread about as long as the tensor pipe needs for a 128 x 128 x 32
-        // tile, so Q K^T and P V are issued by two different threads (this warp and kPvWarp): their streams share no operand, and the
-        // pipe interleaves them. Descriptors are prepared once.
+        // One lane runs the role. Q K^T and P V are issued by two different threads (this warp and kPvWarp): their streams share no
+        // operand, the pipe interleaves them, and neither thread's instruction stream holds the other up. Descriptors are prepared once.
         if (lane == 0) {
             const uint32_t idesc_qk = idesc_mxf8_block_scaled(128, 128, 0, 0, 0, 0);
             const uint32_t t_sfq = tmem + kColSfQ;
@@ -563,18 +556,16 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         __syncwarp();
     } else if (warp >= kFirstSoftmaxWarp) {
         // =========================================================== softmax + epilogue ===========================================================
-        // 2 * kHalves warpgroups: wg = 2 * half + parity. Parity = which tiles (counter g = parity mod 2) and which S / P buffer; half =
-        // which kCols key columns of the tile. Thread r of a group owns query row r.
+        // Two warpgroups: wg = parity = which tiles (counter g = parity mod 2) and which S / P buffer. Thread r of a group owns query row r.
         const uint32_t st_id = threadIdx.x - 32u * kFirstSoftmaxWarp;
         const uint32_t wg = st_id >> 7;
-        const uint32_t par = wg & 1u, half = wg >> 1;
+        const uint32_t par = wg;
         const uint32_t r = 32u * (static_cast<uint32_t>(warp) & 3u) + static_cast<uint32_t>(lane);   // TMEM lane = 32 * (warp % 4) + lane
         const uint32_t lane_base = (static_cast<uint32_t>(warp & 3) * 32u) << 16;
         const uint32_t xref = smem_base + SmemLayout::xref;   // 8-byte slots, accessed with single 64-bit shared loads / stores
-        const uint32_t xmax = smem_base + SmemLayout::xmax;
-        const uint32_t t_s = tmem + (par ? kColS1 : kColS0) + lane_base + kCols * half;
-        const uint32_t t_p = tmem + (par ? kColP1 : kColP0) + lane_base + (kCols / 4) * half;
-        const uint32_t t_o_part = tmem + kColO + lane_base + kCols * half;
+        const uint32_t t_s = tmem + (par ? kColS1 : kColS0) + lane_base;
+        const uint32_t t_p = tmem + (par ? kColP1 : kColP0) + lane_base;
+        const uint32_t t_o_part = tmem + kColO + lane_base;
         const uint32_t t_l = tmem + kColL + lane_base;
         bool ok = true;
 
@@ -592,10 +583,8 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             out = __uint_as_float(o.x);
             return true;
         };
-        // the reference the row has after tile g: published by every thread of the row that handled tile g, read from the same half
-        auto ref_slot = [&](uint32_t g) { return xref + 8u * (((g & 1u) * 2u + half) * 128u + r); };
-        // the half-row maximum of tile g (kHalves = 2): double buffered over this parity's consecutive tiles
-        auto max_slot = [&](uint32_t g, uint32_t h) { return xmax + 8u * (((((g >> 1) & 1u) * 2u + par) * 2u + h) * 128u + r); };
+        // the reference the row has after tile g, published by the thread that handled it
+        auto ref_slot = [&](uint32_t g) { return xref + 8u * ((g & 1u) * 128u + r); };
 
         uint32_t g0 = 0, n = 0;   // tile counter at the item's first tile; ordinal of the item
         for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
@@ -604,104 +593,62 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             {
                 const Item it = decode_item<kSplit>(w, p);
                 n_tiles = it.n_tiles;
-                tail_valid = static_cast<int>(it.key_hi - it.key_lo) - (n_tiles - 1) * kKeys - kCols * static_cast<int>(half);
+                tail_valid = static_cast<int>(it.key_hi - it.key_lo) - (n_tiles - 1) * kKeys;
             }
             const bool tracing = cta_traced && n == 0;
             const bool dumping = tracing && !(p.flags & 0x4u);   // flag 0x4: time stamps only, no tile dumps
             float ref = -INFINITY;   // the row's reference (log2 units) after the last tile this thread has seen
 
             // The tile body exists twice: the copy in the loop has no code for keys past the range; an item's ragged last tile, if this parity
-            // owns it, runs through a second copy placed behind the loop (instruction fetch is scarce enough with all SMs busy that even
-            // never-executed masking code inside the loop costs 3-4 %).
+            // owns it, runs through a second copy placed behind the loop (with all SMs busy, instruction fetch is scarce enough that even
+            // never-executed masking code inside the loop costs 3-4 %; moving the rare rescale out of the loop the same way did not pay).
             auto tile = [&](int j, auto masked_c) {
+                uint32_t v[128];   // the row's scores, converted in place below
+                float f = 1.0f;    // factor of a rescale
+                bool pv_seen = false;   // P V of this parity's previous tile is known to be done
                 constexpr bool kMasked = decltype(masked_c)::value;
                 const uint32_t g = g0 + static_cast<uint32_t>(j);
                 const uint32_t k = g >> 1;   // this parity's tile counter
-                float* st_trace = (cta_traced && r == 0 && half == 0) ? p.trace : nullptr;
+                float* st_trace = (cta_traced && r == 0) ? p.trace : nullptr;
                 stamp(st_trace, par, static_cast<int>(g), 0);
                 if (!mbar_wait(bar_s_full(par), k & 1u, abort_flag)) ok = false;   // no divergent exit: a failed wait only clears `ok`, the vote after the tile loop ends the role
                 tc_fence_after_sync();
                 stamp(st_trace, par, static_cast<int>(g), 1);
-                const int nvalid = kMasked ? tail_valid : kCols;   // valid keys among this thread's kCols
-                float mt;
-                bool pv_seen = false;   // P V of this parity's previous tile is known to be done
-#if FMHA_SOFTMAX_HALVES == 1
                 // All 128 scores of the row in registers with one tensor-memory round trip; the score buffer is handed back at once, so
                 // that Q K^T of tile g + 2 runs under this tile's conversion. The scores are converted in place further down.
-                uint32_t v[128];
-                {
 #pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) tmem_ld32(t_s + 32 * ch, *reinterpret_cast<uint32_t(*)[32]>(&v[32 * ch]));
-                    pv_seen = k == 0 || mbar_test_wait(bar_o_done(par), (k - 1u) & 1u);   // probed under the tensor-memory round trip
-                    tmem_wait_ld();
-                    tc_fence_before_sync();
-                    mbar_arrive(bar_s_free(par));
-                    if (kMasked) {   // keys past the range: -inf for the maximum, 0 for P (crates/amdgpu-tile/src/reduce.rs:35-49)
+                for (int ch = 0; ch < 4; ++ch) tmem_ld32(t_s + 32 * ch, *reinterpret_cast<uint32_t(*)[32]>(&v[32 * ch]));
+                pv_seen = k == 0 || mbar_test_wait(bar_o_done(par), (k - 1u) & 1u);   // probed under the tensor-memory round trip
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                mbar_arrive(bar_s_free(par));
+                if (kMasked) {   // keys past the range: -inf for the maximum, 0 for P (crates/amdgpu-tile/src/reduce.rs:35-49)
 #pragma unroll
-                        for (int c = 0; c < 128; ++c) {
-                            if (c >= nvalid) v[c] = 0xFF800000u;
-                        }
+                    for (int c = 0; c < 128; ++c) {
+                        if (c >= tail_valid) v[c] = 0xFF800000u;
                     }
-                    if (dumping && j == 0) {
-#pragma unroll
-                        for (int c = 0; c < 128; ++c) p.trace[r * 128 + c] = __uint_as_float(v[c]);
-                    }
-                    float m[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) m[i] = -INFINITY;
-#pragma unroll
-                    for (int c = 0; c < 128; c += 16) {   // eight independent chains of three-input maxima
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) m[i] = max3(m[i], __uint_as_float(v[c + 2 * i]), __uint_as_float(v[c + 2 * i + 1]));
-                    }
-                    mt = fmaxf(fmaxf(max3(m[0], m[1], m[2]), max3(m[3], m[4], m[5])), fmaxf(m[6], m[7]));
-                    stamp(st_trace, par, static_cast<int>(g), 2);
-                    stamp(st_trace, par, static_cast<int>(g), 3);
                 }
-#else
-                {
-                    // Pass 1 over the 64 scores of this half row, 32 at a time: the maximum only. The scores are read again for the conversion
-                    // below instead of being kept, which keeps a softmax thread under 96 registers (20 warps share the register file).
-                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-#pragma unroll 1
-                    for (int ch = 0; ch < 2; ++ch) {
-                        uint32_t s[32];
-                        tmem_ld32(t_s + 32 * ch, s);
-                        tmem_wait_ld();
-                        if (kMasked) {
+                if (dumping && j == 0) {
 #pragma unroll
-                            for (int c = 0; c < 32; ++c) {
-                                if (c + 32 * ch >= nvalid) s[c] = 0xFF800000u;
-                            }
-                        }
-                        if (dumping && j == 0) {
-#pragma unroll
-                            for (int c = 0; c < 32; ++c) p.trace[r * 128 + 64 * half + 32 * ch + c] = __uint_as_float(s[c]);
-                        }
-#pragma unroll
-                        for (int c = 0; c < 32; c += 8) {   // four independent chains of three-input maxima
-                            m0 = max3(m0, __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
-                            m1 = max3(m1, __uint_as_float(s[c + 2]), __uint_as_float(s[c + 3]));
-                            m2 = max3(m2, __uint_as_float(s[c + 4]), __uint_as_float(s[c + 5]));
-                            m3 = max3(m3, __uint_as_float(s[c + 6]), __uint_as_float(s[c + 7]));
-                        }
-                    }
-                    mt = fmaxf(max3(m0, m1, m2), m3);
-                    stamp(st_trace, par, static_cast<int>(g), 2);
-                    // exchange the half-row maxima with the thread that holds the other 64 keys of this row
-                    st_shared_v2(max_slot(g, half), __float_as_uint(mt), g);
-                    stamp(st_trace, par, static_cast<int>(g), 3);
-                    float other = mt;
-                    if (!wait_slot(max_slot(g, half ^ 1u), g, other)) ok = false;
-                    mt = fmaxf(mt, other);
+                    for (int c = 0; c < 128; ++c) p.trace[r * 128 + c] = __uint_as_float(v[c]);
                 }
-#endif
-                // take over the row's reference from the threads that handled the item's previous tile
+                float m[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) m[i] = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 128; c += 16) {   // eight independent chains of three-input maxima
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) m[i] = max3(m[i], __uint_as_float(v[c + 2 * i]), __uint_as_float(v[c + 2 * i + 1]));
+                }
+                const float mt = fmaxf(fmaxf(max3(m[0], m[1], m[2]), max3(m[3], m[4], m[5])), fmaxf(m[6], m[7]));
+                stamp(st_trace, par, static_cast<int>(g), 2);
+                stamp(st_trace, par, static_cast<int>(g), 3);
+                // take over the row's reference from the thread that handled the item's previous tile
                 if (ok && j > 0 && !wait_slot(ref_slot(g - 1u), g - 1u, ref)) ok = false;
                 // the reference moves when this tile's maximum passes it by more than the threshold (negative for short sequences: it then
-                // also follows the tile maximum down, and f > 1 scales O and L up). All threads of a row see the same mt and ref.
+                // also follows the tile maximum down, and f > 1 scales O and L up)
                 const bool move = mt > ref + thr;
-                float f = 1.0f;
+                f = 1.0f;
                 if (move) {
                     const float nref = lazy ? ceilf(mt) : mt;
                     f = ex2_approx(ref - nref);   // 0 on the first tile (ref = -inf); an exact power of two for integer references
@@ -717,9 +664,9 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     // O holds P V of all the item's tiles before j once the other parity's last P V is done; P V of tile j cannot start before this thread's arrive below
                     if (!mbar_wait(bar_o_done(par ^ 1u), ((g - 1u) >> 1) & 1u, abort_flag)) ok = false;
                     tc_fence_after_sync();
-#pragma unroll 1
+    #pragma unroll 1
                     for (int c = 0; c < kCols / 32; ++c) scale_tmem32(t_o_part + 32 * c, f);
-                    if (half == 0) {   // the row sum lives in column 0 of L
+                    {   // the row sum lives in column 0 of L
                         uint32_t lv;
                         asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(lv) : "r"(t_l) : "memory");
                         tmem_wait_ld();
@@ -732,7 +679,6 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 const float sh = kPOffset - ref;
                 const float cf = (kPOffset + 7.0f - kFastBias - ref) * 0.03125f;
                 uint32_t pw[kCols / 4];
-#if FMHA_SOFTMAX_HALVES == 1
                 if (lazy) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
@@ -744,44 +690,12 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
                     for (int c = 0; c < 32; ++c) pw[c] = p_word(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3], sh);
                 }
-#else
-#pragma unroll
-                for (int ch = 0; ch < 2; ++ch) {
-                    uint32_t s[32];
-                    tmem_ld32(t_s + 32 * ch, s);
-                    tmem_wait_ld();
-                    if (ch == 1) {
-                        tc_fence_before_sync();
-                        mbar_arrive(bar_s_free(par));   // the score buffer can take tile g + 2 once all 256 threads of this parity are done with it
-                    }
-                    if (kMasked) {
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) {
-                            if (c + 32 * ch >= nvalid) s[c] = 0xFF800000u;
-                        }
-                    }
-                    if (lazy) {
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            pw[8 * ch + c] = (c % kMufuEvery == 0) ? p_word_hybrid(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], sh, cf)
-                                                                   : p_word_fast(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], cf);
-                        }
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) pw[8 * ch + c] = p_word(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3], sh);
-                    }
-                }
-#endif
                 if (dumping && j == 0) {
 #pragma unroll
-                    for (int c = 0; c < kCols / 4; ++c) reinterpret_cast<uint32_t*>(p.trace)[32768 + 256 + r * 32 + (kCols / 4) * half + c] = pw[c];
+                    for (int c = 0; c < kCols / 4; ++c) reinterpret_cast<uint32_t*>(p.trace)[32768 + 256 + r * 32 + c] = pw[c];
                 }
                 stamp(st_trace, par, static_cast<int>(g), 6);
-#if FMHA_SOFTMAX_HALVES == 1
                 tmem_st32(t_p, pw);
-#else
-                tmem_st16(t_p, pw);
-#endif
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(bar_p_full(par));
@@ -795,9 +709,9 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
             // ---- epilogue: O * v_descale / l; warpgroup wg stores head dims [kOutCols wg, kOutCols wg + kOutCols) ----
             {
-                constexpr int kOutCols = 128 / (2 * kHalves);
+                constexpr int kOutCols = 64;
                 const float vd = __ldg(p.v_descale);   // issued ahead of the waits below
-                float* ep_trace = (cta_traced && r == 0 && half == 0) ? p.trace : nullptr;   // epilogue stamps: tile index 24 + item ordinal
+                float* ep_trace = (cta_traced && r == 0) ? p.trace : nullptr;   // epilogue stamps: tile index 24 + item ordinal
                 stamp(ep_trace, par, 24 + static_cast<int>(n), 0);
                 const uint32_t g_last = g0 + static_cast<uint32_t>(n_tiles) - 1u;
                 // this parity's last tile of the item first (its barrier is observed phase by phase), then the other parity's
@@ -836,7 +750,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
                     for (int c = 0; c < kOutCols; ++c) p.trace[16384 + r * 128 + kOutCols * wg + c] = __uint_as_float(o[c]);
                 }
-                if (kStagedOut && kSplit) {
+                if (kSplit) {
                     // The split kernel's f32 partial goes the same way as the bf16 output below: the warpgroup's 128 x 64 f32 tile in two
                     // halves of 32 columns (128 bytes per row) through its 16 KB staging tile, one TMA store each.
                     const uint32_t stg = smem_base + SmemLayout::ostage + wg * 16384u;
@@ -862,7 +776,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         }
                     }
                 }
-                if (kStagedOut && !kSplit) {
+                if (!kSplit) {
                     // A thread owns a row, so direct stores would touch 32 different lines per instruction. The warpgroup's 128 x 64 bf16
                     // tile goes through shared memory (128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8)) and out with
                     // one TMA store, which also leaves out the rows past the sequence.
@@ -891,28 +805,6 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     }
                 }
                 if (row_ok) {
-                    if (kSplit && !kStagedOut) {
-                        const size_t prow = static_cast<size_t>(it.split) * p.rows_total + (static_cast<size_t>(it.batch) * p.S + row) * p.H + it.head;
-                        float4* dst = reinterpret_cast<float4*>(p.ohat + prow * 128 + kOutCols * wg);
-#pragma unroll
-                        for (int c = 0; c < kOutCols / 4; ++c) {
-                            dst[c] = make_float4(__uint_as_float(o[4 * c]) * fin, __uint_as_float(o[4 * c + 1]) * fin,
-                                                 __uint_as_float(o[4 * c + 2]) * fin, __uint_as_float(o[4 * c + 3]) * fin);
-                        }
-                    } else if (!kStagedOut) {
-                        uint8_t* orow = p.o + static_cast<size_t>(it.batch) * p.o_batch_stride + static_cast<size_t>(row) * p.o_row_stride + it.head * 256u;
-                        uint4* dst = reinterpret_cast<uint4*>(orow + 2 * kOutCols * wg);
-#pragma unroll
-                        for (int c = 0; c < kOutCols / 8; ++c) {
-                            uint32_t wv[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[8 * c + 2 * e]) * fin, __uint_as_float(o[8 * c + 2 * e + 1]) * fin);
-                                wv[e] = *reinterpret_cast<const uint32_t*>(&b2);
-                            }
-                            dst[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-                        }
-                    }
                     if (wg == 0) {
                         const float lse2 = ref - kPOffset + lg2_approx(l);   // log2 of sum_j 2^(s_j)
                         if (kSplit) {
@@ -924,10 +816,10 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     }
                 }
             }
-            stamp((cta_traced && r == 0 && half == 0) ? p.trace : nullptr, par, 24 + static_cast<int>(n), 6);
+            stamp((cta_traced && r == 0) ? p.trace : nullptr, par, 24 + static_cast<int>(n), 6);
             g0 += static_cast<uint32_t>(n_tiles);
         }
-        if (kStagedOut && (st_id & 127u) == 0u) bulk_wait_group_read0();   // the staging tiles have been read out before the CTA gives its shared memory back
+        if ((st_id & 127u) == 0u) bulk_wait_group_read0();   // the staging tiles have been read out before the CTA gives its shared memory back
     }
 
     // ---- teardown ----

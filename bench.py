@@ -318,13 +318,13 @@ def main():
                 "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(wl) if world == 1 else None, "traffic_unit": "bytes per launch (ncu, DRAM read + write)",
                 "algorithmic_bytes": B * Hl * S * (128 + 4 + 256) + 2 * B * HKl * SKl * 128 + B * HKl * SKl * 4, "peak_source": peak_src,
                 "frac_of_nominal_4500": achieved / NOMINAL_MXFP8_TFLOPS, "note": "achieved = 4*B*H*Sq*Skv*128 per launch / mean step time (CUDA events); for kvsplit steps the combine launch is inside the step"}
-    # issue-only ceiling of the tensor pipe, measured now: two issuing threads per SM (N = 256 and N = 128 fp8 MMAs, K = 32), no data movement
+    # issue-only ceiling of the tensor pipe, measured now: one thread per SM issues M128 N128 K32 fp8 MMAs on resident operands in a tight loop
     try:
         import ctypes as C
         ms = C.c_float(0)
         lib = _abi.load()
-        if lib.fmha_mxfp8_probe_mma_peak(8, 4000, 148, None, C.byref(ms)) == 0 and ms.value > 0:
-            roofline["mma_issue_ceiling_tflops"] = 148 * 4000 * 4 * 2.0 * 128 * (256 + 128) * 32 / (ms.value * 1e-3) / 1e12
+        if lib.fmha_mxfp8_probe_mma_peak(9, 8000, 148, None, C.byref(ms)) == 0 and ms.value > 0:
+            roofline["mma_issue_ceiling_tflops"] = 148 * 8000 * 4 * 2.0 * 128 * 128 * 32 / (ms.value * 1e-3) / 1e12
     except Exception:
         pass
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True,

@@ -309,7 +309,11 @@ int fmha_mxfp8_trace_attach(void* dev_buf, size_t bytes);
  * Issue-only ceiling of the tensor pipe: every CTA issues `iters` x 4 tcgen05.mma (M128 N128 K32, e4m3) back to back on resident
  * operands. variant 0 = block-scaled, A from shared memory; 1 = block-scaled, A from tensor memory, B MN-major; 2 = kind::f8f6f4, A
  * from tensor memory, B MN-major; 3 = f8f6f4, A from shared memory, B MN-major; 4 = f8f6f4, A from tensor memory, B K-major;
- * 5 = f8f6f4, both from shared memory, K-major; 6 = the N16 row-sum MMA (counted as if it were N128). Writes the elapsed milliseconds (CUDA events on `stream`) and returns 0. Used for the roofline denominator.
+ * 5 = f8f6f4, both from shared memory, K-major; 6 = the N16 row-sum MMA (counted as if it were N128); 7, 8 = N256 with one / two issuing
+ * threads. Variants 0-8 rebuild their descriptors inside the loop and so measure that overhead too. 9-12 are tight loops on prepared
+ * operands (f8f6f4): 9 = four dependent MMAs per tile, tiles alternating between two accumulators; 10 = the two accumulators interleaved;
+ * 11 = one accumulator throughout; 12 = A from tensor memory, N144 (the P V shape). Writes the elapsed milliseconds (CUDA events on
+ * `stream`) and returns 0. Variant 9 is the roofline's issue ceiling.
  */
 int fmha_mxfp8_probe_mma_peak(int variant, int iters, int ctas, void* stream, float* ms);
 
