@@ -262,14 +262,18 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, nwarm, nsteps):
+    def timed(fn, nwarm, nsteps, join=None):
         for i in range(nwarm):
             fn(i)
+        if join:
+            join()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(nsteps):
             fn(nwarm + i)
+        if join:
+            join()   # the launching stream waits for the copy streams: the end event covers the last read-back
         e1.record()
         barrier()
         ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
@@ -287,15 +291,38 @@ def main():
     h2d = sum(host[n].numel() for n in ("q", "k", "v", "qs", "ks"))
     d2h = out_host.numel() * 2
 
+    # The steps are pipelined the way a caller with a queue of requests would: one stream copies step i + 1's inputs in and another reads
+    # step i - 1's result back while step i computes; every step still pays its own host-to-device and device-to-host copies in the region.
+    main = torch.cuda.current_stream(dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    ev_in = [torch.cuda.Event() for _ in sets]
+    ev_done = [torch.cuda.Event() for _ in sets]
+    ev_out = [torch.cuda.Event() for _ in sets]
+    out_hosts = [out_host] + [torch.empty_like(out_host).pin_memory() for _ in sets[1:]]
+
     def e2e_step(i):
-        s = sets[i % nsets]
-        for n in ("q", "k", "v", "qs", "ks"):
-            s[n].copy_(host[n], non_blocking=True)
+        k = i % nsets
+        s = sets[k]
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_done[k])      # the set's previous step has consumed its inputs
+            for n in ("q", "k", "v", "qs", "ks"):
+                s[n].copy_(host[n], non_blocking=True)
+            ev_in[k].record(s_in)
+        main.wait_event(ev_in[k])
+        main.wait_event(ev_out[k])           # the set's previous result has been read back
         step(s)
-        out_host.copy_(s["out"], non_blocking=True)
+        ev_done[k].record(main)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_done[k])
+            out_hosts[k].copy_(s["out"], non_blocking=True)
+            ev_out[k].record(s_out)
+
+    def e2e_join():
+        main.wait_stream(s_in)
+        main.wait_stream(s_out)
 
     Ke = max(3, min(K, 50))
-    ms_e2e = timed(e2e_step, 3, Ke)
+    ms_e2e = timed(e2e_step, 3, Ke, e2e_join)
     clocks = sampler.stop() if sampler else None
     status = device_status()
 
