@@ -116,6 +116,10 @@ def load():
     lib.fmha_mxfp8_auto.argtypes = [C.POINTER(Problem), C.c_int, C.c_uint32, C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_uint32), C.c_char_p, C.c_size_t]
     lib.fmha_mxfp8_kvsplit_static_scratch.restype = C.c_int
     lib.fmha_mxfp8_kvsplit_static_scratch.argtypes = [C.POINTER(Problem), C.c_uint32, C.c_void_p, C.c_char_p, C.c_size_t]
+    lib.fmha_mxfp8_quantize_qk.restype = C.c_int
+    lib.fmha_mxfp8_quantize_qk.argtypes = [C.c_void_p, C.c_uint64, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.fmha_mxfp8_quantize_v.restype = C.c_int
+    lib.fmha_mxfp8_quantize_v.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.fmha_mxfp8_device_status.restype = C.c_int
     lib.fmha_mxfp8_device_status.argtypes = [C.POINTER(C.c_uint32)]
     lib.fmha_mxfp8_trace_attach.restype = C.c_int
@@ -129,7 +133,7 @@ def load():
 EXPORTS = (
     "fmha_mxfp8_kernel_name", "fmha_mxfp8_kernarg_size", "fmha_mxfp8_workgroup_size", "fmha_mxfp8_validate", "fmha_mxfp8_grid",
     "fmha_mxfp8_launch", "fmha_mxfp8_dispatch", "fmha_mxfp8_auto", "fmha_mxfp8_device_status", "fmha_mxfp8_trace_attach",
-    "fmha_mxfp8_probe_mma_peak", "fmha_mxfp8_kvsplit_static_scratch",
+    "fmha_mxfp8_probe_mma_peak", "fmha_mxfp8_kvsplit_static_scratch", "fmha_mxfp8_quantize_qk", "fmha_mxfp8_quantize_v",
 )
 
 

@@ -429,6 +429,22 @@ int fmha_mxfp8_auto(const fmha_mxfp8_problem* pr, int path, uint32_t splits, voi
     return 0;
 }
 
+int fmha_mxfp8_quantize_qk(const void* x_bf16, uint64_t rows, float mul, void* out_e4m3, void* out_scales, void* stream) {
+    if (!x_bf16 || !out_e4m3 || !out_scales) return FMHA_MXFP8_E_ARG;
+    if (rows == 0) return 0;
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) || (reinterpret_cast<uintptr_t>(out_e4m3) & 7u) || (reinterpret_cast<uintptr_t>(out_scales) & 3u)) return FMHA_MXFP8_E_ARG;
+    const cudaError_t e = fmha::launch_quantize_qk(x_bf16, rows, mul, out_e4m3, out_scales, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+int fmha_mxfp8_quantize_v(const void* x_bf16, uint64_t n_elems, void* out_e4m3, void* v_descale, void* stream) {
+    if (!x_bf16 || !out_e4m3 || !v_descale || (n_elems & 7u)) return FMHA_MXFP8_E_ARG;
+    if (n_elems == 0) return 0;
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) || (reinterpret_cast<uintptr_t>(out_e4m3) & 7u) || (reinterpret_cast<uintptr_t>(v_descale) & 7u)) return FMHA_MXFP8_E_ARG;
+    const cudaError_t e = fmha::launch_quantize_v(x_bf16, n_elems, out_e4m3, static_cast<float*>(v_descale), static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
 int fmha_mxfp8_device_status(uint32_t* status) {
     uint32_t* d = fmha::device_status_word();
     if (!d || !status) return FMHA_MXFP8_E_ARG;

@@ -37,6 +37,11 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
 
 cudaError_t launch_combine(const float* ohat, const float* lse2, uint8_t* out, uint32_t rows_total, uint32_t splits, cudaStream_t stream);
 
+// Quantisers in front of the path (quantize.cu): bf16 -> e4m3 + E8M0 per 32 head-dim elements (Q with `mul` folded in, K), bf16 -> e4m3 +
+// one f32 descale (V; `descale` needs 8 bytes: [0] the result, [1] scratch).
+cudaError_t launch_quantize_qk(const void* x_bf16, unsigned long long rows, float mul, void* out_e4m3, void* out_scales, cudaStream_t stream);
+cudaError_t launch_quantize_v(const void* x_bf16, unsigned long long n_elems, void* out_e4m3, float* descale, cudaStream_t stream);
+
 cudaError_t launch_mma_probe(int variant, int iters, int ctas, uint32_t* status, cudaStream_t stream);
 
 uint32_t* device_status_word();   // address of the per-device status word (device pointer)

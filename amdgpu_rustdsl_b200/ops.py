@@ -133,3 +133,39 @@ def device_status() -> int:
     if rc:
         raise RuntimeError(f"fmha_mxfp8_device_status failed with code {rc}")
     return int(st.value)
+
+
+Q_PRESCALE = 1.4426950408889634 / math.sqrt(128.0)   # log2(e) / sqrt(d): the softmax scale the kernels expect folded into Q
+
+
+def quantize_qk(x, out, out_scales, *, mul=1.0, stream=None):
+    """bf16 ``x`` [..., 128] -> e4m3 bytes ``out`` (same shape, uint8) and E8M0 scale bytes at the start of the flat uint8 buffer
+    ``out_scales`` (rows * 4 bytes, followed by whatever zeroed slack the caller allocated). The harness's host rule
+    (tests/gpu/ref_host.cpp:239-254) on the device; pass ``mul=Q_PRESCALE`` for Q and 1 for K."""
+    import torch
+    lib = _abi.load()
+    rows = x.numel() // D
+    if x.dtype != torch.bfloat16 or x.shape[-1] != D or not x.is_contiguous() or not x.is_cuda:
+        raise ValueError("quantize_qk: x must be a contiguous CUDA bf16 tensor [..., 128]")
+    if out.numel() != x.numel() or out.element_size() != 1 or not out.is_contiguous() or _nbytes(out_scales) < rows * 4:
+        raise ValueError("quantize_qk: out must hold one byte per element and out_scales 4 bytes per row")
+    if stream is None:
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+    rc = lib.fmha_mxfp8_quantize_qk(x.data_ptr(), rows, float(mul), out.data_ptr(), out_scales.data_ptr(), C.c_void_p(stream))
+    if rc:
+        raise RuntimeError(f"fmha_mxfp8_quantize_qk failed with code {rc}")
+
+
+def quantize_v(x, out, v_descale, *, stream=None):
+    """bf16 ``x`` -> e4m3 bytes ``out`` with one f32 descale written to ``v_descale[0]`` (f32 buffer, the contract asks for >= 4096 bytes)."""
+    import torch
+    lib = _abi.load()
+    if x.dtype != torch.bfloat16 or not x.is_contiguous() or not x.is_cuda or x.numel() % 8:
+        raise ValueError("quantize_v: x must be a contiguous CUDA bf16 tensor with a multiple of 8 elements")
+    if out.numel() != x.numel() or out.element_size() != 1 or not out.is_contiguous() or _nbytes(v_descale) < 8:
+        raise ValueError("quantize_v: out must hold one byte per element and v_descale at least 8 bytes")
+    if stream is None:
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+    rc = lib.fmha_mxfp8_quantize_v(x.data_ptr(), x.numel(), out.data_ptr(), v_descale.data_ptr(), C.c_void_p(stream))
+    if rc:
+        raise RuntimeError(f"fmha_mxfp8_quantize_v failed with code {rc}")

@@ -291,6 +291,21 @@ int fmha_mxfp8_auto(const fmha_mxfp8_problem* prob, int path, uint32_t splits, v
 int fmha_mxfp8_kvsplit_static_scratch(const fmha_mxfp8_problem* prob, uint32_t splits, void* stream, char* err, size_t cap);
 
 /*
+ * The quantisers in front of the path: bf16 activations -> the MXFP8 operands the attention kernels take. The reference has no device
+ * code for this step (SURVEY "next" item): the rule is the one its harness applies on the host (tests/gpu/ref_host.cpp:239-254).
+ *   quantize_qk: x bf16 [rows][128] -> out e4m3 [rows][128], scales E8M0 [rows][4] (one per 32 head-dim elements):
+ *                E8M0 = clamp(floor(log2 amax(x * mul)) - 8 + 127, 0, 254), element = e4m3_rne_sat(x * mul * 2^-(E8M0 - 127)).
+ *                mul = log2(e) / sqrt(128) for Q (the softmax scale the kernels expect folded into Q), 1 for K.
+ *                The caller appends the contract's zeroed slack behind `out_scales` itself.
+ *   quantize_v:  x bf16 [n_elems] (a multiple of 8) -> out e4m3, v_descale[0] = amax / 448 (1 if the tensor is all zero),
+ *                element = e4m3_rne_sat(x / v_descale[0]). v_descale needs 8 writable bytes (the contract's buffer has 4096).
+ * f32 arithmetic, one rounding per operation; inputs must be finite. x 16-byte aligned, out 8-byte aligned. Return 0, FMHA_MXFP8_E_ARG,
+ * or minus a cudaError_t.
+ */
+int fmha_mxfp8_quantize_qk(const void* x_bf16, uint64_t rows, float mul, void* out_e4m3, void* out_scales, void* stream);
+int fmha_mxfp8_quantize_v(const void* x_bf16, uint64_t n_elems, void* out_e4m3, void* v_descale, void* stream);
+
+/*
  * Device status word: 0 when no kernel of this library ever gave up a bounded wait on the current device, else a bit mask of the
  * roles that did. Synchronises the device. No counterpart in the reference (its kernels have no bounded waits); it stands where
  * the reference harness checks hipDeviceSynchronize() after a launch (tests/gpu/ref_host.cpp:400).

@@ -107,6 +107,48 @@ static void quant_rows(xs64* g, uint8_t* dst, uint8_t* scales, long nrows, int h
             }
 }
 
+/* The harness's Q / K quantisation rule (tests/gpu/ref_host.cpp:239-252) as a function of f32 inputs, every step in f32 with one rounding
+ * (product with `mul`, maximum, power-of-two scaling, RNE saturating e4m3): the statement the device quantiser is checked against bit for
+ * bit. For inputs whose product with `mul` is exact this is the harness's arithmetic. */
+void oracle_quantize_rows(const float* x, long nrows, float mul, uint8_t* out, uint8_t* scales) {
+    for (long r = 0; r < nrows; ++r)
+        for (int bk = 0; bk < 4; ++bk) {
+            float y[32], amax = 0.0f;
+            for (int i = 0; i < 32; ++i) {
+                volatile float prod = x[(size_t)r * D + 32 * bk + i] * mul;   /* volatile: no fused or extended-precision evaluation */
+                y[i] = prod;
+                amax = fmaxf(amax, fabsf(y[i]));
+            }
+            int e = -127;
+            if (amax > 0.0f) { int ex; frexpf(amax, &ex); e = ex - 1 - 8; }   /* floor(log2 amax) - 8 */
+            int eb = e + 127; if (eb > 254) eb = 254; if (eb < 0) eb = 0;
+            scales[(size_t)r * 4 + bk] = (uint8_t)eb;
+            for (int i = 0; i < 32; ++i) out[(size_t)r * D + 32 * bk + i] = oracle_e4m3_encode(ldexpf(y[i], 127 - eb));
+        }
+}
+
+/* The harness's V rule (ref_host.cpp:253-258) in f32: descale = amax / 448 (1 for an all-zero tensor), elements e4m3(x / descale). */
+void oracle_quantize_tensor(const float* x, size_t n, uint8_t* out, float* descale) {
+    float amax = 0.0f;
+    for (size_t i = 0; i < n; ++i) amax = fmaxf(amax, fabsf(x[i]));
+    volatile float vd = amax > 0.0f ? amax / 448.0f : 1.0f;
+    *descale = vd;
+    for (size_t i = 0; i < n; ++i) { volatile float q = x[i] / vd; out[i] = oracle_e4m3_encode(q); }
+}
+
+/* The unquantised samples of the `normal` generator, rounded to f32 (Q with its softmax scale already folded in, as the harness draws
+ * them): what a quantiser must turn into the generator's bytes. Same stream order as oracle_generate (Q rows, K rows, V flat). */
+int oracle_generate_raw_normal(const oracle_shape* sh, float* q_raw, float* k_raw, float* v_raw) {
+    const int B = sh->B, H = sh->H, HK = sh->HK, S = sh->S, SK = sh->SK;
+    xs64 g = {0x9E3779B97F4A7C15ull};
+    const double qmul = 1.4426950408889634 / sqrt((double)D);
+    const size_t nq = (size_t)B * S * H * D, nk = (size_t)B * SK * HK * D;
+    for (size_t i = 0; i < nq; ++i) q_raw[i] = (float)(xs_gauss(&g) * qmul);
+    for (size_t i = 0; i < nk; ++i) k_raw[i] = (float)xs_gauss(&g);
+    for (size_t i = 0; i < nk; ++i) v_raw[i] = (float)xs_gauss(&g);
+    return 0;
+}
+
 static int generate_impl(int mode, const oracle_shape* sh, uint8_t* q, uint8_t* k, uint8_t* v, uint8_t* qs, uint8_t* ks, float* vdescale,
                          uint8_t* v_bs, uint8_t* vscale) {
     static const uint8_t palette[11] = {0x00, 0x20, 0x28, 0x30, 0x38, 0x3C, 0x40, 0xA0, 0xA8, 0xB0, 0xB8};

@@ -36,6 +36,11 @@ double oracle_e4m3_decode(uint8_t b);
 uint8_t oracle_e4m3_encode(float x);
 
 /* The harness's three input generators (ref_host.cpp:183-263): fills q, k, v (e4m3 bytes), qs, ks (E8M0 with slack) and *vdescale. */
+/* The harness's quantisation rules as functions of f32 inputs (ref_host.cpp:239-258), and the generator's unquantised samples. */
+void oracle_quantize_rows(const float* x, long nrows, float mul, uint8_t* out, uint8_t* scales);
+void oracle_quantize_tensor(const float* x, size_t n, uint8_t* out, float* descale);
+int oracle_generate_raw_normal(const oracle_shape* sh, float* q_raw, float* k_raw, float* v_raw);
+
 int oracle_generate(int mode, const oracle_shape* sh, uint8_t* q, uint8_t* k, uint8_t* v, uint8_t* qs, uint8_t* ks, float* vdescale);
 
 /*

@@ -153,6 +153,38 @@ def combine_f32(ohat: np.ndarray, lse2: np.ndarray, rows_total: int, splits: int
     return out
 
 
+def quantize_rows(x: np.ndarray, mul: float = 1.0):
+    """The harness's Q / K rule (ref_host.cpp:239-252) on f32 rows of 128: returns (e4m3 bytes [rows,128], E8M0 bytes [rows,4])."""
+    L = lib()
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, 128)
+    out = np.empty(x.shape, np.uint8)
+    scales = np.empty((x.shape[0], 4), np.uint8)
+    L.oracle_quantize_rows(_p(x), C.c_long(x.shape[0]), C.c_float(mul), _p(out), _p(scales))
+    return out, scales
+
+
+def quantize_tensor(x: np.ndarray):
+    """The harness's V rule (ref_host.cpp:253-258) on an f32 tensor: returns (e4m3 bytes, f32 descale)."""
+    L = lib()
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.empty(x.shape, np.uint8)
+    vd = C.c_float(0)
+    L.oracle_quantize_tensor(_p(x), C.c_size_t(x.size), _p(out), C.byref(vd))
+    return out, float(vd.value)
+
+
+def generate_raw_normal(B: int, H: int, S: int, SK: int, HK: int | None = None):
+    """The `normal` generator's unquantised samples as f32: (q [B,S,H,128] with the softmax scale folded in, k, v [B,SK,HK,128])."""
+    HK = HK or H
+    L = lib()
+    sh = _Shape(B, H, HK, S, SK)
+    q = np.empty((B, S, H, 128), np.float32)
+    k = np.empty((B, SK, HK, 128), np.float32)
+    v = np.empty((B, SK, HK, 128), np.float32)
+    L.oracle_generate_raw_normal(C.byref(sh), _p(q), _p(k), _p(v))
+    return q, k, v
+
+
 def dispatch(B, H, S, SK):
     L = lib()
     path, splits = C.c_int(0), C.c_uint32(0)
