@@ -27,7 +27,8 @@
 //              counter g = p (mod 2). Thread r of a group owns query row r = TMEM lane r: it reads the row's 128 scores with one
 //              tensor-memory round trip and hands the S buffer back at once, takes the row's reference from the group of the previous
 //              tile through an 8-byte shared-memory slot {value, tile counter}, converts in place, writes P (packed e4m3) with
-//              tcgen05.st, and rescales O in TMEM on the rare tiles that move the reference. 12 warps = 168 registers per thread.
+//              tcgen05.st, and rescales O in TMEM on the rare tiles that move the reference. 12 warps start with 168 registers per thread;
+//              the service warps then drop to 80 and the softmax warps rise to 208 (setmaxnreg).
 //              The output tile leaves through shared memory and one TMA store per warpgroup.
 // TMEM columns: S0 [0,128) S1 [128,256) O [256,384) L [384,400) P0 [400,432) P1 [432,464) SFQ [464,468) SFK0 [468,472) SFK1 [472,476).
 #include "kernels.h"
@@ -54,6 +55,8 @@ constexpr int kMmaWarp = 0, kKProducerWarp = 1, kPvWarp = 2, kVProducerWarp = 3,
 constexpr int kCols = 128;                  // score columns per softmax thread
 constexpr int kThreads = 32 * (4 + 8);
 constexpr int kMaxRegs = 168;
+constexpr int kServiceRegs = 80, kSoftmaxRegs = 208;   // after the roles part: 4 * 80 + 8 * 208 = 12 * 165.3
+static_assert(4 * kServiceRegs + 8 * kSoftmaxRegs <= 12 * kMaxRegs && kServiceRegs % 8 == 0 && kSoftmaxRegs % 8 == 0, "register file split");
 constexpr uint32_t kTileBytes = 128 * 128;   // one e4m3 tile
 constexpr uint32_t kSfBytes = 512;           // 128 rows x 4 scale bytes
 
@@ -311,6 +314,11 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     // The four service roles are single chains of dependent instructions that share their scheduler with four arithmetic-dense softmax
     // warps, so every instruction costs them several clocks: each role is its own warp, waits with blocking mbarrier waits (its
     // conditions are conjunctions, never alternatives) and keeps its per-tile instruction count small.
+    // The register file is split unevenly: the kernel starts with kMaxRegs registers in every thread; the four service warps (one
+    // warpgroup) give most of theirs back and the softmax warpgroups take them, which lets the compiler keep the whole score row plus
+    // enough temporaries to interleave the conversion's dependent chains without spilling (4-6 % on the full machine).
+    if (warp < kFirstSoftmaxWarp) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kServiceRegs));
     if (warp == kKProducerWarp) {
         // =========================================================== producer: Q and K tiles, Q and K scales ===========================================================
         // K scales run four tiles ahead of the K tiles in four register sets, each use naming its set statically, so that a tile
@@ -554,7 +562,9 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             }
         }
         __syncwarp();
-    } else if (warp >= kFirstSoftmaxWarp) {
+    }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
         // =========================================================== softmax + epilogue ===========================================================
         // Two warpgroups: wg = parity = which tiles (counter g = parity mod 2) and which S / P buffer. Thread r of a group owns query row r.
         const uint32_t st_id = threadIdx.x - 32u * kFirstSoftmaxWarp;
