@@ -45,7 +45,7 @@ using namespace sm100;
 namespace {
 
 constexpr int kRows = 128;          // query rows per CTA tile
-constexpr int kKeys = 128;          // keys per tile
+constexpr int kKeys = kKeysPerTile; // keys per tile (128)
 constexpr int kStages = 4;          // depth of the K ring and of the V ring (freed separately: K after Q K^T, V after P V)
 // The four service warps get the lowest warp ids, one per scheduler (scheduler = warp % 4). Softmax = warps 4-19: a warp's TMEM lane
 // quadrant is warp % 4, so any four consecutive warps cover the 128 rows.
@@ -473,9 +473,11 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         __syncwarp();
     } else if (warp == kMmaWarp) {
         // =========================================================== MMA issuer: score tiles ===========================================================
-        // One lane runs the role. Q K^T and P V are issued by two different threads (this warp and kPvWarp): their streams share no
-        // operand, the pipe interleaves them, and neither thread's instruction stream holds the other up. Descriptors are prepared once.
-        if (lane == 0) {
+        // The whole warp runs the role in step on warp-uniform values and an elected lane issues: written as `if (lane == 0) { ... }` the
+        // role spent 400 clocks per tile on issuing four MMAs and 200 on the commits, because every operand of a tcgen05 instruction then
+        // has to be moved over from vector registers; now 120 and 45. Q K^T and P V are issued by two different threads (this warp's and
+        // kPvWarp's elected lanes): their streams share no operand, the pipe interleaves them, and neither holds the other up.
+        {
             const uint32_t idesc_qk = idesc_mxf8_block_scaled(128, 128, 0, 0, 0, 0);
             const uint32_t t_sfq = tmem + kColSfQ;
             // K-major 128-byte-swizzled Q / K tiles: 8-row groups 1024 B apart, 32 head-dim bytes (two 16-byte units) per MMA
@@ -494,7 +496,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 if (!ok) break;
                 tc_fence_after_sync();
                 // issued behind the previous item's MMAs by the same thread, so it cannot overtake their reads of these columns
-                tmem_cp_sf(t_sfq, dsfq0 + static_cast<uint64_t>((qb * kSfBytes) >> 4));
+                if (elect_one_sync()) tmem_cp_sf(t_sfq, dsfq0 + static_cast<uint64_t>((qb * kSfBytes) >> 4));
                 const uint64_t dq = dq0 + static_cast<uint64_t>((qb * kTileBytes) >> 4);
                 for (int j = 0; j < n_tiles; ++j) {
                     // S[g&1] = Q K(j)^T: needs the K tile and its scales, and the softmax of tile g-2 to have read S[g&1] out
@@ -502,22 +504,24 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     if (ok && g >= 2) ok = mbar_wait(bar_s_free(g & 1u), ((g >> 1) - 1u) & 1u, abort_flag);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    stamp(mma_trace, 2, static_cast<int>(g), 2);
+                    if (lane == 0) stamp(mma_trace, 2, static_cast<int>(g), 2);
                     const uint32_t t_sfk = tmem + ((g & 1u) ? kColSfK1 : kColSfK0);
                     const uint32_t t_s = tmem + ((g & 1u) ? kColS1 : kColS0);
-                    tmem_cp_sf(t_sfk, dsf0 + static_cast<uint64_t>((st * kSfBytes) >> 4));
                     const uint64_t dk = dk0 + static_cast<uint64_t>((st * kTileBytes) >> 4);
+                    if (elect_one_sync()) {
+                        tmem_cp_sf(t_sfk, dsf0 + static_cast<uint64_t>((st * kSfBytes) >> 4));
 #pragma unroll
-                    for (int kb = 0; kb < 4; ++kb) {
-                        const uint32_t id = idesc_qk | (static_cast<uint32_t>(kb) << 29) | (static_cast<uint32_t>(kb) << 4);
-                        mma_mxf8_ss(t_s, dq + 2u * kb, dk + 2u * kb, id, t_sfq + (static_cast<uint32_t>(kb) << 30),
-                                    t_sfk + (static_cast<uint32_t>(kb) << 30), kb > 0 ? 1u : 0u);
+                        for (int kb = 0; kb < 4; ++kb) {
+                            const uint32_t id = idesc_qk | (static_cast<uint32_t>(kb) << 29) | (static_cast<uint32_t>(kb) << 4);
+                            mma_mxf8_ss(t_s, dq + 2u * kb, dk + 2u * kb, id, t_sfq + (static_cast<uint32_t>(kb) << 30),
+                                        t_sfk + (static_cast<uint32_t>(kb) << 30), kb > 0 ? 1u : 0u);
+                        }
+                        stamp(mma_trace, 2, static_cast<int>(g), 4);
+                        tc_commit(bar_s_full(g & 1u));
+                        tc_commit(bar_k_empty(st));
+                        if (j == n_tiles - 1) tc_commit(bar_q_empty(qb));   // the Q buffer can take the item after next
+                        stamp(mma_trace, 2, static_cast<int>(g), 5);
                     }
-                    stamp(mma_trace, 2, static_cast<int>(g), 4);
-                    tc_commit(bar_s_full(g & 1u));
-                    tc_commit(bar_k_empty(st));
-                    if (j == n_tiles - 1) tc_commit(bar_q_empty(qb));   // the Q buffer can take the item after next
-                    stamp(mma_trace, 2, static_cast<int>(g), 5);
                     ++g;
                     if (++st == kStages) { st = 0; ph ^= 1u; }
                 }
@@ -526,7 +530,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         __syncwarp();
     } else if (warp == kPvWarp) {
         // =========================================================== MMA issuer: P V ===========================================================
-        if (lane == 0) {
+        {
             // P V with N = 144: head dims 0..127 from the V tile, 16 more columns from the tile of ones (O | L are adjacent in TMEM)
             const uint32_t idesc_pv = idesc_f8_dense(128, 144, 0, 1);
             uint32_t g = 0, n = 0, ph = 0;
@@ -543,19 +547,21 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     if (ok) ok = mbar_wait(bar_p_full(g & 1u), (g >> 1) & 1u, abort_flag);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    stamp(mma_trace, 3, static_cast<int>(g), 2);
+                    if (lane == 0) stamp(mma_trace, 3, static_cast<int>(g), 2);
                     const uint32_t t_p = tmem + ((g & 1u) ? kColP1 : kColP0);
+                    if (elect_one_sync()) {
 #pragma unroll
-                    for (int kb = 0; kb < 4; ++kb) {
-                        // MN-major B: 8-key groups 1024 B apart; the second 128-byte-wide atom (columns 128..) is the tile of ones
-                        const uint32_t v_addr = v_smem + st * kTileBytes + kb * 4096;
-                        const uint64_t dv = make_smem_desc(v_addr, ones_smem - v_addr, 1024, kSwizzle128B);
-                        mma_f8_ts(tmem + kColO, t_p + 8 * kb, dv, idesc_pv, (i > 0 || kb > 0) ? 1u : 0u);
+                        for (int kb = 0; kb < 4; ++kb) {
+                            // MN-major B: 8-key groups 1024 B apart; the second 128-byte-wide atom (columns 128..) is the tile of ones
+                            const uint32_t v_addr = v_smem + st * kTileBytes + kb * 4096;
+                            const uint64_t dv = make_smem_desc(v_addr, ones_smem - v_addr, 1024, kSwizzle128B);
+                            mma_f8_ts(tmem + kColO, t_p + 8 * kb, dv, idesc_pv, (i > 0 || kb > 0) ? 1u : 0u);
+                        }
+                        stamp(mma_trace, 3, static_cast<int>(g), 3);
+                        tc_commit(bar_v_empty(st));
+                        tc_commit(bar_o_done(g & 1u));
+                        stamp(mma_trace, 3, static_cast<int>(g), 4);
                     }
-                    stamp(mma_trace, 3, static_cast<int>(g), 3);
-                    tc_commit(bar_v_empty(st));
-                    tc_commit(bar_o_done(g & 1u));
-                    stamp(mma_trace, 3, static_cast<int>(g), 4);
                     ++g;
                     if (++st == kStages) { st = 0; ph ^= 1u; }
                 }
@@ -692,6 +698,9 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 if (lazy) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
+                        // a scheduling point every eight words: without them the converting warp keeps its scheduler for long stretches
+                        // and the service warp that shares it falls behind (2-3 %)
+                        if (c % 8 == 4) __syncwarp();
                         pw[c] = kMufuEvery == 0 ? p_word(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3], sh)
                                 : (c % (kMufuEvery ? kMufuEvery : 1) == 0) ? p_word_hybrid(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3], sh, cf)
                                                                            : p_word_fast(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3], cf);

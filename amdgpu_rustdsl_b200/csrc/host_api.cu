@@ -150,15 +150,15 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// A [batch, seq, heads, 128] e4m3 tensor as a 4-D map (head dim, head, row, batch) with a 128-row x 128-byte box, 128-byte swizzle.
-// Rows past `seq` read as zero.
+// A [batch, seq, heads, 128] e4m3 tensor as a 4-D map (head dim, head, row, batch) with a box of `box_rows` rows x 128 bytes, 128-byte
+// swizzle. Rows past `seq` read as zero.
 int make_tile_map(CUtensorMap* m, const void* base, uint64_t seq, uint64_t heads, uint64_t batches, uint64_t head_stride, uint64_t row_stride,
-                  uint64_t batch_stride) {
+                  uint64_t batch_stride, uint32_t box_rows) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return -static_cast<int>(cudaErrorSymbolNotFound);
     const cuuint64_t dims[4] = {128, heads, seq, batches};
     const cuuint64_t strides[3] = {head_stride, row_stride, batch_stride == 0 ? row_stride * seq : batch_stride};
-    const cuuint32_t box[4] = {128, 1, 128, 1};
+    const cuuint32_t box[4] = {128, 1, box_rows, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -244,11 +244,11 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
         B = grid[2] / p.splits;
     }
     CUtensorMap tq, tk, tv;
-    int r = make_tile_map(&tq, a->ptr_q, p.S, p.H, B, a->s_Hs, a->s_Seqs, a->s_Bs);
+    int r = make_tile_map(&tq, a->ptr_q, p.S, p.H, B, a->s_Hs, a->s_Seqs, a->s_Bs, 128u);
     if (r) return r;
-    r = make_tile_map(&tk, a->ptr_k, p.SK, p.HK, B, a->s_k_Hs, a->s_k_Seqs, a->s_k_Bs);
+    r = make_tile_map(&tk, a->ptr_k, p.SK, p.HK, B, a->s_k_Hs, a->s_k_Seqs, a->s_k_Bs, fmha::kKeysPerTile);
     if (r) return r;
-    r = make_tile_map(&tv, a->ptr_v, p.SK, p.HK, B, a->s_v_Hs, a->s_v_Seqs, a->s_v_Bs);
+    r = make_tile_map(&tv, a->ptr_v, p.SK, p.HK, B, a->s_v_Hs, a->s_v_Seqs, a->s_v_Bs, fmha::kKeysPerTile);
     if (r) return r;
     CUtensorMap to;   // the output of the kernel's TMA stores: bf16 O, or the split kernel's f32 partials
     if (!split) {

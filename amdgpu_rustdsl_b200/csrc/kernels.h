@@ -6,6 +6,9 @@
 
 namespace fmha {
 
+// Keys per K / V tile of the attention kernel = rows of the K and V tensor maps' boxes.
+constexpr int kKeysPerTile = 128;
+
 // Everything one attention launch needs, already decoded from the packed kernel arguments.
 struct AttnParams {
     // outputs

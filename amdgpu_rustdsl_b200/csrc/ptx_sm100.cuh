@@ -69,6 +69,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// One lane of a converged warp (always the same one for the full mask). The warp roles that issue tcgen05 / TMA instructions run
+// with all 32 lanes in step on warp-uniform values and let only the elected lane issue: the compiler can then keep descriptors and
+// addresses in uniform registers, where a role written as `if (lane == 0) { ... }` moves every operand over from vector registers.
+__device__ __forceinline__ bool elect_one_sync() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "elect.sync _|P, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // ----------------------------------------------------------------------------------------------- fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
