@@ -319,158 +319,159 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     // enough temporaries to interleave the conversion's dependent chains without spilling (4-6 % on the full machine).
     if (warp < kFirstSoftmaxWarp) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kServiceRegs));
-    if (warp == kKProducerWarp) {
-        // =========================================================== producer: Q and K tiles, Q and K scales ===========================================================
-        // K scales run four tiles ahead of the K tiles in four register sets, each use naming its set statically, so that a tile
-        // never waits for loads issued for the tiles behind it. The scale cursor therefore walks the items on its own.
-        const uint32_t row_step = 32u * p.HK * 4u, tile_step = 4u * row_step;   // bytes between a lane's four keys / between key tiles
-        struct ScaleCursor {
-            const uint8_t* ptr;   // scale word of this lane's first key of the tile
-            int keys_left;        // sequence keys from the tile's first key on (lanes compare against it)
-            int tiles_left;       // of the item
-            uint32_t w;           // the item
-            bool live;
-        };
-        auto enter_item = [&](ScaleCursor& c) {
-            c.live = c.w < n_items;
-            if (!c.live) return;
-            const Item it = decode_item<kSplit>(c.w, p);
-            c.ptr = p.k_descale + static_cast<size_t>(it.batch) * p.ks_batch_stride + (static_cast<size_t>(it.key_lo + lane) * p.HK + it.kv_head) * 4u;
-            c.keys_left = static_cast<int>(p.SK - it.key_lo) - lane;
-            c.tiles_left = it.n_tiles;
-        };
-        auto load_and_advance = [&](ScaleCursor& c, uint32_t (&w)[4]) {
+    if (warp == kKProducerWarp || warp == kVProducerWarp) {
+        // =========================================================== producers: Q, K, V tiles; Q and K scales ===========================================================
+        // Warp 1 issues the Q and K tile copies and gathers the Q scales, warp 3 issues the V tile copies. The K scale bytes (4 per key,
+        // strided by the head count, which a TMA box cannot express) are gathered by both: warp 1 takes the tiles with an even counter,
+        // warp 3 the odd ones, so that neither warp's per-tile instruction stream is long (a producer that needs more clocks per tile
+        // than the softmax sets the pace of the whole CTA). A tile's scales are loaded four tiles (two of the warp's own) ahead into
+        // one of two register sets, each use naming its set statically, so that a tile never waits for loads issued behind it. The
+        // scale cursor therefore walks the items on its own.
+        auto producer = [&](auto is_k_c) {
+            constexpr bool kIsK = decltype(is_k_c)::value;
+            constexpr uint32_t kPar = kIsK ? 0u : 1u;   // parity of the tile counters whose K scales this warp gathers
+            const uint32_t row_step = 32u * p.HK * 4u, tile_step = 4u * row_step;   // bytes between a lane's four keys / between key tiles
+            struct ScaleCursor {
+                const uint8_t* ptr;   // scale word of this lane's first key of the tile
+                int keys_left;        // sequence keys from the tile's first key on (lanes compare against it)
+                int tiles_left;       // of the item
+                uint32_t w;           // the item
+                bool live;
+            };
+            auto enter_item = [&](ScaleCursor& c) {
+                c.live = c.w < n_items;
+                if (!c.live) return;
+                const Item it = decode_item<kSplit>(c.w, p);
+                c.ptr = p.k_descale + static_cast<size_t>(it.batch) * p.ks_batch_stride + (static_cast<size_t>(it.key_lo + lane) * p.HK + it.kv_head) * 4u;
+                c.keys_left = static_cast<int>(p.SK - it.key_lo) - lane;
+                c.tiles_left = it.n_tiles;
+            };
+            auto advance = [&](ScaleCursor& c) {
+                if (!c.live) return;
+                c.ptr += tile_step;
+                c.keys_left -= kKeys;
+                if (--c.tiles_left == 0) {
+                    c.w += stride;
+                    enter_item(c);
+                }
+            };
+            // loads the scales of the cursor's tile and moves the cursor to the warp's next tile (two on)
+            auto load_and_advance = [&](ScaleCursor& c, uint32_t (&w)[4]) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                w[i] = 0x7F7F7F7Fu;   // keys past the sequence: data is zero-filled by TMA, any finite scale does
-                if (c.live && 32 * i < c.keys_left) w[i] = __ldg(reinterpret_cast<const uint32_t*>(c.ptr + i * row_step));
-            }
-            if (!c.live) return;
-            c.ptr += tile_step;
-            c.keys_left -= kKeys;
-            if (--c.tiles_left == 0) {
-                c.w += stride;
-                enter_item(c);
-            }
-        };
-        // Q scale bytes -> [row % 32][row / 32][4] (the layout tcgen05.cp 32x128b.warpx4 spreads over the four lane quadrants)
-        auto load_q_scales = [&](const Item& it, uint32_t (&w)[4]) {
+                for (int i = 0; i < 4; ++i) {
+                    w[i] = 0x7F7F7F7Fu;   // keys past the sequence: data is zero-filled by TMA, any finite scale does
+                    if (c.live && 32 * i < c.keys_left) w[i] = __ldg(reinterpret_cast<const uint32_t*>(c.ptr + i * row_step));
+                }
+                advance(c);
+                advance(c);
+            };
+            // Q scale bytes -> [row % 32][row / 32][4] (the layout tcgen05.cp 32x128b.warpx4 spreads over the four lane quadrants)
+            auto load_q_scales = [&](const Item& it, uint32_t (&w)[4]) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                uint32_t r = it.row0 + lane + 32 * i;
-                r = min(r, p.S - 1u);   // rows past the sequence reuse the last row's scales (block3.rs:110-113)
-                const size_t off = static_cast<size_t>(it.batch) * p.qs_batch_stride + (static_cast<size_t>(r) * p.H + it.head) * 4u;
-                w[i] = __ldg(reinterpret_cast<const uint32_t*>(p.q_descale + off));
+                for (int i = 0; i < 4; ++i) {
+                    uint32_t r = it.row0 + lane + 32 * i;
+                    r = min(r, p.S - 1u);   // rows past the sequence reuse the last row's scales (block3.rs:110-113)
+                    const size_t off = static_cast<size_t>(it.batch) * p.qs_batch_stride + (static_cast<size_t>(r) * p.H + it.head) * 4u;
+                    w[i] = __ldg(reinterpret_cast<const uint32_t*>(p.q_descale + off));
+                }
+            };
+            // The CTA's first copies (Q tile and first K tile, first V tile of its first item) go out before anything else of the role's set-up.
+            if (blockIdx.x < n_items && elect_one_sync()) {
+                const Item it = decode_item<kSplit>(blockIdx.x, p);
+                if (kIsK) {
+                    mbar_arrive_expect_tx(bar_q_full(0), kTileBytes);
+                    tma_load_4d(q_smem, &tm_q, bar_q_full(0), 0, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
+                    stamp(cta_traced ? p.trace : nullptr, 2, 0, 6);
+                    mbar_arrive_expect_tx(bar_k_full(0), kTileBytes);
+                    tma_load_4d(k_smem, &tm_k, bar_k_full(0), 0, static_cast<int>(it.kv_head), static_cast<int>(it.key_lo), static_cast<int>(it.batch));
+                } else {
+                    stamp(cta_traced ? p.trace : nullptr, 3, 0, 6);
+                    mbar_arrive_expect_tx(bar_v_full(0), kTileBytes);
+                    tma_load_4d(v_smem, &tm_v, bar_v_full(0), 0, static_cast<int>(it.kv_head), static_cast<int>(it.key_lo), static_cast<int>(it.batch));
+                }
             }
-        };
-        // The CTA's first two copies (Q tile and first K tile of its first item) go out before anything else of this role's set-up.
-        if (lane == 0 && blockIdx.x < n_items) {
-            const Item it = decode_item<kSplit>(blockIdx.x, p);
-            mbar_arrive_expect_tx(bar_q_full(0), kTileBytes);
-            tma_load_4d(q_smem, &tm_q, bar_q_full(0), 0, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
-            stamp(cta_traced ? p.trace : nullptr, 2, 0, 6);
-            mbar_arrive_expect_tx(bar_k_full(0), kTileBytes);
-            tma_load_4d(k_smem, &tm_k, bar_k_full(0), 0, static_cast<int>(it.kv_head), static_cast<int>(it.key_lo), static_cast<int>(it.batch));
-        }
-        ScaleCursor cs;
-        cs.w = blockIdx.x;
-        enter_item(cs);
-        uint32_t wq[4] = {0u, 0u, 0u, 0u}, w0[4], w1[4], w2[4], w3[4];
-        if (blockIdx.x < n_items) load_q_scales(decode_item<kSplit>(blockIdx.x, p), wq);
-        load_and_advance(cs, w0);
-        load_and_advance(cs, w1);
-        load_and_advance(cs, w2);
-        load_and_advance(cs, w3);
+            ScaleCursor cs;
+            cs.w = blockIdx.x;
+            enter_item(cs);
+            if (kPar) advance(cs);   // this warp's first tile is the CTA's second
+            uint32_t wq[4] = {0u, 0u, 0u, 0u}, w0[4], w1[4];
+            if (kIsK && blockIdx.x < n_items) load_q_scales(decode_item<kSplit>(blockIdx.x, p), wq);
+            load_and_advance(cs, w0);
+            load_and_advance(cs, w1);
 
-        uint32_t gk = 0, n = 0, ph = 0, q_issued = 0;
-        int st = 0;
-        bool ok = true;
-        for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
-            const Item it = decode_item<kSplit>(w, p);
-            const uint32_t qb = n & 1u;
-            // the Q buffer was last used two items ago
-            if (n >= 2) ok = mbar_wait(bar_q_empty(qb), ((n >> 1) - 1u) & 1u, abort_flag);
-            if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
-            // the tile copy goes out first: it does not depend on the scale bytes, whose global loads may still be in flight
-            if (lane == 0 && n > 0) {
-                mbar_arrive_expect_tx(bar_q_full(qb), kTileBytes);
-                tma_load_4d(q_smem + qb * kTileBytes, &tm_q, bar_q_full(qb), 0, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
-            }
-            *reinterpret_cast<uint4*>(smem_gen + SmemLayout::sfq + qb * kSfBytes + lane * 16) = make_uint4(wq[0], wq[1], wq[2], wq[3]);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_q_full(qb));
-            ++q_issued;
-            if (w + stride < n_items) load_q_scales(decode_item<kSplit>(w + stride, p), wq);   // the next item's Q scales, a whole item ahead
-            float* k_trace = cta_traced ? p.trace : nullptr;   // stamps are indexed by the running tile counter
-            int key = static_cast<int>(it.key_lo);
-            for (int j = 0; j < it.n_tiles; ++j, key += kKeys) {
-                // the stage is free once Q K^T of the tile that held it is done
-                if (gk >= static_cast<uint32_t>(kStages)) ok = mbar_wait(bar_k_empty(st), ph ^ 1u, abort_flag);
-                if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
-                if (lane == 0 && gk > 0) {
-                    stamp(k_trace, 2, static_cast<int>(gk), 6);
-                    mbar_arrive_expect_tx(bar_k_full(st), kTileBytes);
-                    tma_load_4d(k_smem + st * kTileBytes, &tm_k, bar_k_full(st), 0, static_cast<int>(it.kv_head), key, static_cast<int>(it.batch));
-                }
-                uint4* sf_dst = reinterpret_cast<uint4*>(smem_gen + SmemLayout::sfk + st * kSfBytes + lane * 16);
-                auto put_and_refill = [&](uint32_t (&set)[4]) {
-                    *sf_dst = make_uint4(set[0], set[1], set[2], set[3]);
-                    load_and_advance(cs, set);   // for the tile four ahead
-                };
-                switch (gk & 3u) {
-                    case 0: put_and_refill(w0); break;
-                    case 1: put_and_refill(w1); break;
-                    case 2: put_and_refill(w2); break;
-                    default: put_and_refill(w3); break;
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_k_full(st));
-                ++gk;
-                if (++st == kStages) { st = 0; ph ^= 1u; }
-            }
-        }
-        if (*abort_flag != 0u) {
-            // leaving early: let the copies already in flight land before the CTA's shared memory is given back
-            for (uint32_t g = gk > static_cast<uint32_t>(kStages) ? gk - kStages : 0u; g < gk; ++g) {
-                const long long t0 = clock64();
-                while (!mbar_test_wait(bar_k_full(g % kStages), (g / kStages) & 1u) && clock64() - t0 < kWaitBudgetCycles) {}
-            }
-            for (uint32_t m = q_issued > 2u ? q_issued - 2u : 0u; m < q_issued; ++m) {
-                const long long t0 = clock64();
-                while (!mbar_test_wait(bar_q_full(m & 1u), (m >> 1) & 1u) && clock64() - t0 < kWaitBudgetCycles) {}
-            }
-        }
-    } else if (warp == kVProducerWarp) {
-        // =========================================================== producer: V tiles ===========================================================
-        if (lane == 0) {
-            uint32_t gv = 0, n = 0, ph = 0;
+            uint32_t g = 0, n = 0, ph = 0, q_issued = 0;   // g: the running tile counter
             int st = 0;
             bool ok = true;
             for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
                 const Item it = decode_item<kSplit>(w, p);
-                float* v_trace = cta_traced ? p.trace : nullptr;
+                const uint32_t qb = n & 1u;
+                if (kIsK) {
+                    // the Q buffer was last used two items ago
+                    if (n >= 2) ok = mbar_wait(bar_q_empty(qb), ((n >> 1) - 1u) & 1u, abort_flag);
+                    if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+                    // the tile copy goes out first: it does not depend on the scale bytes, whose global loads may still be in flight
+                    if (n > 0 && elect_one_sync()) {
+                        mbar_arrive_expect_tx(bar_q_full(qb), kTileBytes);
+                        tma_load_4d(q_smem + qb * kTileBytes, &tm_q, bar_q_full(qb), 0, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
+                    }
+                    *reinterpret_cast<uint4*>(smem_gen + SmemLayout::sfq + qb * kSfBytes + lane * 16) = make_uint4(wq[0], wq[1], wq[2], wq[3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (elect_one_sync()) mbar_arrive(bar_q_full(qb));
+                    ++q_issued;
+                    if (w + stride < n_items) load_q_scales(decode_item<kSplit>(w + stride, p), wq);   // the next item's Q scales, a whole item ahead
+                }
+                float* k_trace = cta_traced ? p.trace : nullptr;   // stamps are indexed by the running tile counter
                 int key = static_cast<int>(it.key_lo);
-                for (int j = 0; ok && j < it.n_tiles; ++j, key += kKeys) {
-                    // the stage is free once P V of the tile that held it is done
-                    if (gv >= static_cast<uint32_t>(kStages)) ok = mbar_wait(bar_v_empty(st), ph ^ 1u, abort_flag);
-                    if (!ok) break;
-                    stamp(v_trace, 3, static_cast<int>(gv), 6);
-                    mbar_arrive_expect_tx(bar_v_full(st), kTileBytes);
-                    tma_load_4d(v_smem + st * kTileBytes, &tm_v, bar_v_full(st), 0, static_cast<int>(it.kv_head), key, static_cast<int>(it.batch));
-                    ++gv;
+                for (int j = 0; j < it.n_tiles; ++j, key += kKeys) {
+                    const bool own_scales = (g & 1u) == kPar;
+                    // K: the stage (tile and scale bytes) is free once Q K^T of the tile that held it is done
+                    if ((kIsK || own_scales) && g >= static_cast<uint32_t>(kStages)) ok = mbar_wait(bar_k_empty(st), ph ^ 1u, abort_flag);
+                    if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+                    if (kIsK && g > 0 && elect_one_sync()) {
+                        stamp(k_trace, 2, static_cast<int>(g), 6);
+                        mbar_arrive_expect_tx(bar_k_full(st), kTileBytes);
+                        tma_load_4d(k_smem + st * kTileBytes, &tm_k, bar_k_full(st), 0, static_cast<int>(it.kv_head), key, static_cast<int>(it.batch));
+                    }
+                    if (own_scales) {
+                        uint4* sf_dst = reinterpret_cast<uint4*>(smem_gen + SmemLayout::sfk + st * kSfBytes + lane * 16);
+                        auto put_and_refill = [&](uint32_t (&set)[4]) {
+                            *sf_dst = make_uint4(set[0], set[1], set[2], set[3]);
+                            load_and_advance(cs, set);   // for the tile four ahead
+                        };
+                        if (g & 2u) put_and_refill(w1); else put_and_refill(w0);
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (elect_one_sync()) mbar_arrive(bar_k_full(st));
+                    }
+                    if (!kIsK) {
+                        // V: the stage is free once P V of the tile that held it is done
+                        if (g >= static_cast<uint32_t>(kStages)) ok = mbar_wait(bar_v_empty(st), ph ^ 1u, abort_flag);
+                        if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+                        if (g > 0 && elect_one_sync()) {
+                            stamp(k_trace, 3, static_cast<int>(g), 6);
+                            mbar_arrive_expect_tx(bar_v_full(st), kTileBytes);
+                            tma_load_4d(v_smem + st * kTileBytes, &tm_v, bar_v_full(st), 0, static_cast<int>(it.kv_head), key, static_cast<int>(it.batch));
+                        }
+                    }
+                    ++g;
                     if (++st == kStages) { st = 0; ph ^= 1u; }
                 }
             }
             if (*abort_flag != 0u) {
-                for (uint32_t g = gv > static_cast<uint32_t>(kStages) ? gv - kStages : 0u; g < gv; ++g) {
+                // leaving early: let the copies already in flight land before the CTA's shared memory is given back
+                for (uint32_t t = g > static_cast<uint32_t>(kStages) ? g - kStages : 0u; t < g; ++t) {
                     const long long t0 = clock64();
-                    while (!mbar_test_wait(bar_v_full(g % kStages), (g / kStages) & 1u) && clock64() - t0 < kWaitBudgetCycles) {}
+                    while (!mbar_test_wait(kIsK ? bar_k_full(t % kStages) : bar_v_full(t % kStages), (t / kStages) & 1u) && clock64() - t0 < kWaitBudgetCycles) {}
+                }
+                for (uint32_t m = q_issued > 2u ? q_issued - 2u : 0u; m < q_issued; ++m) {
+                    const long long t0 = clock64();
+                    while (!mbar_test_wait(bar_q_full(m & 1u), (m >> 1) & 1u) && clock64() - t0 < kWaitBudgetCycles) {}
                 }
             }
-        }
-        __syncwarp();
+        };
+        if (warp == kKProducerWarp) producer(std::true_type{});
+        else producer(std::false_type{});
     } else if (warp == kMmaWarp) {
         // =========================================================== MMA issuer: score tiles ===========================================================
         // The whole warp runs the role in step on warp-uniform values and an elected lane issues: written as `if (lane == 0) { ... }` the
