@@ -660,18 +660,19 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 const float mt = fmaxf(fmaxf(max3(m[0], m[1], m[2]), max3(m[3], m[4], m[5])), fmaxf(m[6], m[7]));
                 stamp(st_trace, par, static_cast<int>(g), 2);
                 stamp(st_trace, par, static_cast<int>(g), 3);
-                // take over the row's reference from the thread that handled the item's previous tile
+                // The hand-over of the row's reference from the thread that handled the item's previous tile is the one dependency that runs
+                // from tile to tile across the two groups, so everything that does not need the old reference is computed before the slot is
+                // read, and the new reference is published before the rescale factor is worked out.
+                const float cand = lazy ? ceilf(mt) : mt;   // where the reference goes if it moves
+                const float mt_thr = mt - thr;
                 if (ok && j > 0 && !wait_slot(ref_slot(g - 1u), g - 1u, ref)) ok = false;
                 // the reference moves when this tile's maximum passes it by more than the threshold (negative for short sequences: it then
                 // also follows the tile maximum down, and f > 1 scales O and L up)
-                const bool move = mt > ref + thr;
-                f = 1.0f;
-                if (move) {
-                    const float nref = lazy ? ceilf(mt) : mt;
-                    f = ex2_approx(ref - nref);   // 0 on the first tile (ref = -inf); an exact power of two for integer references
-                    ref = nref;
-                }
+                const bool move = mt_thr > ref;
+                const float old_ref = ref;
+                ref = move ? cand : ref;
                 st_shared_v2(ref_slot(g), __float_as_uint(ref), g);
+                f = move ? ex2_approx(old_ref - ref) : 1.0f;   // 0 on the first tile (old reference -inf); an exact power of two for integer references
                 stamp(st_trace, par, static_cast<int>(g), 4);
                 // P V of this parity's previous tile must be done before its P columns are overwritten (and, observed in order, this keeps
                 // the phase parity of the other parity's barrier below unambiguous)
