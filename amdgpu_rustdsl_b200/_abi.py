@@ -15,6 +15,7 @@ PATH_NAMES = {VS128: "vs128", T128: "t128", KVSPLIT: "kvsplit"}
 PATH_IDS = {v: k for k, v in PATH_NAMES.items()}
 FLAG_V_BLOCKSCALE = 0x1
 FLAG_EXACT_REBASE = 0x2
+FLAG_CAUSAL = 0x8
 TRACE_BYTES = 4 * (16384 + 16384 + 256 + 4096 + 2048)
 STATIC_SCRATCH_MAX_ROW_SPLITS = 65536   # FMHA_MXFP8_STATIC_SCRATCH_MAX_ROW_SPLITS
 

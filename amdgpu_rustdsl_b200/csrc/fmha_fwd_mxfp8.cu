@@ -74,6 +74,7 @@ constexpr uint32_t kTmemCols = 512;
 constexpr float kPOffset = 5.0f;
 constexpr float kLazyThreshold = 3.5f;
 constexpr float kFollowWindow = 11.0f;
+constexpr uint32_t kFlagCausal = 0x8u;   // FMHA_MXFP8_FLAG_CAUSAL: selects the kCausal instantiations
 
 struct SmemLayout {
     // all tile buffers are 1024-byte aligned (128-byte swizzle atom = 8 rows x 128 B)
@@ -191,11 +192,24 @@ struct Item {
     int n_tiles;
 };
 
-template <bool kSplit>
+template <bool kSplit, bool kCausal>
 __device__ __forceinline__ Item decode_item(uint32_t w, const AttnParams& p) {
     // w = (z * H + head) * n_qtiles + q tile: neighbouring CTAs work on neighbouring row blocks of one head, whose K / V they share in L2
     Item it;
-    const uint32_t x = w % p.n_qtiles, yz = w / p.n_qtiles;
+    uint32_t x = w % p.n_qtiles, yz = w / p.n_qtiles;
+    constexpr bool causal = kCausal && !kSplit;
+    if (causal) {
+        // Items in the order of falling work (the row block's visible keys): rank = (n_qtiles - 1 - q tile) * (H * B) + (batch * H + head).
+        // The CTAs walk the ranks in rounds of gridDim.x, odd rounds backwards, so that the CTA that got the heaviest item of one round
+        // gets the lightest of the next and every CTA ends with about the same number of key tiles.
+        const uint32_t round = w / gridDim.x, base = round * gridDim.x;
+        uint32_t pos = w - base;
+        if (round & 1u) pos = min(gridDim.x, p.n_items - base) - 1u - pos;
+        const uint32_t rank = base + pos;
+        const uint32_t hb = p.n_items / p.n_qtiles;
+        x = p.n_qtiles - 1u - rank / hb;
+        yz = rank % hb;
+    }
     it.row0 = x * kRows;
     it.head = yz % p.H;
     const uint32_t z = yz / p.H;
@@ -216,6 +230,8 @@ __device__ __forceinline__ Item decode_item(uint32_t w, const AttnParams& p) {
         it.key_lo = tile_lo * kKeys;
         it.key_hi = min(tile_hi * kKeys, p.SK);
     }
+    // causal (crates/amdgpu-stage/src/attention/attn3.rs:298-306): row i sees the keys below min(i + SK - S + 1, SK); the item's last row decides
+    if (causal) it.key_hi = min(p.SK, it.row0 + kRows + (p.SK - p.S));
     it.n_tiles = (it.key_hi > it.key_lo) ? static_cast<int>((it.key_hi - it.key_lo + kKeys - 1) / kKeys) : 0;
     return it;
 }
@@ -227,7 +243,7 @@ __device__ __forceinline__ Item decode_item(uint32_t w, const AttnParams& p) {
 // two score tiles overlap the current item's last tiles and epilogue; only O is single: P V of an item's first tile waits until the
 // epilogue of the item before has read O out (o_free).
 // kTrace = false compiles every diagnostic (tile dumps, time stamps) out of the tile loop: the production launches use that variant.
-template <bool kSplit, bool kTrace, bool kLazy>
+template <bool kSplit, bool kTrace, bool kLazy, bool kCausal>
 __global__ void __maxnreg__(kMaxRegs)
 fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const AttnParams p) {
@@ -341,7 +357,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             auto enter_item = [&](ScaleCursor& c) {
                 c.live = c.w < n_items;
                 if (!c.live) return;
-                const Item it = decode_item<kSplit>(c.w, p);
+                const Item it = decode_item<kSplit, kCausal>(c.w, p);
                 c.ptr = p.k_descale + static_cast<size_t>(it.batch) * p.ks_batch_stride + (static_cast<size_t>(it.key_lo + lane) * p.HK + it.kv_head) * 4u;
                 c.keys_left = static_cast<int>(p.SK - it.key_lo) - lane;
                 c.tiles_left = it.n_tiles;
@@ -377,7 +393,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             };
             // The CTA's first copies (Q tile and first K tile, first V tile of its first item) go out before anything else of the role's set-up.
             if (blockIdx.x < n_items && elect_one_sync()) {
-                const Item it = decode_item<kSplit>(blockIdx.x, p);
+                const Item it = decode_item<kSplit, kCausal>(blockIdx.x, p);
                 if (kIsK) {
                     mbar_arrive_expect_tx(bar_q_full(0), kTileBytes);
                     tma_load_4d(q_smem, &tm_q, bar_q_full(0), 0, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
@@ -395,7 +411,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             enter_item(cs);
             if (kPar) advance(cs);   // this warp's first tile is the CTA's second
             uint32_t wq[4] = {0u, 0u, 0u, 0u}, w0[4], w1[4];
-            if (kIsK && blockIdx.x < n_items) load_q_scales(decode_item<kSplit>(blockIdx.x, p), wq);
+            if (kIsK && blockIdx.x < n_items) load_q_scales(decode_item<kSplit, kCausal>(blockIdx.x, p), wq);
             load_and_advance(cs, w0);
             load_and_advance(cs, w1);
 
@@ -403,7 +419,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             int st = 0;
             bool ok = true;
             for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
-                const Item it = decode_item<kSplit>(w, p);
+                const Item it = decode_item<kSplit, kCausal>(w, p);
                 const uint32_t qb = n & 1u;
                 if (kIsK) {
                     // the Q buffer was last used two items ago
@@ -419,7 +435,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     __syncwarp();
                     if (elect_one_sync()) mbar_arrive(bar_q_full(qb));
                     ++q_issued;
-                    if (w + stride < n_items) load_q_scales(decode_item<kSplit>(w + stride, p), wq);   // the next item's Q scales, a whole item ahead
+                    if (w + stride < n_items) load_q_scales(decode_item<kSplit, kCausal>(w + stride, p), wq);   // the next item's Q scales, a whole item ahead
                 }
                 float* k_trace = cta_traced ? p.trace : nullptr;   // stamps are indexed by the running tile counter
                 int key = static_cast<int>(it.key_lo);
@@ -490,7 +506,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             int st = 0;
             bool ok = true;
             for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
-                const int n_tiles = decode_item<kSplit>(w, p).n_tiles;
+                const int n_tiles = decode_item<kSplit, kCausal>(w, p).n_tiles;
                 const uint32_t qb = n & 1u;
                 float* mma_trace = cta_traced ? p.trace : nullptr;
                 ok = mbar_wait(bar_q_full(qb), (n >> 1) & 1u, abort_flag);
@@ -538,7 +554,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             int st = 0;
             bool ok = true;
             for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
-                const int n_tiles = decode_item<kSplit>(w, p).n_tiles;
+                const int n_tiles = decode_item<kSplit, kCausal>(w, p).n_tiles;
                 float* mma_trace = cta_traced ? p.trace : nullptr;
                 // an item's first tile overwrites O and L, which the epilogue of the item before must have read out
                 if (n > 0) ok = mbar_wait(bar_o_free, (n - 1u) & 1u, abort_flag);
@@ -606,11 +622,19 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         uint32_t g0 = 0, n = 0;   // tile counter at the item's first tile; ordinal of the item
         for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
             // only the tile count and the last tile's valid keys stay live through the tile loop; the item is decoded again for the epilogue
-            int n_tiles, tail_valid;
+            // only the tile count, the number of tiles every row sees in full and the row's own key limit stay live through the tile loop;
+            // the item is decoded again for the epilogue
+            int n_tiles, j_full, row_lim;   // row_lim: this row's visible keys, counted from the item's first key
             {
-                const Item it = decode_item<kSplit>(w, p);
+                const Item it = decode_item<kSplit, kCausal>(w, p);
                 n_tiles = it.n_tiles;
-                tail_valid = static_cast<int>(it.key_hi - it.key_lo) - (n_tiles - 1) * kKeys;
+                row_lim = static_cast<int>(it.key_hi - it.key_lo);
+                int first_lim = row_lim;   // the limit of the item's first row: the tiles below it need no mask
+                if (kCausal && !kSplit) {
+                    first_lim = min(row_lim, static_cast<int>(it.row0 + 1u + (p.SK - p.S)));
+                    row_lim = min(row_lim, static_cast<int>(it.row0 + r + 1u + (p.SK - p.S)));
+                }
+                j_full = first_lim / kKeys;
             }
             const bool tracing = cta_traced && n == 0;
             const bool dumping = tracing && !(p.flags & 0x4u);   // flag 0x4: time stamps only, no tile dumps
@@ -640,9 +664,10 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 tc_fence_before_sync();
                 mbar_arrive(bar_s_free(par));
                 if (kMasked) {   // keys past the range: -inf for the maximum, 0 for P (crates/amdgpu-tile/src/reduce.rs:35-49)
+                    const int valid = row_lim - j * kKeys;   // may be <= 0 on the causal diagonal: the row then has no key in this tile
 #pragma unroll
                     for (int c = 0; c < 128; ++c) {
-                        if (c >= tail_valid) v[c] = 0xFF800000u;
+                        if (c >= valid) v[c] = 0xFF800000u;
                     }
                 }
                 if (dumping && j == 0) {
@@ -722,10 +747,11 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 mbar_arrive(bar_p_full(par));
                 stamp(st_trace, par, static_cast<int>(g), 7);
             };
-            const bool ragged = tail_valid < kCols;
-            const int j_full = ragged ? n_tiles - 1 : n_tiles;   // tiles [0, j_full) have all their keys
-            for (int j = static_cast<int>((g0 ^ par) & 1u); j < j_full; j += 2) tile(j, std::false_type{});
-            if (ragged && ((g0 + static_cast<uint32_t>(n_tiles) - 1u) & 1u) == par) tile(n_tiles - 1, std::true_type{});
+            // tiles [0, j_full) have all their keys for every row; behind them come at most two tiles (a ragged end: one; the causal
+            // diagonal: up to two), of which this parity owns at most one
+            int j = static_cast<int>((g0 ^ par) & 1u);
+            for (; j < j_full; j += 2) tile(j, std::false_type{});
+            if (j < n_tiles) tile(j, std::true_type{});
             if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
 
             // ---- epilogue: O * v_descale / l; warpgroup wg stores head dims [kOutCols wg, kOutCols wg + kOutCols) ----
@@ -757,7 +783,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 stamp(ep_trace, par, 24 + static_cast<int>(n), 4);
                 uint32_t w_again;          // opaque copy: keeps the compiler from holding the decoded item in registers across the tile loop
                 asm volatile("mov.u32 %0, %1;" : "=r"(w_again) : "r"(w));
-                const Item it = decode_item<kSplit>(w_again, p);
+                const Item it = decode_item<kSplit, kCausal>(w_again, p);
                 stamp(ep_trace, par, 24 + static_cast<int>(n), 5);
                 const float l = __uint_as_float(lv);
                 const float fin = vd / l;   // crates/amdgpu-stage/src/attention/state.rs:79-82
@@ -858,17 +884,24 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
                              uint32_t B, bool split, uint32_t rows_per_cta, cudaStream_t stream) {
     (void)rows_per_cta;   // both logical block heights run as 128-row CTAs
     using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
-    static const Kernel kernels[8] = {fmha_fwd_mxfp8_kernel<false, false, false>, fmha_fwd_mxfp8_kernel<true, false, false>,
-                                      fmha_fwd_mxfp8_kernel<false, true, false>,  fmha_fwd_mxfp8_kernel<true, true, false>,
-                                      fmha_fwd_mxfp8_kernel<false, false, true>,  fmha_fwd_mxfp8_kernel<true, false, true>,
-                                      fmha_fwd_mxfp8_kernel<false, true, true>,   fmha_fwd_mxfp8_kernel<true, true, true>};
+    // [causal][recipe][trace][split]; the causal mask has no split form
+    static const Kernel kernels[16] = {fmha_fwd_mxfp8_kernel<false, false, false, false>, fmha_fwd_mxfp8_kernel<true, false, false, false>,
+                                       fmha_fwd_mxfp8_kernel<false, true, false, false>,  fmha_fwd_mxfp8_kernel<true, true, false, false>,
+                                       fmha_fwd_mxfp8_kernel<false, false, true, false>,  fmha_fwd_mxfp8_kernel<true, false, true, false>,
+                                       fmha_fwd_mxfp8_kernel<false, true, true, false>,   fmha_fwd_mxfp8_kernel<true, true, true, false>,
+                                       fmha_fwd_mxfp8_kernel<false, false, false, true>,  nullptr,
+                                       fmha_fwd_mxfp8_kernel<false, true, false, true>,   nullptr,
+                                       fmha_fwd_mxfp8_kernel<false, false, true, true>,   nullptr,
+                                       fmha_fwd_mxfp8_kernel<false, true, true, true>,    nullptr};
     constexpr int kMaxDevices = 64;
-    static bool attr_done[kMaxDevices][8] = {};   // the shared-memory attribute is per device
+    static bool attr_done[kMaxDevices][16] = {};   // the shared-memory attribute is per device
     static int sm_count[kMaxDevices] = {};
     // the long-sequence recipe from 4 key tiles of the whole sequence on (crates/amdgpu-stage/src/attention/state.rs:73-77), unless the
     // caller asks for the exact one; each recipe is its own instantiation, which halves the code of the tile loop
     const bool lazy_recipe = (p.SK + kKeys - 1) / kKeys >= 4 && !(p.flags & 0x2u);
-    const int which = (split ? 1 : 0) + (p.trace != nullptr ? 2 : 0) + (lazy_recipe ? 4 : 0);
+    const bool causal = (p.flags & kFlagCausal) != 0u;
+    if (causal && split) return cudaErrorInvalidValue;
+    const int which = (split ? 1 : 0) + (p.trace != nullptr ? 2 : 0) + (lazy_recipe ? 4 : 0) + (causal ? 8 : 0);
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;

@@ -223,6 +223,7 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
     p.ks_batch_stride = a->s_descale_k_Bs;
     p.flags = a->ext_flags;
     if (p.flags & FMHA_MXFP8_FLAG_V_BLOCKSCALE) return FMHA_MXFP8_E_ARG;   // per-32-key V scales are declared in the ABI but no kernel implements them
+    if ((p.flags & FMHA_MXFP8_FLAG_CAUSAL) && (split || p.SK < p.S)) return FMHA_MXFP8_E_ARG;   // causal: unsplit kernels, SK >= S
     p.v_blockscale = (p.flags & FMHA_MXFP8_FLAG_V_BLOCKSCALE) ? static_cast<const uint8_t*>(a->ext_ptr_v_blockscale) : nullptr;
     p.lse_nat = split ? nullptr : static_cast<float*>(a->ext_ptr_lse);
     p.trace = g_trace;
@@ -360,6 +361,10 @@ int fmha_mxfp8_auto(const fmha_mxfp8_problem* pr, int path, uint32_t splits, voi
     if ((gqa & (gqa - 1)) != 0 || gqa > 16) return fail(err, cap, FMHA_MXFP8_E_ARG, "H / HK must be a power of two <= 16");
     if (path < 0) {
         fmha_mxfp8_dispatch(pr->B, pr->H, pr->S, pr->SK, &path, &splits);
+        if ((pr->flags & FMHA_MXFP8_FLAG_CAUSAL) && path == FMHA_MXFP8_KVSPLIT) {   // the causal extension has no split form
+            path = FMHA_MXFP8_VS128;
+            splits = 0;
+        }
     } else if (path == FMHA_MXFP8_KVSPLIT) {
         if (splits == 0) splits = 4;
         if (splits != 2 && splits != 4 && splits != 8) return fail(err, cap, FMHA_MXFP8_E_ARG, "splits must be 2, 4 or 8");

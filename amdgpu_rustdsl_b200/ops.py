@@ -71,7 +71,7 @@ def fill_common(a, q, k, v, q_scale, k_scale, v_scale, out, B, S, H, SK, HK, fla
 
 
 def fmha_fwd_mxfp8(q, k, v, q_scale, k_scale, v_scale, out, *, path="auto", splits=None, stream=None, check=True, flags=0,
-                   v_blockscale=None, lse=None):
+                   v_blockscale=None, lse=None, causal=False):
     """MXFP8 attention forward, head dim 128: ``out = softmax2(q k^T) v`` with E8M0 1x32 scales on q and k and a scalar f32 V descale.
 
     q        [B, S, H, 128]  e4m3 bytes (uint8 or float8_e4m3fn)      k, v  [B, SK, HK, 128]  (H = gqa * HK, gqa a power of two <= 16)
@@ -80,6 +80,8 @@ def fmha_fwd_mxfp8(q, k, v, q_scale, k_scale, v_scale, out, *, path="auto", spli
     v_scale  f32 buffer of at least 4096 bytes, element 0 is the V descale
     out      [B, S, H, 128]  bf16
     path     "auto" | "vs128" | "t128" | "kvsplit" (splits in {2, 4, 8}).  Returns (path, splits) like the reference.
+    causal   extension (the reference's MXFP8 path has no mask): key k visible to row i when k < min(i + SK - S + 1, SK); needs SK >= S,
+             unsplit paths only ("auto" then never picks the split).
     """
     import torch
     lib = _abi.load()
@@ -94,8 +96,14 @@ def fmha_fwd_mxfp8(q, k, v, q_scale, k_scale, v_scale, out, *, path="auto", spli
         raise ValueError("fmha_fwd_mxfp8: q, k, v are 1-byte e4m3 tensors and out is bf16")
     if _nbytes(v_scale) < 4:
         raise ValueError("v_scale: needs at least one f32")
+    if causal:
+        flags |= _abi.FLAG_CAUSAL
+        if SK < S:
+            raise ValueError("fmha_fwd_mxfp8: causal needs SK >= S")
     if path == "auto":
         path, splits = select_path(B, H, S, SK)
+        if causal and path == "kvsplit":
+            path, splits = "vs128", 0
     elif path == "kvsplit":
         splits = splits or 4
     if stream is None:

@@ -46,6 +46,14 @@ enum fmha_mxfp8_error {
 #define FMHA_MXFP8_FLAG_V_BLOCKSCALE 0x1u /* V carries one E8M0 per 32 keys per column at ext_ptr_v_blockscale (extension) */
 #define FMHA_MXFP8_FLAG_EXACT_REBASE 0x2u /* move the softmax reference on every tile (the short-sequence recipe) for any length */
 #define FMHA_MXFP8_FLAG_TRACE_STAMPS_ONLY 0x4u /* with a trace buffer attached: record the time stamps but not the tile dumps */
+/*
+ * Causal mask (extension: the reference's MXFP8 kernels have none; the rule is the one of its per-tensor sibling family,
+ * crates/amdgpu-stage/src/attention/attn3.rs:298-306): key k is visible to query row i when k < min(i + SK - S + 1, SK), i.e. the last
+ * query row sees every key. Needs SK >= S (every row then sees key 0). Unsplit kernels only: a launch of the kvsplit kernel with this
+ * flag, or with SK < S, returns FMHA_MXFP8_E_ARG before anything is launched; fmha_mxfp8_auto runs a causal problem unsplit whatever the
+ * shape dispatch says.
+ */
+#define FMHA_MXFP8_FLAG_CAUSAL 0x8u
 
 #pragma pack(push, 1)
 /*

@@ -235,29 +235,33 @@ int oracle_generate_v_blockscaled(const oracle_shape* sh, uint8_t* v, uint8_t* v
 /* ------------------------------------------------------------------------------------------------ fp64 oracle */
 
 /* tests/gpu/ref_host.cpp:438-471 (`check`), same operation order: dequantise, scores * ln 2, max-subtracted exp, normalise, * V descale. */
-int oracle_reference(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
-                     float vdescale, const uint8_t* vscale, int rows, double* ref) {
-    const int B = sh->B, H = sh->H, HK = sh->HK, S = sh->S, SK = sh->SK, GQA = sh->H / sh->HK;
+static int reference_impl(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
+                          float vdescale, const uint8_t* vscale, int rows, int causal, double* ref) {
+    const int B = sh->B, H = sh->H, HK = sh->HK, S = sh->S, SK_all = sh->SK, GQA = sh->H / sh->HK;
     const int rows_eff = rows < S ? rows : S;
     const double cpu_scale = 0.6931471805599453;
-    const int nblk = (SK + 31) / 32;
+    const int nblk = (SK_all + 31) / 32;
     double tab[256];
     for (int i = 0; i < 256; ++i) tab[i] = oracle_e4m3_decode((uint8_t)i);
 #pragma omp parallel
     {
-        double* sc = (double*)malloc((size_t)SK * sizeof(double));
+        double* sc = (double*)malloc((size_t)SK_all * sizeof(double));
         double qd[D];
 #pragma omp for collapse(3) schedule(dynamic, 1)
         for (int b = 0; b < B; ++b)
             for (int h = 0; h < H; ++h)
                 for (int i = 0; i < rows_eff; ++i) {
                     const int hk = h / GQA;
+                    /* the keys the row sees: all of them, or (causal, crates/amdgpu-stage/src/attention/attn3.rs:298-306) those below
+                       min(i + SK - S + 1, SK) */
+                    int SK = SK_all;
+                    if (causal) { SK = i + SK_all - S + 1; if (SK > SK_all) SK = SK_all; if (SK < 0) SK = 0; }
                     for (int kk = 0; kk < D; ++kk)
                         qd[kk] = tab[q[(((size_t)b * S + i) * H + h) * D + kk]] * ldexp(1.0, (int)qs[(((size_t)b * S + i) * H + h) * 4 + kk / 32] - 127);
                     double mx = -1e300;
                     for (int t = 0; t < SK; ++t) {
-                        const uint8_t* kr = k + (((size_t)b * SK + t) * HK + hk) * D;
-                        const uint8_t* sr = ks + (((size_t)b * SK + t) * HK + hk) * 4;
+                        const uint8_t* kr = k + (((size_t)b * SK_all + t) * HK + hk) * D;
+                        const uint8_t* sr = ks + (((size_t)b * SK_all + t) * HK + hk) * 4;
                         double acc = 0.0;
                         for (int kk = 0; kk < D; ++kk) acc += qd[kk] * tab[kr[kk]] * ldexp(1.0, (int)sr[kk / 32] - 127);
                         sc[t] = acc * cpu_scale;
@@ -270,10 +274,10 @@ int oracle_reference(const oracle_shape* sh, const uint8_t* q, const uint8_t* k,
                         double acc = 0.0;
                         if (vscale) {
                             for (int t = 0; t < SK; ++t)
-                                acc += sc[t] / den * tab[v[(((size_t)b * SK + t) * HK + hk) * D + d]] *
+                                acc += sc[t] / den * tab[v[(((size_t)b * SK_all + t) * HK + hk) * D + d]] *
                                        ldexp(1.0, (int)vscale[(((size_t)b * nblk + t / 32) * HK + hk) * D + d] - 127);
                         } else {
-                            for (int t = 0; t < SK; ++t) acc += sc[t] / den * tab[v[(((size_t)b * SK + t) * HK + hk) * D + d]];
+                            for (int t = 0; t < SK; ++t) acc += sc[t] / den * tab[v[(((size_t)b * SK_all + t) * HK + hk) * D + d]];
                             acc *= vdescale;
                         }
                         o[d] = acc;
@@ -282,6 +286,16 @@ int oracle_reference(const oracle_shape* sh, const uint8_t* q, const uint8_t* k,
         free(sc);
     }
     return 0;
+}
+
+int oracle_reference(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
+                     float vdescale, const uint8_t* vscale, int rows, double* ref) {
+    return reference_impl(sh, q, k, v, qs, ks, vdescale, vscale, rows, 0, ref);
+}
+
+int oracle_reference_causal(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
+                            float vdescale, int rows, double* ref) {
+    return reference_impl(sh, q, k, v, qs, ks, vdescale, NULL, rows, 1, ref);
 }
 
 /* tests/gpu/ref_host.cpp:463-469: err = |got - ref|; bad when !(err <= 0.05 + 0.05 |ref|) (NaN counts); worst, mean, max|ref| */

@@ -57,6 +57,11 @@ int oracle_generate_v_blockscaled(const oracle_shape* sh, uint8_t* v, uint8_t* v
 int oracle_reference(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
                      float vdescale, const uint8_t* vscale, int rows, double* ref);
 
+/* The same oracle with the causal mask of the reference's per-tensor sibling family (crates/amdgpu-stage/src/attention/attn3.rs:298-306):
+ * row i sees the keys below min(i + SK - S + 1, SK). The reference's MXFP8 path has no mask; this checks the library's extension. */
+int oracle_reference_causal(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
+                            float vdescale, int rows, double* ref);
+
 typedef struct oracle_stats {
     uint64_t checked, bad;
     double worst_err, mean_err, max_ref;

@@ -98,12 +98,19 @@ def generate(mode: str, B: int, H: int, S: int, SK: int, HK: int | None = None, 
     return Inputs(B, H, HK, S, SK, q.reshape(B, S, H, 128), k.reshape(B, SK, HK, 128), v.reshape(B, SK, HK, 128), qs, ks, float(vd.value), vscale)
 
 
-def reference(inp: Inputs, rows: int) -> np.ndarray:
-    """fp64 oracle (ref_host.cpp:438-471) for the first ``rows`` query rows of every (b,h): float64 [B,H,rows_eff,128]."""
+def reference(inp: Inputs, rows: int, causal: bool = False) -> np.ndarray:
+    """fp64 oracle (ref_host.cpp:438-471) for the first ``rows`` query rows of every (b,h): float64 [B,H,rows_eff,128].
+    ``causal``: row i sees the keys below min(i + SK - S + 1, SK) (the mask of the reference's per-tensor sibling family, attn3.rs:298-306)."""
     L = lib()
     re = min(rows, inp.S)
     ref = np.empty((inp.B, inp.H, re, 128), np.float64)
     sh = inp.shape
+    if causal:
+        rc = L.oracle_reference_causal(C.byref(sh), _p(inp.q), _p(inp.k), _p(inp.v), _p(inp.qs), _p(inp.ks), C.c_float(inp.vdescale),
+                                       C.c_int(rows), _p(ref))
+        if rc:
+            raise RuntimeError(f"oracle_reference_causal failed: {rc}")
+        return ref
     rc = L.oracle_reference(C.byref(sh), _p(inp.q), _p(inp.k), _p(inp.v), _p(inp.qs), _p(inp.ks), C.c_float(inp.vdescale), _p(inp.vscale),
                             C.c_int(rows), _p(ref))
     if rc:
