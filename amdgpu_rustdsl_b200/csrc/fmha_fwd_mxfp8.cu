@@ -13,16 +13,20 @@
 //
 // Mapping onto the SM (not a translation of the gfx950 wave layout): a persistent kernel, one CTA of 12 warps per SM, each CTA walking
 // work items (128 query rows of one (batch, head[, split])) with its rings, buffers and barriers running on across items.
-//   warp  0    Q K^T issuer: one lane issues S[g % 2] = Q K_g^T as kind::mxf8f6f4.block_scale tcgen05.mma, both operands in swizzled
-//              shared memory, the E8M0 factors copied to TMEM with tcgen05.cp. Two score tiles are always ahead of the softmax.
+// The four service warps run their loops with all 32 lanes in step on warp-uniform values and let an elected lane issue the tcgen05 /
+// TMA instructions (operands then stay in uniform registers).
+//   warp  0    Q K^T issuer: S[g % 2] = Q K_g^T as kind::mxf8f6f4.block_scale tcgen05.mma, both operands in swizzled shared memory,
+//              the E8M0 factors copied to TMEM with tcgen05.cp. Two score tiles are always ahead of the softmax.
 //   warp  1    Q / K producer: TMA loads of the Q tile (double buffered across items) and of the K ring, plus the 4-byte-per-row scale
-//              gathers, which a TMA box cannot express, written in the 32x16-byte layout tcgen05.cp expects.
+//              gathers (Q, and K for the tiles with an even counter), which a TMA box cannot express, written in the 32x16-byte
+//              layout tcgen05.cp expects.
 //   warp  2    P V issuer: O += P_g V_g with P from TMEM and V (keys x head dim, i.e. MN-major B) from shared memory. The B operand
 //              is 144 wide: 128 head dims plus 16 columns of a tile of e4m3 ones, so that O[:, 128..143] (= the L columns) holds the
 //              row sums of the *quantised* P at no ALU cost (the reference sums P with a matrix instruction too, reduce.rs:163-173).
 //              It has a thread of its own: the tensor pipe takes MMAs from one thread at its full rate, but a thread that shares its
 //              scheduler with softmax warps only gets an instruction in every few clocks.
-//   warp  3    V producer: TMA loads of the V ring (K is freed after Q K^T, V after P V, so the two rings run apart).
+//   warp  3    V producer: TMA loads of the V ring (K is freed after Q K^T, V after P V, so the two rings run apart), and the K scale
+//              gathers of the tiles with an odd counter.
 //   warps 4-11 softmax + epilogue, two warpgroups: warpgroup p works on the tiles with
 //              counter g = p (mod 2). Thread r of a group owns query row r = TMEM lane r: it reads the row's 128 scores with one
 //              tensor-memory round trip and hands the S buffer back at once, takes the row's reference from the group of the previous
@@ -243,6 +247,7 @@ __device__ __forceinline__ Item decode_item(uint32_t w, const AttnParams& p) {
 // two score tiles overlap the current item's last tiles and epilogue; only O is single: P V of an item's first tile waits until the
 // epilogue of the item before has read O out (o_free).
 // kTrace = false compiles every diagnostic (tile dumps, time stamps) out of the tile loop: the production launches use that variant.
+// kLazy: the long-sequence softmax recipe. kCausal: the causal mask (never with kSplit).
 template <bool kSplit, bool kTrace, bool kLazy, bool kCausal>
 __global__ void __maxnreg__(kMaxRegs)
 fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
