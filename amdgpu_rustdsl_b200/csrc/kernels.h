@@ -34,7 +34,8 @@ struct AttnParams {
 };
 
 // rows_per_cta is 128 (t128) or 256 (vs128 / kvsplit): the logical block height of the reference's grids.
-// tm_o: the bf16 output as a 4-D map with a 128-row x 64-column box (unsplit kernels; ignored by the split kernel)
+// tm_o: the target of the kernel's TMA stores: the bf16 output as a 4-D map with a 128-row x 64-column box (unsplit kernels), or the
+// f32 partials as a 5-D map with a 128-row x 32-column box (split kernel)
 cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnParams& p,
                              uint32_t B, bool split, uint32_t rows_per_cta, cudaStream_t stream);
 

@@ -168,8 +168,58 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def run_quantizer_bench(args):
+    """Side bench of the device quantisers in front of the path (not the headline metric): algorithmic GB/s against the measured HBM rate.
+    Rows of 128 bf16; per row the Q/K kernel moves 256 + 128 + 4 bytes, the V path 2 x 256 + 128 (a maximum pass and a conversion pass)."""
+    import torch
+    from amdgpu_rustdsl_b200 import Q_PRESCALE, _abi, quantize_qk, quantize_v
+    _abi.load()
+    dev = torch.device("cuda", 0)
+    rows = args.rows
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234)
+    x = torch.randn(rows, 128, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    out = torch.empty(rows, 128, dtype=torch.uint8, device=dev)
+    sc = torch.zeros(rows * 4, dtype=torch.uint8, device=dev)
+    vd = torch.zeros(1024, dtype=torch.float32, device=dev)
+    peaks = measured_peaks()
+    peak = float(peaks["hbm_gbs"]) if peaks else 6650.0
+    res = {}
+    for name, fn, nbytes in (("quantize_qk", lambda: quantize_qk(x, out, sc, mul=Q_PRESCALE), rows * 388), ("quantize_v", lambda: quantize_v(x, out, vd), rows * 640)):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        res[name] = {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "bytes": nbytes}
+    # CPU beside it: the oracle's restatement of the same rule on a sample of the rows (one core)
+    from oracle import oracle as O
+    n = min(rows, 65536)
+    xs = x[:n].float().cpu().numpy()
+    t0 = time.perf_counter()
+    O.quantize_rows(xs, Q_PRESCALE)
+    dt = time.perf_counter() - t0
+    line = {"metric": "MXFP8 quantiser (bf16 -> e4m3 + E8M0 per 32) algorithmic GB/s", "value": res["quantize_qk"]["gbs"], "unit": "GB/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": res["quantize_qk"]["ms"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16 -> u8 (e4m3) + u8 (E8M0)", "data": "synthetic (seeded standard-normal bf16)",
+            "config": {"workload": f"quantiser: {rows} rows of 128 bf16 ({rows * 256 / 2**20:.0f} MiB in, larger than L2)"},
+            "roofline": {"bound": "hbm", "achieved": res["quantize_qk"]["gbs"], "peak": peak, "unit": "GB/s", "frac": res["quantize_qk"]["gbs"] / peak,
+                         "traffic": None, "peak_source": "measured HBM copy rate (MEASURED_PEAKS.json)" if peaks else "fallback 6.65 TB/s"},
+            "quantize_v": {"ms_per_step": res["quantize_v"]["ms"], "achieved": res["quantize_v"]["gbs"], "frac": res["quantize_v"]["gbs"] / peak},
+            "cpu_baseline": {"value": n * 388 / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "port", "sample": f"oracle_quantize_rows on the first {n} rows"},
+            "gpu_launches": args.steps}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--quantizer", action="store_true", help="side bench: the device quantisers in front of the path (not the headline metric)")
+    ap.add_argument("--rows", type=int, default=4194304, help="rows of 128 bf16 for --quantizer")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
@@ -181,6 +231,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.quantizer:
+        return run_quantizer_bench(args)
 
     import torch
     import torch.distributed as dist
