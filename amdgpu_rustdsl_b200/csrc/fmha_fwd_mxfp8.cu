@@ -626,12 +626,13 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
         uint32_t g0 = 0, n = 0;   // tile counter at the item's first tile; ordinal of the item
         for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
-            // only the tile count and the last tile's valid keys stay live through the tile loop; the item is decoded again for the epilogue
-            // only the tile count, the number of tiles every row sees in full and the row's own key limit stay live through the tile loop;
-            // the item is decoded again for the epilogue
+            // the tile count, the number of tiles every row sees in full, the row's own key limit and the item's coordinates (for the
+            // epilogue's stores) stay live through the tile loop
             int n_tiles, j_full, row_lim;   // row_lim: this row's visible keys, counted from the item's first key
+            uint32_t it_row0, it_head, it_batch, it_split;
             {
                 const Item it = decode_item<kSplit, kCausal>(w, p);
+                it_row0 = it.row0, it_head = it.head, it_batch = it.batch, it_split = it.split;
                 n_tiles = it.n_tiles;
                 row_lim = static_cast<int>(it.key_hi - it.key_lo);
                 int first_lim = row_lim;   // the limit of the item's first row: the tiles below it need no mask
@@ -773,7 +774,9 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 stamp(ep_trace, par, 24 + static_cast<int>(n), 1);
                 if (ok && n_tiles > (((g_last & 1u) == par) ? 1 : 0)) ok = mbar_wait(bar_o_done(par ^ 1u), (g_theirs >> 1) & 1u, abort_flag);
                 stamp(ep_trace, par, 24 + static_cast<int>(n), 2);
-                if (ok) ok = wait_slot(ref_slot(g_last), g_last, ref);
+                // the row's final reference goes into the log-sum-exp only: group 0 fetches it, if it did not handle the last tile itself
+                const bool want_lse = wg == 0u && (kSplit || p.lse_nat != nullptr || tracing);
+                if (ok && want_lse && (g_last & 1u) != par) ok = wait_slot(ref_slot(g_last), g_last, ref);
                 if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
                 stamp(ep_trace, par, 24 + static_cast<int>(n), 3);
                 tc_fence_after_sync();
@@ -786,9 +789,8 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 tc_fence_before_sync();
                 mbar_arrive(bar_o_free);   // O and L are in registers: the next item's first P V may overwrite them
                 stamp(ep_trace, par, 24 + static_cast<int>(n), 4);
-                uint32_t w_again;          // opaque copy: keeps the compiler from holding the decoded item in registers across the tile loop
-                asm volatile("mov.u32 %0, %1;" : "=r"(w_again) : "r"(w));
-                const Item it = decode_item<kSplit, kCausal>(w_again, p);
+                Item it;   // what the stores need of the item, kept from the decode at the item's start
+                it.row0 = it_row0, it.head = it_head, it.batch = it_batch, it.split = it_split;
                 stamp(ep_trace, par, 24 + static_cast<int>(n), 5);
                 const float l = __uint_as_float(lv);
                 const float fin = vd / l;   // crates/amdgpu-stage/src/attention/state.rs:79-82
