@@ -125,8 +125,10 @@ def load():
     lib.fmha_mxfp8_device_status.argtypes = [C.POINTER(C.c_uint32)]
     lib.fmha_mxfp8_trace_attach.restype = C.c_int
     lib.fmha_mxfp8_trace_attach.argtypes = [C.c_void_p, C.c_size_t]
-    lib.fmha_mxfp8_probe_mma_peak.restype = C.c_int
-    lib.fmha_mxfp8_probe_mma_peak.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float)]
+    lib.fmha_mxfp8_mma_issue_ceiling.restype = C.c_int
+    lib.fmha_mxfp8_mma_issue_ceiling.argtypes = [C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float)]
+    lib.fmha_mxfp8_selftest_bounded_wait.restype = C.c_int
+    lib.fmha_mxfp8_selftest_bounded_wait.argtypes = [C.c_uint32, C.c_void_p, C.POINTER(C.c_uint32), C.POINTER(C.c_float)]
     _lib = lib
     return lib
 
@@ -134,7 +136,7 @@ def load():
 EXPORTS = (
     "fmha_mxfp8_kernel_name", "fmha_mxfp8_kernarg_size", "fmha_mxfp8_workgroup_size", "fmha_mxfp8_validate", "fmha_mxfp8_grid",
     "fmha_mxfp8_launch", "fmha_mxfp8_dispatch", "fmha_mxfp8_auto", "fmha_mxfp8_device_status", "fmha_mxfp8_trace_attach",
-    "fmha_mxfp8_probe_mma_peak", "fmha_mxfp8_kvsplit_static_scratch", "fmha_mxfp8_quantize_qk", "fmha_mxfp8_quantize_v",
+    "fmha_mxfp8_mma_issue_ceiling", "fmha_mxfp8_selftest_bounded_wait", "fmha_mxfp8_kvsplit_static_scratch", "fmha_mxfp8_quantize_qk", "fmha_mxfp8_quantize_v",
 )
 
 

@@ -10,7 +10,7 @@
 
 #include <cuda_bf16.h>
 
-namespace fmha {
+namespace b200mx {
 
 namespace {
 
@@ -27,7 +27,7 @@ __device__ __forceinline__ float4 ld_stream(const float4* p) {
 }
 
 __global__ void __launch_bounds__(256)
-fmha_kvsplit_combine_kernel(const float* __restrict__ ohat, const float* __restrict__ lse2, uint8_t* __restrict__ out,
+kvsplit_combine_kernel(const float* __restrict__ ohat, const float* __restrict__ lse2, uint8_t* __restrict__ out,
                             uint32_t rows_total, uint32_t splits) {
     const uint64_t ngroups = static_cast<uint64_t>(rows_total) * 16u;   // 16 groups of 8 elements per row
     for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < ngroups; t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
@@ -68,8 +68,8 @@ cudaError_t launch_combine(const float* ohat, const float* lse2, uint8_t* out, u
     const uint64_t cap = 148u * 8u * 4u;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    fmha_kvsplit_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(ohat, lse2, out, rows_total, splits);
+    kvsplit_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(ohat, lse2, out, rows_total, splits);
     return cudaGetLastError();
 }
 
-}  // namespace fmha
+}  // namespace b200mx

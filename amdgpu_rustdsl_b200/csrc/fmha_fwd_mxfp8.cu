@@ -40,10 +40,11 @@
 
 #include <cuda_bf16.h>
 
+#include <atomic>
 #include <type_traits>
 #include <cuda_fp8.h>
 
-namespace fmha {
+namespace b200mx {
 using namespace sm100;
 
 namespace {
@@ -147,22 +148,12 @@ __device__ __forceinline__ uint32_t fast_p_bits(uint32_t s, float c) {
     asm("fma.rn.sat.f32 %0, %1, 0f3D000000, %2;" : "=f"(t) : "f"(__uint_as_float(s)), "f"(c));   // s / 32 + c
     return __float_as_uint(t + 32768.0f);
 }
-// Every kMufuEvery-th P word takes two of its four values from the exp2 unit; all the other values come from the FMA pipe.
-#ifndef FMHA_MUFU_EVERY
-#define FMHA_MUFU_EVERY 1
-#endif
-constexpr int kMufuEvery = FMHA_MUFU_EVERY;
+// One P word of the long-sequence conversion: keys 0 and 1 from the exp2 unit, keys 2 and 3 from the FMA pipe.
 __device__ __forceinline__ uint32_t p_word_hybrid(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t s3, float sh, float c) {
     const uint32_t lo = cvt_e4m3x2(ex2_approx(__uint_as_float(s0) + sh), ex2_approx(__uint_as_float(s1) + sh));
     const uint32_t hi = __byte_perm(fast_p_bits(s2, c), fast_p_bits(s3, c), 0x0040);
     return __byte_perm(lo, hi, 0x5410);
 }
-__device__ __forceinline__ uint32_t p_word_fast(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t s3, float c) {
-    const uint32_t lo = __byte_perm(fast_p_bits(s0, c), fast_p_bits(s1, c), 0x0040);
-    const uint32_t hi = __byte_perm(fast_p_bits(s2, c), fast_p_bits(s3, c), 0x0040);
-    return __byte_perm(lo, hi, 0x5410);
-}
-
 __device__ __forceinline__ void st_shared_v2(uint32_t addr, uint32_t a, uint32_t b) {
     asm volatile("st.volatile.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
@@ -250,7 +241,7 @@ __device__ __forceinline__ Item decode_item(uint32_t w, const AttnParams& p) {
 // kLazy: the long-sequence softmax recipe. kCausal: the causal mask (never with kSplit).
 template <bool kSplit, bool kTrace, bool kLazy, bool kCausal>
 __global__ void __maxnreg__(kMaxRegs)
-fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const AttnParams p) {
     auto stamp = [](float* trace, int role, int tile, int slot) { stamp_t<kTrace>(trace, role, tile, slot); };
     extern __shared__ uint8_t smem_raw[];
@@ -734,9 +725,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         // a scheduling point every eight words: without them the converting warp keeps its scheduler for long stretches
                         // and the service warp that shares it falls behind (2-3 %)
                         if (c % 8 == 4) __syncwarp();
-                        pw[c] = kMufuEvery == 0 ? p_word(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3], sh)
-                                : (c % (kMufuEvery ? kMufuEvery : 1) == 0) ? p_word_hybrid(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3], sh, cf)
-                                                                           : p_word_fast(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3], cf);
+                        pw[c] = p_word_hybrid(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3], sh, cf);
                     }
                 } else {
 #pragma unroll
@@ -758,7 +747,9 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             int j = static_cast<int>((g0 ^ par) & 1u);
             for (; j < j_full; j += 2) tile(j, std::false_type{});
             if (j < n_tiles) tile(j, std::true_type{});
-            if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+            // The decision to leave is taken by the whole warpgroup at once (every thread reaches this barrier: a failed wait above only
+            // clears `ok`): the epilogue's named barriers below count all 128 threads, so no warp may go on while a sibling leaves.
+            if (!named_bar_all(1u + wg, 128u, ok)) { ok = false; break; }
 
             // ---- epilogue: O * v_descale / l; warpgroup wg stores head dims [kOutCols wg, kOutCols wg + kOutCols) ----
             {
@@ -777,7 +768,7 @@ fmha_fwd_mxfp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 // the row's final reference goes into the log-sum-exp only: group 0 fetches it, if it did not handle the last tile itself
                 const bool want_lse = wg == 0u && (kSplit || p.lse_nat != nullptr || tracing);
                 if (ok && want_lse && (g_last & 1u) != par) ok = wait_slot(ref_slot(g_last), g_last, ref);
-                if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+                if (!named_bar_all(1u + wg, 128u, ok)) { ok = false; break; }   // again uniform over the warpgroup
                 stamp(ep_trace, par, 24 + static_cast<int>(n), 3);
                 tc_fence_after_sync();
                 uint32_t lv;
@@ -892,17 +883,18 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
     (void)rows_per_cta;   // both logical block heights run as 128-row CTAs
     using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
     // [causal][recipe][trace][split]; the causal mask has no split form
-    static const Kernel kernels[16] = {fmha_fwd_mxfp8_kernel<false, false, false, false>, fmha_fwd_mxfp8_kernel<true, false, false, false>,
-                                       fmha_fwd_mxfp8_kernel<false, true, false, false>,  fmha_fwd_mxfp8_kernel<true, true, false, false>,
-                                       fmha_fwd_mxfp8_kernel<false, false, true, false>,  fmha_fwd_mxfp8_kernel<true, false, true, false>,
-                                       fmha_fwd_mxfp8_kernel<false, true, true, false>,   fmha_fwd_mxfp8_kernel<true, true, true, false>,
-                                       fmha_fwd_mxfp8_kernel<false, false, false, true>,  nullptr,
-                                       fmha_fwd_mxfp8_kernel<false, true, false, true>,   nullptr,
-                                       fmha_fwd_mxfp8_kernel<false, false, true, true>,   nullptr,
-                                       fmha_fwd_mxfp8_kernel<false, true, true, true>,    nullptr};
+    static const Kernel kernels[16] = {mxfp8_prefill_kernel<false, false, false, false>, mxfp8_prefill_kernel<true, false, false, false>,
+                                       mxfp8_prefill_kernel<false, true, false, false>,  mxfp8_prefill_kernel<true, true, false, false>,
+                                       mxfp8_prefill_kernel<false, false, true, false>,  mxfp8_prefill_kernel<true, false, true, false>,
+                                       mxfp8_prefill_kernel<false, true, true, false>,   mxfp8_prefill_kernel<true, true, true, false>,
+                                       mxfp8_prefill_kernel<false, false, false, true>,  nullptr,
+                                       mxfp8_prefill_kernel<false, true, false, true>,   nullptr,
+                                       mxfp8_prefill_kernel<false, false, true, true>,   nullptr,
+                                       mxfp8_prefill_kernel<false, true, true, true>,    nullptr};
     constexpr int kMaxDevices = 64;
-    static bool attr_done[kMaxDevices][16] = {};   // the shared-memory attribute is per device
-    static int sm_count[kMaxDevices] = {};
+    // per-device set-up done lazily from whichever thread launches first: plain flags would be a data race, and both steps are idempotent
+    static std::atomic<bool> attr_done[kMaxDevices][16];   // the shared-memory attribute is per device
+    static std::atomic<int> sm_count[kMaxDevices];
     // the long-sequence recipe from 4 key tiles of the whole sequence on (crates/amdgpu-stage/src/attention/state.rs:73-77), unless the
     // caller asks for the exact one; each recipe is its own instantiation, which halves the code of the tile loop
     const bool lazy_recipe = (p.SK + kKeys - 1) / kKeys >= 4 && !(p.flags & 0x2u);
@@ -913,16 +905,18 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
-    if (!attr_done[dev][which]) {
+    if (!attr_done[dev][which].load(std::memory_order_acquire)) {
         e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernels[which]), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
-        attr_done[dev][which] = true;
+        attr_done[dev][which].store(true, std::memory_order_release);
     }
-    if (sm_count[dev] == 0) {
+    int sms = sm_count[dev].load(std::memory_order_relaxed);
+    if (sms == 0) {
         int n = 0;
         e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
         if (e != cudaSuccess) return e;
-        sm_count[dev] = n > 0 ? n : 1;
+        sms = n > 0 ? n : 1;
+        sm_count[dev].store(sms, std::memory_order_relaxed);
     }
     // Persistent launch: one CTA per SM (a CTA takes all of an SM's tensor memory and nearly all of its shared memory), each walking the
     // work items blockIdx.x, blockIdx.x + gridDim.x, ...
@@ -931,7 +925,7 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
     const unsigned long long items = 1ull * q.n_qtiles * p.H * B * (split ? p.splits : 1u);
     if (items == 0 || items > 0xFFFFFFFFull) return cudaErrorInvalidValue;
     q.n_items = static_cast<uint32_t>(items);
-    const uint32_t ctas = q.n_items < static_cast<uint32_t>(sm_count[dev]) ? q.n_items : static_cast<uint32_t>(sm_count[dev]);
+    const uint32_t ctas = q.n_items < static_cast<uint32_t>(sms) ? q.n_items : static_cast<uint32_t>(sms);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas, 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
@@ -945,4 +939,4 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
     return cudaLaunchKernelEx(&cfg, kernels[which], tm_q, tm_k, tm_v, tm_o, q);
 }
 
-}  // namespace fmha
+}  // namespace b200mx

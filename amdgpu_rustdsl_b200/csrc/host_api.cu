@@ -3,13 +3,14 @@
 #include "../../include/fmha_mxfp8_abi.h"
 #include "kernels.h"
 
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
 
 namespace {
 
-using fmha::AttnParams;
+using b200mx::AttnParams;
 
 static_assert(sizeof(fmha_mxfp8_attn_args) == 656, "vs128/t128 kernarg size");
 static_assert(sizeof(fmha_mxfp8_kvsplit_args) == 648, "kvsplit kernarg size");
@@ -200,7 +201,7 @@ uint32_t log2_u32(uint32_t x) {
     return l;
 }
 
-float* g_trace = nullptr;
+std::atomic<float*> g_trace{nullptr};
 
 int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3], cudaStream_t stream) {
     // the common prefix of the three attention argument blocks
@@ -211,6 +212,8 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
     p.SK = a->s_kv_seq_len;
     p.H = a->s_q_head_num;
     if (a->s_gqa == 0 || p.H == 0 || p.S == 0 || p.SK == 0) return FMHA_MXFP8_E_KA_RANGE;
+    // the kernels find a head's KV head with a shift (crates/amdgpu-stage/src/components.rs:8-17): the group size must be a power of two that divides H
+    if ((a->s_gqa & (a->s_gqa - 1u)) != 0u || p.H % a->s_gqa != 0u) return FMHA_MXFP8_E_KA_RANGE;
     p.HK = p.H / a->s_gqa;
     p.gqa_shift = log2_u32(a->s_gqa);
     p.o = static_cast<uint8_t*>(a->ptr_o);
@@ -226,8 +229,8 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
     if ((p.flags & FMHA_MXFP8_FLAG_CAUSAL) && (split || p.SK < p.S)) return FMHA_MXFP8_E_ARG;   // causal: unsplit kernels, SK >= S
     p.v_blockscale = (p.flags & FMHA_MXFP8_FLAG_V_BLOCKSCALE) ? static_cast<const uint8_t*>(a->ext_ptr_v_blockscale) : nullptr;
     p.lse_nat = split ? nullptr : static_cast<float*>(a->ext_ptr_lse);
-    p.trace = g_trace;
-    p.status = fmha::device_status_word();
+    p.trace = g_trace.load(std::memory_order_relaxed);
+    p.status = b200mx::device_status_word();
     if (p.status == nullptr) return -static_cast<int>(cudaErrorInvalidSymbol);
     uint32_t B = grid[2];
     p.splits = 1;
@@ -247,9 +250,9 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
     CUtensorMap tq, tk, tv;
     int r = make_tile_map(&tq, a->ptr_q, p.S, p.H, B, a->s_Hs, a->s_Seqs, a->s_Bs, 128u);
     if (r) return r;
-    r = make_tile_map(&tk, a->ptr_k, p.SK, p.HK, B, a->s_k_Hs, a->s_k_Seqs, a->s_k_Bs, fmha::kKeysPerTile);
+    r = make_tile_map(&tk, a->ptr_k, p.SK, p.HK, B, a->s_k_Hs, a->s_k_Seqs, a->s_k_Bs, b200mx::kKeysPerTile);
     if (r) return r;
-    r = make_tile_map(&tv, a->ptr_v, p.SK, p.HK, B, a->s_v_Hs, a->s_v_Seqs, a->s_v_Bs, fmha::kKeysPerTile);
+    r = make_tile_map(&tv, a->ptr_v, p.SK, p.HK, B, a->s_v_Hs, a->s_v_Seqs, a->s_v_Bs, b200mx::kKeysPerTile);
     if (r) return r;
     CUtensorMap to;   // the output of the kernel's TMA stores: bf16 O, or the split kernel's f32 partials
     if (!split) {
@@ -259,20 +262,20 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
         r = make_partial_map(&to, p.ohat, p.S, p.H, B, p.splits);
     }
     if (r) return r;
-    const cudaError_t e = fmha::launch_attention(tq, tk, tv, to, p, B, split, kernel == FMHA_MXFP8_T128 ? 128u : 256u, stream);
+    const cudaError_t e = b200mx::launch_attention(tq, tk, tv, to, p, B, split, kernel == FMHA_MXFP8_T128 ? 128u : 256u, stream);
     return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }
 
 }  // namespace
 
-namespace fmha {
+namespace b200mx {
 __device__ uint32_t g_status_word = 0;
 uint32_t* device_status_word() {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
     return static_cast<uint32_t*>(p);
 }
-}  // namespace fmha
+}  // namespace b200mx
 
 extern "C" {
 
@@ -326,7 +329,7 @@ int fmha_mxfp8_launch(int kernel, const void* args, const uint32_t grid[3], void
     if (kernel == FMHA_MXFP8_COMBINE8H) {
         const fmha_mxfp8_combine_args* c = static_cast<const fmha_mxfp8_combine_args*>(args);
         if (c->d != 128 || c->rows_total == 0 || c->splits == 0) return FMHA_MXFP8_E_KA_RANGE;
-        const cudaError_t e = fmha::launch_combine(static_cast<const float*>(c->ptr_ohat), static_cast<const float*>(c->ptr_lse),
+        const cudaError_t e = b200mx::launch_combine(static_cast<const float*>(c->ptr_ohat), static_cast<const float*>(c->ptr_lse),
                                                    static_cast<uint8_t*>(c->ptr_out), c->rows_total, c->splits, st);
         return e == cudaSuccess ? 0 : -static_cast<int>(e);
     }
@@ -438,7 +441,7 @@ int fmha_mxfp8_quantize_qk(const void* x_bf16, uint64_t rows, float mul, void* o
     if (!x_bf16 || !out_e4m3 || !out_scales) return FMHA_MXFP8_E_ARG;
     if (rows == 0) return 0;
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) || (reinterpret_cast<uintptr_t>(out_e4m3) & 7u) || (reinterpret_cast<uintptr_t>(out_scales) & 3u)) return FMHA_MXFP8_E_ARG;
-    const cudaError_t e = fmha::launch_quantize_qk(x_bf16, rows, mul, out_e4m3, out_scales, static_cast<cudaStream_t>(stream));
+    const cudaError_t e = b200mx::launch_quantize_qk(x_bf16, rows, mul, out_e4m3, out_scales, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }
 
@@ -446,12 +449,12 @@ int fmha_mxfp8_quantize_v(const void* x_bf16, uint64_t n_elems, void* out_e4m3, 
     if (!x_bf16 || !out_e4m3 || !v_descale || (n_elems & 7u)) return FMHA_MXFP8_E_ARG;
     if (n_elems == 0) return 0;
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) || (reinterpret_cast<uintptr_t>(out_e4m3) & 7u) || (reinterpret_cast<uintptr_t>(v_descale) & 7u)) return FMHA_MXFP8_E_ARG;
-    const cudaError_t e = fmha::launch_quantize_v(x_bf16, n_elems, out_e4m3, static_cast<float*>(v_descale), static_cast<cudaStream_t>(stream));
+    const cudaError_t e = b200mx::launch_quantize_v(x_bf16, n_elems, out_e4m3, static_cast<float*>(v_descale), static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }
 
 int fmha_mxfp8_device_status(uint32_t* status) {
-    uint32_t* d = fmha::device_status_word();
+    uint32_t* d = b200mx::device_status_word();
     if (!d || !status) return FMHA_MXFP8_E_ARG;
     cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return -static_cast<int>(e);
@@ -461,28 +464,39 @@ int fmha_mxfp8_device_status(uint32_t* status) {
 
 int fmha_mxfp8_trace_attach(void* dev_buf, size_t bytes) {
     if (dev_buf && bytes < FMHA_MXFP8_TRACE_BYTES) return FMHA_MXFP8_E_EXTENT;
-    g_trace = static_cast<float*>(dev_buf);
+    g_trace.store(static_cast<float*>(dev_buf), std::memory_order_relaxed);
     return 0;
 }
 
-int fmha_mxfp8_probe_mma_peak(int variant, int iters, int ctas, void* stream, float* ms) {
-    if (variant < 0 || variant > 12 || iters < 1 || ctas < 1 || !ms) return FMHA_MXFP8_E_ARG;
+int fmha_mxfp8_mma_issue_ceiling(int iters, int ctas, void* stream, float* ms) {
+    if (iters < 2 || ctas < 1 || !ms) return FMHA_MXFP8_E_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    uint32_t* status = fmha::device_status_word();
+    uint32_t* status = b200mx::device_status_word();
     if (!status) return -static_cast<int>(cudaErrorInvalidSymbol);
     cudaEvent_t e0, e1;
     cudaError_t e = cudaEventCreate(&e0);
     if (e != cudaSuccess) return -static_cast<int>(e);
     e = cudaEventCreate(&e1);
     if (e != cudaSuccess) { cudaEventDestroy(e0); return -static_cast<int>(e); }
-    e = fmha::launch_mma_probe(variant, 8, ctas, status, st);   // warm-up
+    e = b200mx::launch_mma_issue_ceiling(8, ctas, status, st);   // warm-up
     if (e == cudaSuccess) e = cudaEventRecord(e0, st);
-    if (e == cudaSuccess) e = fmha::launch_mma_probe(variant, iters, ctas, status, st);
+    if (e == cudaSuccess) e = b200mx::launch_mma_issue_ceiling(iters, ctas, status, st);
     if (e == cudaSuccess) e = cudaEventRecord(e1, st);
     if (e == cudaSuccess) e = cudaEventSynchronize(e1);
     if (e == cudaSuccess) e = cudaEventElapsedTime(ms, e0, e1);
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+int fmha_mxfp8_selftest_bounded_wait(uint32_t budget_us, void* stream, uint32_t* word, float* ms) {
+    if (!word || !ms || budget_us == 0 || budget_us > 100000u) return FMHA_MXFP8_E_ARG;   // at most 0.1 s: this is a self-test, not a stall
+    int dev = 0, khz = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev);
+    if (e != cudaSuccess) return -static_cast<int>(e);
+    const long long cycles = static_cast<long long>(budget_us) * (khz > 0 ? khz : 1965000) / 1000;
+    e = b200mx::run_bounded_wait_selftest(cycles, static_cast<cudaStream_t>(stream), word, ms);
     return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }
 

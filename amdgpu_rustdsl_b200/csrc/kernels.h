@@ -4,7 +4,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
-namespace fmha {
+namespace b200mx {
 
 // Keys per K / V tile of the attention kernel = rows of the K and V tensor maps' boxes.
 constexpr int kKeysPerTile = 128;
@@ -46,8 +46,11 @@ cudaError_t launch_combine(const float* ohat, const float* lse2, uint8_t* out, u
 cudaError_t launch_quantize_qk(const void* x_bf16, unsigned long long rows, float mul, void* out_e4m3, void* out_scales, cudaStream_t stream);
 cudaError_t launch_quantize_v(const void* x_bf16, unsigned long long n_elems, void* out_e4m3, float* descale, cudaStream_t stream);
 
-cudaError_t launch_mma_probe(int variant, int iters, int ctas, uint32_t* status, cudaStream_t stream);
+cudaError_t launch_mma_issue_ceiling(int iters, int ctas, uint32_t* status, cudaStream_t stream);
+
+// wait_selftest.cu: one CTA lets a bounded wait run out (budget in SM cycles) and reports what happened in *word; *ms = kernel time.
+cudaError_t run_bounded_wait_selftest(long long budget_cycles, cudaStream_t stream, uint32_t* word, float* ms);
 
 uint32_t* device_status_word();   // address of the per-device status word (device pointer)
 
-}  // namespace fmha
+}  // namespace b200mx

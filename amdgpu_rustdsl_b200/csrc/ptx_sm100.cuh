@@ -54,15 +54,17 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 // (a whole launch takes well under 100 ms), small enough that a protocol bug ends by itself.
 constexpr long long kWaitBudgetCycles = 4000000000LL;
 
-// Waits for the phase with the given parity. Returns false when the budget ran out or when another
-// thread of the CTA already flagged a failure (`*abort_flag != 0`, a shared-memory word).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+// Waits for the phase with the given parity. Returns false when the budget (SM cycles) ran out or when another thread of the CTA
+// already flagged a failure (`*abort_flag != 0`, a shared-memory word). A failed try_wait has already been parked by the hardware
+// for a time slice, so the flag and the clock are only looked at on every eighth failure.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, long long budget = kWaitBudgetCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (true) {
+    for (uint32_t spins = 1;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 7u) != 0u) continue;
         if (*abort_flag != 0u) return false;
-        if (clock64() - t0 > kWaitBudgetCycles) {
+        if (clock64() - t0 > budget) {
             *abort_flag = 1u;
             return false;
         }
@@ -123,6 +125,19 @@ __device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async
 __device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // named barrier among `count` threads (a multiple of 32); id 0 is __syncthreads
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+// named barrier among `count` threads that also ANDs a predicate over them: every thread gets the same answer
+__device__ __forceinline__ bool named_bar_all(uint32_t id, uint32_t count, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 q, %3, 0;\n\t"
+        "bar.red.and.pred p, %1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"(id), "r"(count), "r"(static_cast<uint32_t>(pred))
+        : "memory");
+    return r != 0;
+}
 
 // ----------------------------------------------------------------------------------------------- TMEM
 // Allocation is a warp-wide instruction; `ncols` a power of two in [32, 512]. The base address lands in `*slot` (shared memory).

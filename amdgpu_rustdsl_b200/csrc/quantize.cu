@@ -12,7 +12,7 @@
 
 #include <cuda_bf16.h>
 
-namespace fmha {
+namespace b200mx {
 
 namespace {
 
@@ -130,4 +130,4 @@ cudaError_t launch_quantize_v(const void* x_bf16, unsigned long long n_elems, vo
     return cudaGetLastError();
 }
 
-}  // namespace fmha
+}  // namespace b200mx

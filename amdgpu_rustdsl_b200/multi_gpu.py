@@ -60,7 +60,8 @@ def local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, l
     sizes = _abi.BufferSizes(ptr_q=_nbytes(q), ptr_k=_nbytes(k_local), ptr_v=_nbytes(v_local), ptr_o=B * S * H * 256, ptr_q_descale=_nbytes(q_scale),
                              ptr_k_descale=_nbytes(k_scale_local), ptr_v_descale=_nbytes(v_scale), ptr_ohat=_nbytes(ohat), ptr_lse=_nbytes(lse))
     syms = _abi.Symbols(B=B, HK=HK, KL=0)
-    _check_launch(lib, _abi.KVSPLIT, a, sizes, _abi.grid3(math.ceil(S / 256), H, B), syms, stream, check)
+    with torch.cuda.device(q.device):
+        _check_launch(lib, _abi.KVSPLIT, a, sizes, _abi.grid3(math.ceil(S / 256), H, B), syms, stream, check)
 
 
 def combine_gathered(ohat_all, lse_all, out, world: int, *, stream=None, check=True):
@@ -74,7 +75,8 @@ def combine_gathered(ohat_all, lse_all, out, world: int, *, stream=None, check=T
         stream = torch.cuda.current_stream(out.device).cuda_stream
     c = _abi.CombineArgs(ptr_ohat=ohat_all.data_ptr(), ptr_lse=lse_all.data_ptr(), ptr_out=out.data_ptr(), rows_total=rows_total, d=D, splits=world)
     sizes = _abi.BufferSizes(ptr_ohat=_nbytes(ohat_all), ptr_lse=_nbytes(lse_all), ptr_out=_nbytes(out))
-    _check_launch(lib, _abi.COMBINE8H, c, sizes, _abi.grid3(max(1, math.ceil(rows_total * D / 2048)), 1, 1), None, stream, check)
+    with torch.cuda.device(out.device):
+        _check_launch(lib, _abi.COMBINE8H, c, sizes, _abi.grid3(max(1, math.ceil(rows_total * D / 2048)), 1, 1), None, stream, check)
 
 
 def exchange_partials(ohat, lse, ohat_all, lse_all, group=None):
@@ -131,3 +133,64 @@ def fmha_fwd_mxfp8_kv_sharded(q, k_local, v_local, q_scale, k_scale_local, v_sca
         return
     exchange_partials(ws["ohat"], ws["lse"], ws["ohat_all"], ws["lse_all"], group)
     combine_gathered(ws["ohat_all"], ws["lse_all"], out, world)
+
+
+class KvShardedPlan:
+    """Workspaces and schedule of the key-range-sharded forward for one problem size on one rank (`world` = 1 runs the same two
+    kernels without an exchange). `forward` runs a step; `timed_stages` runs steps with CUDA events between the stages."""
+
+    def __init__(self, rows_total: int, world: int, device, group=None):
+        self.rows_total, self.world, self.device, self.group = rows_total, world, device, group
+        self.ws = kv_sharded_workspace(rows_total, world, device, sliced=True)
+        self.sliced = "ohat_recv" in self.ws
+
+    def describe(self) -> str:
+        if self.world == 1:
+            return "one rank: split kernel over all keys + combine (splits = 1), no exchange"
+        if self.sliced:
+            return "key-range shards: split kernel -> NCCL all-to-all of the f32 partial row slices and their log-sum-exps -> combine of the own slice -> NCCL all-gather of the bf16 slices"
+        return "key-range shards: split kernel -> NCCL all-gather of the f32 partials -> combine of all rows"
+
+    def stages(self, q, k_local, v_local, q_scale, k_scale_local, v_scale, out):
+        """The step as a list of (name, callable) in stream order."""
+        ws, world = self.ws, self.world
+        st = [("split_kernel", lambda: local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ws["ohat"], ws["lse"], check=False))]
+        if world == 1:
+            st.append(("combine", lambda: combine_gathered(ws["ohat"].view(1, self.rows_total, D), ws["lse"].view(1, self.rows_total), out, 1, check=False)))
+        elif self.sliced:
+            st.append(("exchange_partials", lambda: exchange_row_slices(ws["ohat"], ws["lse"], ws["ohat_recv"], ws["lse_recv"], self.group)))
+            st.append(("combine", lambda: combine_gathered(ws["ohat_recv"], ws["lse_recv"], ws["out_slice"], world, check=False)))
+            st.append(("gather_output", lambda: gather_output_slices(out, ws["out_slice"], self.group)))
+        else:
+            st.append(("exchange_partials", lambda: exchange_partials(ws["ohat"], ws["lse"], ws["ohat_all"], ws["lse_all"], self.group)))
+            st.append(("combine", lambda: combine_gathered(ws["ohat_all"], ws["lse_all"], out, world, check=False)))
+        return st
+
+    def forward(self, q, k_local, v_local, q_scale, k_scale_local, v_scale, out):
+        for _, fn in self.stages(q, k_local, v_local, q_scale, k_scale_local, v_scale, out):
+            fn()
+
+    def timed_stages(self, q, k_local, v_local, q_scale, k_scale_local, v_scale, out, reps: int = 5):
+        """Median over `reps` steps of the time between the CUDA events that bracket each stage on the launching stream (ms). The ranks
+        are lined up by a barrier before each step, so that a stage's time is its own and not the wait for a late peer."""
+        import statistics
+        import torch
+        import torch.distributed as dist
+        st = self.stages(q, k_local, v_local, q_scale, k_scale_local, v_scale, out)
+        acc = {name: [] for name, _ in st}
+        for _ in range(reps):
+            if self.world > 1:
+                dist.barrier(group=self.group)
+            torch.cuda.synchronize(self.device)
+            evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(st) + 1)]
+            evs[0].record()
+            for i, (_, fn) in enumerate(st):
+                fn()
+                evs[i + 1].record()
+            torch.cuda.synchronize(self.device)
+            for i, (name, _) in enumerate(st):
+                acc[name].append(evs[i].elapsed_time(evs[i + 1]))
+        return {name: statistics.median(v) for name, v in acc.items()}
+
+    def close(self):
+        self.ws = None

@@ -28,11 +28,21 @@ def select_path(B: int, H: int, S: int, SK: int):
 _workspace = {}
 
 
-def _ws(key, nbytes, device):
-    """Grow-only per-stream workspace for the KV-split partials (the reference's ``_ws``, ops.py:72-85)."""
+def _ws_key(name, device, stream):
+    """Workspaces are per (device, stream): stream handle 0 (the default stream) exists on every device."""
+    return (name, device.index if device.index is not None else -1, int(stream))
+
+
+def _ws(name, nbytes, device, stream):
+    """Grow-only per-device, per-stream workspace for the KV-split partials (the reference's ``_ws``, ops.py:72-85, which frees the old
+    buffer with a synchronising ``hipFree``). Here the old buffer goes back to torch's caching allocator, which only orders its reuse
+    against torch's own current stream: a split or combine still running on ``stream`` is therefore waited for first."""
     import torch
+    key = _ws_key(name, device, stream)
     buf = _workspace.get(key)
     if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            (torch.cuda.ExternalStream(int(stream), device=device) if stream else torch.cuda.default_stream(device)).synchronize()
         buf = _workspace[key] = torch.empty(nbytes, dtype=torch.uint8, device=device)
     return buf
 
@@ -108,7 +118,12 @@ def fmha_fwd_mxfp8(q, k, v, q_scale, k_scale, v_scale, out, *, path="auto", spli
         splits = splits or 4
     if stream is None:
         stream = torch.cuda.current_stream(q.device).cuda_stream
+    # the library works on the current device (status word, SM count, kernel attributes, stream 0): make it the tensors' device
+    with torch.cuda.device(q.device):
+        return _launch_path(lib, q, k, v, q_scale, k_scale, v_scale, out, path, splits, stream, check, flags, v_blockscale, lse, B, S, H, SK, HK)
 
+
+def _launch_path(lib, q, k, v, q_scale, k_scale, v_scale, out, path, splits, stream, check, flags, v_blockscale, lse, B, S, H, SK, HK):
     sizes = _abi.BufferSizes(ptr_q=_nbytes(q), ptr_k=_nbytes(k), ptr_v=_nbytes(v), ptr_o=_nbytes(out), ptr_q_descale=_nbytes(q_scale),
                              ptr_k_descale=_nbytes(k_scale), ptr_v_descale=_nbytes(v_scale))
     syms = _abi.Symbols(B=B, HK=HK, KL=0)
@@ -120,8 +135,8 @@ def fmha_fwd_mxfp8(q, k, v, q_scale, k_scale, v_scale, out, *, path="auto", spli
     if path != "kvsplit" or splits not in (2, 4, 8):
         raise ValueError(f"fmha_fwd_mxfp8: unknown path {path!r} / splits {splits}")
     rows_total = B * S * H
-    ohat = _ws(("ohat", stream), splits * rows_total * D * 4, q.device)
-    lse_ws = _ws(("lse", stream), splits * rows_total * 4, q.device)
+    ohat = _ws("ohat", splits * rows_total * D * 4, q.device, stream)
+    lse_ws = _ws("lse", splits * rows_total * 4, q.device, stream)
     a = fill_common(_abi.KvSplitArgs(), q, k, v, q_scale, k_scale, v_scale, out, B, S, H, SK, HK, flags, v_blockscale, None)
     a.ptr_ohat, a.ptr_lse, a.kvs_splits, a.kvs_rows_total = ohat.data_ptr(), lse_ws.data_ptr(), splits, rows_total
     sizes.ptr_ohat, sizes.ptr_lse = splits * rows_total * D * 4, splits * rows_total * 4
@@ -159,7 +174,8 @@ def quantize_qk(x, out, out_scales, *, mul=1.0, stream=None):
         raise ValueError("quantize_qk: out must hold one byte per element and out_scales 4 bytes per row")
     if stream is None:
         stream = torch.cuda.current_stream(x.device).cuda_stream
-    rc = lib.fmha_mxfp8_quantize_qk(x.data_ptr(), rows, float(mul), out.data_ptr(), out_scales.data_ptr(), C.c_void_p(stream))
+    with torch.cuda.device(x.device):
+        rc = lib.fmha_mxfp8_quantize_qk(x.data_ptr(), rows, float(mul), out.data_ptr(), out_scales.data_ptr(), C.c_void_p(stream))
     if rc:
         raise RuntimeError(f"fmha_mxfp8_quantize_qk failed with code {rc}")
 
@@ -174,6 +190,7 @@ def quantize_v(x, out, v_descale, *, stream=None):
         raise ValueError("quantize_v: out must hold one byte per element and v_descale at least 8 bytes")
     if stream is None:
         stream = torch.cuda.current_stream(x.device).cuda_stream
-    rc = lib.fmha_mxfp8_quantize_v(x.data_ptr(), x.numel(), out.data_ptr(), v_descale.data_ptr(), C.c_void_p(stream))
+    with torch.cuda.device(x.device):
+        rc = lib.fmha_mxfp8_quantize_v(x.data_ptr(), x.numel(), out.data_ptr(), v_descale.data_ptr(), C.c_void_p(stream))
     if rc:
         raise RuntimeError(f"fmha_mxfp8_quantize_v failed with code {rc}")

@@ -245,6 +245,8 @@ int fmha_mxfp8_grid(int kernel, const void* args, const fmha_mxfp8_symbols* syms
  * Enqueue one kernel on a CUDA stream: replaces `launch(hipFunction_t, const Args&, dim3 grid, dim3 block, size_t lds, hipStream_t)`
  * (…_vs128_abi.h:205-210). `grid` is the logical grid above; the physical CTA grid is this library's business. `args` is read
  * before the call returns. `stream` is a cudaStream_t (NULL = default stream). Does not validate: call fmha_mxfp8_validate first.
+ * One restriction beyond the contract: s_gqa must be a power of two that divides s_q_head_num (the kernels find the KV head with a
+ * shift, as crates/amdgpu-stage/src/components.rs:8-17 does); any other group size is refused with FMHA_MXFP8_E_KA_RANGE.
  */
 int fmha_mxfp8_launch(int kernel, const void* args, const uint32_t grid[3], void* stream);
 
@@ -300,7 +302,7 @@ int fmha_mxfp8_kvsplit_static_scratch(const fmha_mxfp8_problem* prob, uint32_t s
 
 /*
  * The quantisers in front of the path: bf16 activations -> the MXFP8 operands the attention kernels take. The reference has no device
- * code for this step (SURVEY "next" item): the rule is the one its harness applies on the host (tests/gpu/ref_host.cpp:239-254).
+ * code for this step : the rule is the one its harness applies on the host (tests/gpu/ref_host.cpp:239-254).
  *   quantize_qk: x bf16 [rows][128] -> out e4m3 [rows][128], scales E8M0 [rows][4] (one per 32 head-dim elements):
  *                E8M0 = clamp(floor(log2 amax(x * mul)) - 8 + 127, 0, 254), element = e4m3_rne_sat(x * mul * 2^-(E8M0 - 127)).
  *                mul = log2(e) / sqrt(128) for Q (the softmax scale the kernels expect folded into Q), 1 for K.
@@ -329,16 +331,21 @@ int fmha_mxfp8_device_status(uint32_t* status);
 int fmha_mxfp8_trace_attach(void* dev_buf, size_t bytes);
 
 /*
- * Issue-only ceiling of the tensor pipe: every CTA issues `iters` x 4 tcgen05.mma (M128 N128 K32, e4m3) back to back on resident
- * operands. variant 0 = block-scaled, A from shared memory; 1 = block-scaled, A from tensor memory, B MN-major; 2 = kind::f8f6f4, A
- * from tensor memory, B MN-major; 3 = f8f6f4, A from shared memory, B MN-major; 4 = f8f6f4, A from tensor memory, B K-major;
- * 5 = f8f6f4, both from shared memory, K-major; 6 = the N16 row-sum MMA (counted as if it were N128); 7, 8 = N256 with one / two issuing
- * threads. Variants 0-8 rebuild their descriptors inside the loop and so measure that overhead too. 9-12 are tight loops on prepared
- * operands (f8f6f4): 9 = four dependent MMAs per tile, tiles alternating between two accumulators; 10 = the two accumulators interleaved;
- * 11 = one accumulator throughout; 12 = A from tensor memory, N144 (the P V shape). Writes the elapsed milliseconds (CUDA events on
- * `stream`) and returns 0. Variant 9 is the roofline's issue ceiling.
+ * Issue-only ceiling of the tensor pipe, the second denominator of the attention kernel's roofline fraction: each of `ctas` CTAs has one
+ * thread issue `iters` x 4 tcgen05.mma kind::f8f6f4 (M128 N128 K32, e4m3) back to back on resident operands, four dependent MMAs per
+ * tile, tiles alternating between two accumulators (the shape of the Q K^T stream). Writes the elapsed milliseconds (CUDA events on
+ * `stream`) and returns 0. No counterpart in the reference (its roofline is the vendor kernel measured in the same run,
+ * tools/port_gate.sh:163-187).
  */
-int fmha_mxfp8_probe_mma_peak(int variant, int iters, int ctas, void* stream, float* ms);
+int fmha_mxfp8_mma_issue_ceiling(int iters, int ctas, void* stream, float* ms);
+
+/*
+ * Self-test of the bounded waits: a one-CTA kernel waits `budget_us` microseconds (1 .. 100000) for an mbarrier arrival that never
+ * comes, gives up, and ends normally. *word: bit 0 = the wait ran out, bit 1 = a second warp left its own wait because of the raised
+ * flag (both expected: 3), bit 2 = a wait claimed success (never expected). *ms = the kernel's duration (CUDA events). The library's
+ * device status word is not touched. Synchronises `stream`. No counterpart in the reference, whose kernels wait without a limit.
+ */
+int fmha_mxfp8_selftest_bounded_wait(uint32_t budget_us, void* stream, uint32_t* word, float* ms);
 
 #ifdef __cplusplus
 }

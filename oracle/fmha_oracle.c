@@ -74,6 +74,17 @@ int oracle_num_threads(void) {
 #endif
 }
 
+/* Sets the number of OpenMP threads of the parallel loops below (a launcher may have exported OMP_NUM_THREADS=1); returns what is in force. */
+int oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
 size_t oracle_q_bytes(const oracle_shape* sh) { return (size_t)sh->B * sh->S * sh->H * D; }
 size_t oracle_kv_bytes(const oracle_shape* sh) { return (size_t)sh->B * sh->SK * sh->HK * D; }
 /* tests/gpu/ref_host.cpp:196-198: scale tensors plus zeroed slack of (256+256) / (512+128) rows of H*4 bytes */
@@ -235,10 +246,12 @@ int oracle_generate_v_blockscaled(const oracle_shape* sh, uint8_t* v, uint8_t* v
 /* ------------------------------------------------------------------------------------------------ fp64 oracle */
 
 /* tests/gpu/ref_host.cpp:438-471 (`check`), same operation order: dequantise, scores * ln 2, max-subtracted exp, normalise, * V descale. */
+/* `row_list` (may be NULL = rows 0 .. rows-1, as `check` does) names the query rows to evaluate: ref slot i holds row row_list[i]. */
 static int reference_impl(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
-                          float vdescale, const uint8_t* vscale, int rows, int causal, double* ref) {
+                          float vdescale, const uint8_t* vscale, int rows, const int* row_list, int causal, double* ref) {
     const int B = sh->B, H = sh->H, HK = sh->HK, S = sh->S, SK_all = sh->SK, GQA = sh->H / sh->HK;
-    const int rows_eff = rows < S ? rows : S;
+    const int rows_eff = row_list ? rows : (rows < S ? rows : S);
+    if (row_list) for (int i = 0; i < rows; ++i) if (row_list[i] < 0 || row_list[i] >= S) return -3;
     const double cpu_scale = 0.6931471805599453;
     const int nblk = (SK_all + 31) / 32;
     double tab[256];
@@ -250,7 +263,8 @@ static int reference_impl(const oracle_shape* sh, const uint8_t* q, const uint8_
 #pragma omp for collapse(3) schedule(dynamic, 1)
         for (int b = 0; b < B; ++b)
             for (int h = 0; h < H; ++h)
-                for (int i = 0; i < rows_eff; ++i) {
+                for (int slot = 0; slot < rows_eff; ++slot) {
+                    const int i = row_list ? row_list[slot] : slot;
                     const int hk = h / GQA;
                     /* the keys the row sees: all of them, or (causal, crates/amdgpu-stage/src/attention/attn3.rs:298-306) those below
                        min(i + SK - S + 1, SK) */
@@ -269,7 +283,7 @@ static int reference_impl(const oracle_shape* sh, const uint8_t* q, const uint8_
                     }
                     double den = 0.0;
                     for (int t = 0; t < SK; ++t) { sc[t] = exp(sc[t] - mx); den += sc[t]; }
-                    double* o = ref + (((size_t)b * H + h) * rows_eff + i) * D;
+                    double* o = ref + (((size_t)b * H + h) * rows_eff + slot) * D;
                     for (int d = 0; d < D; ++d) {
                         double acc = 0.0;
                         if (vscale) {
@@ -290,25 +304,32 @@ static int reference_impl(const oracle_shape* sh, const uint8_t* q, const uint8_
 
 int oracle_reference(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
                      float vdescale, const uint8_t* vscale, int rows, double* ref) {
-    return reference_impl(sh, q, k, v, qs, ks, vdescale, vscale, rows, 0, ref);
+    return reference_impl(sh, q, k, v, qs, ks, vdescale, vscale, rows, NULL, 0, ref);
 }
 
 int oracle_reference_causal(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
                             float vdescale, int rows, double* ref) {
-    return reference_impl(sh, q, k, v, qs, ks, vdescale, NULL, rows, 1, ref);
+    return reference_impl(sh, q, k, v, qs, ks, vdescale, NULL, rows, NULL, 1, ref);
+}
+
+int oracle_reference_rows(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
+                          float vdescale, const uint8_t* vscale, const int* row_list, int nrows, int causal, double* ref) {
+    if (!row_list || nrows < 1) return -3;
+    return reference_impl(sh, q, k, v, qs, ks, vdescale, vscale, nrows, row_list, causal, ref);
 }
 
 /* tests/gpu/ref_host.cpp:463-469: err = |got - ref|; bad when !(err <= 0.05 + 0.05 |ref|) (NaN counts); worst, mean, max|ref| */
-int oracle_compare(const oracle_shape* sh, const uint16_t* out, const double* ref, int rows, oracle_stats* st) {
+static int compare_impl(const oracle_shape* sh, const uint16_t* out, const double* ref, int rows, const int* row_list, oracle_stats* st) {
     const int B = sh->B, H = sh->H, S = sh->S;
-    const int rows_eff = rows < S ? rows : S;
+    const int rows_eff = row_list ? rows : (rows < S ? rows : S);
     double worst = 0.0, sum_abs = 0.0, max_ref = 0.0;
     uint64_t bad = 0, cnt = 0;
     for (int b = 0; b < B; ++b)
         for (int h = 0; h < H; ++h)
-            for (int i = 0; i < rows_eff; ++i)
+            for (int slot = 0; slot < rows_eff; ++slot)
                 for (int d = 0; d < D; ++d) {
-                    const double acc = ref[(((size_t)b * H + h) * rows_eff + i) * D + d];
+                    const int i = row_list ? row_list[slot] : slot;
+                    const double acc = ref[(((size_t)b * H + h) * rows_eff + slot) * D + d];
                     const double got = oracle_bf16_to_f32(out[(((size_t)b * S + i) * H + h) * D + d]);
                     const double err = fabs(got - acc);
                     if (err != err) worst = INFINITY; else worst = fmax(worst, err);
@@ -319,6 +340,15 @@ int oracle_compare(const oracle_shape* sh, const uint16_t* out, const double* re
                 }
     st->checked = cnt; st->bad = bad; st->worst_err = worst; st->mean_err = cnt ? sum_abs / cnt : 0.0; st->max_ref = max_ref;
     return 0;
+}
+
+int oracle_compare(const oracle_shape* sh, const uint16_t* out, const double* ref, int rows, oracle_stats* st) {
+    return compare_impl(sh, out, ref, rows, NULL, st);
+}
+
+int oracle_compare_rows(const oracle_shape* sh, const uint16_t* out, const double* ref, const int* row_list, int nrows, oracle_stats* st) {
+    if (!row_list || nrows < 1) return -3;
+    return compare_impl(sh, out, ref, nrows, row_list, st);
 }
 
 /* crates/amdgpu-graph/src/dispatch.rs:494-511 */
@@ -424,10 +454,11 @@ static void recipe_row(const recipe_t* rc, const float* qd, const uint8_t* kbase
     }
 }
 
-int oracle_recipe_forward(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
-                          float vdescale, int splits, int rows, uint16_t* out) {
+static int recipe_impl(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
+                       float vdescale, int splits, int rows, const int* row_list, uint16_t* out) {
     const int B = sh->B, H = sh->H, HK = sh->HK, S = sh->S, SK = sh->SK, GQA = sh->H / sh->HK;
-    const int rows_eff = rows < S ? rows : S;
+    const int rows_eff = row_list ? rows : (rows < S ? rows : S);
+    if (row_list) for (int i = 0; i < rows; ++i) if (row_list[i] < 0 || row_list[i] >= S) return -3;
     const int ntiles = (SK + 127) / 128;
     const recipe_t rc = recipe_for(ntiles);
     const int nsp = splits > 1 ? splits : 1;
@@ -438,7 +469,8 @@ int oracle_recipe_forward(const oracle_shape* sh, const uint8_t* q, const uint8_
 #pragma omp parallel for collapse(3) schedule(dynamic, 1)
     for (int b = 0; b < B; ++b)
         for (int h = 0; h < H; ++h)
-            for (int i = 0; i < rows_eff; ++i) {
+            for (int slot = 0; slot < rows_eff; ++slot) {
+                const int i = row_list ? row_list[slot] : slot;
                 const int hk = h / GQA;
                 float qd[D];
                 for (int kk = 0; kk < D; ++kk) {   /* Q scale bytes - 9: scores come out in units of 1/512 (block3.rs:138-147); folded below */
@@ -475,6 +507,17 @@ int oracle_recipe_forward(const oracle_shape* sh, const uint8_t* q, const uint8_
                 }
             }
     return 0;
+}
+
+int oracle_recipe_forward(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
+                          float vdescale, int splits, int rows, uint16_t* out) {
+    return recipe_impl(sh, q, k, v, qs, ks, vdescale, splits, rows, NULL, out);
+}
+
+int oracle_recipe_forward_rows(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
+                               float vdescale, int splits, const int* row_list, int nrows, uint16_t* out) {
+    if (!row_list || nrows < 1) return -3;
+    return recipe_impl(sh, q, k, v, qs, ks, vdescale, splits, nrows, row_list, out);
 }
 
 /* crates/amdgpu-tile/src/epilogue.rs:117-146 on f32 partials */

@@ -5,7 +5,7 @@
  *
  * Parity pin: the generators are bit-exact against the reference harness's own input dumps, and the fp64 oracle agrees with the
  * harness's `check` to its printed precision, both verified against the reference's tests/gpu/ref_host.cpp compiled from the
- * reference tree with a stub HIP runtime (oracle/build_ref.sh, tests/test_oracle_pin.py, fixtures in tests/golden/).
+ * reference tree with a stub HIP runtime (oracle/Makefile, tests/test_oracle_pin.py, fixtures in tests/golden/).
  * The recipe path (`oracle_recipe_*`) restates gfx950 kernel arithmetic whose exact instruction rounding the reference does not
  * state; it is pinned statistically, against the per-shape mean errors the reference publishes (docs/perf-matrix.md:29-53).
  */
@@ -62,6 +62,11 @@ int oracle_reference(const oracle_shape* sh, const uint8_t* q, const uint8_t* k,
 int oracle_reference_causal(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
                             float vdescale, int rows, double* ref);
 
+/* The same oracle for an explicit list of query rows (the reference's `check` only ever looks at the first REF_ROWS rows; the list lets
+ * the tests reach the query tiles behind the first). ref[((b*H + h)*nrows + i)*128 + d] belongs to row row_list[i]. `causal` as above. */
+int oracle_reference_rows(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
+                          float vdescale, const uint8_t* vscale, const int* row_list, int nrows, int causal, double* ref);
+
 typedef struct oracle_stats {
     uint64_t checked, bad;
     double worst_err, mean_err, max_ref;
@@ -69,6 +74,8 @@ typedef struct oracle_stats {
 
 /* The gate statistics of `check` for a bf16 output tensor [B,S,H,128] against `ref` from oracle_reference. */
 int oracle_compare(const oracle_shape* sh, const uint16_t* out_bf16, const double* ref, int rows, oracle_stats* st);
+
+int oracle_compare_rows(const oracle_shape* sh, const uint16_t* out_bf16, const double* ref, const int* row_list, int nrows, oracle_stats* st);
 
 /* Shape dispatch (crates/amdgpu-graph/src/dispatch.rs:494-511): path 0 = vs128, 1 = t128, 2 = kvsplit. */
 void oracle_dispatch(uint64_t b, uint64_t h, uint64_t s, uint64_t sk, int* path, uint32_t* splits);
@@ -83,6 +90,9 @@ void oracle_dispatch(uint64_t b, uint64_t h, uint64_t s, uint64_t sk, int* path,
 int oracle_recipe_forward(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
                           float vdescale, int splits, int rows, uint16_t* out_bf16);
 
+int oracle_recipe_forward_rows(const oracle_shape* sh, const uint8_t* q, const uint8_t* k, const uint8_t* v, const uint8_t* qs, const uint8_t* ks,
+                               float vdescale, int splits, const int* row_list, int nrows, uint16_t* out_bf16);
+
 /* CPU restatement of the combine kernel on f32 partials (epilogue.rs:117-146): out bf16 [rows_total][128]. */
 int oracle_combine_f32(const float* ohat, const float* lse2, uint32_t rows_total, uint32_t splits, uint16_t* out_bf16);
 
@@ -90,6 +100,7 @@ float oracle_bf16_to_f32(uint16_t x);
 uint16_t oracle_f32_to_bf16(float x);
 
 int oracle_num_threads(void);
+int oracle_set_threads(int n);
 
 #ifdef __cplusplus
 }

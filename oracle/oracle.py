@@ -98,13 +98,38 @@ def generate(mode: str, B: int, H: int, S: int, SK: int, HK: int | None = None, 
     return Inputs(B, H, HK, S, SK, q.reshape(B, S, H, 128), k.reshape(B, SK, HK, 128), v.reshape(B, SK, HK, 128), qs, ks, float(vd.value), vscale)
 
 
-def reference(inp: Inputs, rows: int, causal: bool = False) -> np.ndarray:
-    """fp64 oracle (ref_host.cpp:438-471) for the first ``rows`` query rows of every (b,h): float64 [B,H,rows_eff,128].
+def _row_list(rows):
+    """None for "the first n rows" (an int, the reference's REF_ROWS), else the explicit rows as a C int array."""
+    if isinstance(rows, (int, np.integer)):
+        return None
+    a = np.ascontiguousarray(np.asarray(list(rows), dtype=np.int32))
+    assert a.ndim == 1 and a.size > 0
+    return a
+
+
+def spread_rows(S: int, extra=()) -> list:
+    """Query rows that reach every kind of 128-row tile of a sequence: the first rows, both sides of the first tile edge, a tile in
+    the middle, and the last rows (a ragged last tile included)."""
+    cand = [0, 1, 31, 32, 126, 127, 128, 129, 255, 256, S // 2 - 1, S // 2, S // 2 + 77, (S // 128) * 128 - 1, (S // 128) * 128, S - 2, S - 1, *extra]
+    return sorted({r for r in cand if 0 <= r < S})
+
+
+def reference(inp: Inputs, rows, causal: bool = False) -> np.ndarray:
+    """fp64 oracle (ref_host.cpp:438-471) for the first ``rows`` query rows of every (b,h), or for the rows of a list:
+    float64 [B,H,rows_eff,128].
     ``causal``: row i sees the keys below min(i + SK - S + 1, SK) (the mask of the reference's per-tensor sibling family, attn3.rs:298-306)."""
     L = lib()
+    sh = inp.shape
+    rl = _row_list(rows)
+    if rl is not None:
+        ref = np.empty((inp.B, inp.H, rl.size, 128), np.float64)
+        rc = L.oracle_reference_rows(C.byref(sh), _p(inp.q), _p(inp.k), _p(inp.v), _p(inp.qs), _p(inp.ks), C.c_float(inp.vdescale),
+                                     _p(inp.vscale) if not causal else None, _p(rl), C.c_int(rl.size), C.c_int(1 if causal else 0), _p(ref))
+        if rc:
+            raise RuntimeError(f"oracle_reference_rows failed: {rc}")
+        return ref
     re = min(rows, inp.S)
     ref = np.empty((inp.B, inp.H, re, 128), np.float64)
-    sh = inp.shape
     if causal:
         rc = L.oracle_reference_causal(C.byref(sh), _p(inp.q), _p(inp.k), _p(inp.v), _p(inp.qs), _p(inp.ks), C.c_float(inp.vdescale),
                                        C.c_int(rows), _p(ref))
@@ -127,22 +152,38 @@ class Stats:
     max_ref: float
 
 
-def compare(inp: Inputs, out_bf16: np.ndarray, ref: np.ndarray, rows: int) -> Stats:
-    """The gate statistics of the reference's ``check`` (ref_host.cpp:463-469). ``out_bf16`` is uint16 [B,S,H,128]."""
+def compare(inp: Inputs, out_bf16: np.ndarray, ref: np.ndarray, rows) -> Stats:
+    """The gate statistics of the reference's ``check`` (ref_host.cpp:463-469). ``out_bf16`` is uint16 [B,S,H,128]; ``rows`` as in ``reference``."""
     L = lib()
     out = np.ascontiguousarray(out_bf16, dtype=np.uint16)
     assert out.size == inp.B * inp.S * inp.H * 128
+    ref = np.ascontiguousarray(ref, dtype=np.float64)
     st = _Stats()
     sh = inp.shape
-    L.oracle_compare(C.byref(sh), _p(out), _p(ref), C.c_int(rows), C.byref(st))
+    rl = _row_list(rows)
+    if rl is not None:
+        assert ref.shape[2] == rl.size
+        rc = L.oracle_compare_rows(C.byref(sh), _p(out), _p(ref), _p(rl), C.c_int(rl.size), C.byref(st))
+        if rc:
+            raise RuntimeError(f"oracle_compare_rows failed: {rc}")
+    else:
+        L.oracle_compare(C.byref(sh), _p(out), _p(ref), C.c_int(rows), C.byref(st))
     return Stats(int(st.checked), int(st.bad), float(st.worst_err), float(st.mean_err), float(st.max_ref))
 
 
-def recipe_forward(inp: Inputs, rows: int, splits: int = 0) -> np.ndarray:
-    """CPU restatement of the reference kernels' arithmetic ("the reference path" of the gate): uint16 bf16 [B,S,H,128]."""
+def recipe_forward(inp: Inputs, rows, splits: int = 0) -> np.ndarray:
+    """CPU restatement of the reference kernels' arithmetic ("the reference path" of the gate): uint16 bf16 [B,S,H,128], of which only
+    the asked rows (``rows`` as in ``reference``) are filled."""
     L = lib()
     out = np.zeros((inp.B, inp.S, inp.H, 128), np.uint16)
     sh = inp.shape
+    rl = _row_list(rows)
+    if rl is not None:
+        rc = L.oracle_recipe_forward_rows(C.byref(sh), _p(inp.q), _p(inp.k), _p(inp.v), _p(inp.qs), _p(inp.ks), C.c_float(inp.vdescale),
+                                          C.c_int(splits), _p(rl), C.c_int(rl.size), _p(out))
+        if rc:
+            raise RuntimeError(f"oracle_recipe_forward_rows failed: {rc}")
+        return out
     rc = L.oracle_recipe_forward(C.byref(sh), _p(inp.q), _p(inp.k), _p(inp.v), _p(inp.qs), _p(inp.ks), C.c_float(inp.vdescale), C.c_int(splits),
                                  C.c_int(rows), _p(out))
     if rc:
@@ -201,6 +242,13 @@ def dispatch(B, H, S, SK):
 
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
+
+
+def set_threads(n: int) -> int:
+    """Asks for ``n`` OpenMP threads in the oracle's loops (torch.distributed.run exports OMP_NUM_THREADS=1); returns the count in force."""
+    L = lib()
+    L.oracle_set_threads.restype = C.c_int
+    return int(L.oracle_set_threads(C.c_int(int(n))))
 
 
 def bf16_to_f32(x: np.ndarray) -> np.ndarray:

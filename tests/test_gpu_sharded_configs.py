@@ -1,0 +1,155 @@
+"""GPU parity of the two sharded configurations on one device, and of query tiles behind the first.
+
+The reference's `check` (tests/gpu/ref_host.cpp:438-471) only ever scores the first REF_ROWS rows of a head. With a persistent kernel
+whose rings and barriers run on across work items that leaves every query tile after the first compared only with other launches, so
+these tests score rows spread over the whole sequence (both sides of tile edges, the middle, a ragged end) with the same gate:
+mean_err <= 1.10 x the reference path's, bad <= the reference path's, every element within 2e-2 (normal data).
+
+The head-sharded configuration (B16 H64 S4096 over 8 GPUs) is run at the shape one of its 8 ranks gets, B16 H8 S4096. The
+key-range-sharded configuration (B1 H8 Sq8192 Skv131072 over 8 GPUs) is composed exactly as on 8 GPUs but on one: eight launches of the
+split kernel over the eight key ranges, each writing the partial of "its rank", then the combine kernel with splits = 8
+(amdgpu_rustdsl_b200/multi_gpu.py; algebra: crates/amdgpu-stage/src/components.rs:58-74, crates/amdgpu-tile/src/epilogue.rs:117-146).
+"""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+ABS_TOL_NORMAL = 2e-2
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _no_bounded_wait_ever_ran_out():
+    yield
+    from amdgpu_rustdsl_b200 import device_status
+    assert device_status() == 0, "a kernel gave up a bounded wait during this module"
+
+
+def _to_dev(inp):
+    d = {n: torch.from_numpy(getattr(inp, n)).cuda() for n in ("q", "k", "v", "qs", "ks")}
+    d["vs"] = torch.zeros(1024, dtype=torch.float32, device="cuda")
+    d["vs"][0] = inp.vdescale
+    return d
+
+
+def _bf16_bytes(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def _gate_rows(oracle, inp, out, rows, tag):
+    ref = oracle.reference(inp, rows)
+    ours = oracle.compare(inp, out, ref, rows)
+    theirs = oracle.compare(inp, oracle.recipe_forward(inp, rows, 0), ref, rows)
+    assert ours.bad <= theirs.bad, (tag, ours, theirs)
+    assert ours.mean_err <= 1.10 * theirs.mean_err, (tag, ours, theirs)
+    assert ours.worst_err <= ABS_TOL_NORMAL, (tag, ours, theirs)
+    return ours, theirs
+
+
+@pytest.mark.parametrize("shape,path,splits", [((4, 8, 8, 2048, 2048), "auto", None), ((1, 8, 8, 8192, 8192), "kvsplit", 8), ((1, 8, 8, 8192, 8192), "auto", None),
+                                               ((2, 4, 4, 1024, 1024), "auto", None), ((1, 8, 8, 2048, 2048), "auto", None), ((1, 2, 2, 1024, 1088), "vs128", None),
+                                               ((2, 8, 4, 700, 640), "vs128", None), ((3, 3, 3, 768, 1280), "t128", None), ((1, 2, 1, 200, 1337), "kvsplit", 2)],
+                         ids=["config2", "config3-split8", "B1H8S8192-auto", "B2H4S1024", "B1H8S2048-kvsplit4", "B1H2S1024SK1088", "B2H8S700-gqa2", "B3H3S768", "B1H2S200SK1337-gqa2"])
+def test_rows_spread_over_every_query_tile(oracle, shape, path, splits):
+    from amdgpu_rustdsl_b200 import fmha_fwd_mxfp8
+    B, H, HK, S, SK = shape
+    inp = oracle.generate("normal", B, H, S, SK, HK)
+    d = _to_dev(inp)
+    out = torch.full((B, S, H, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    fmha_fwd_mxfp8(d["q"], d["k"], d["v"], d["qs"], d["ks"], d["vs"], out, path=path, splits=splits)
+    torch.cuda.synchronize()
+    got = _bf16_bytes(out)
+    assert np.isfinite(oracle.bf16_to_f32(got)).all(), "every row of the output must be written"
+    _gate_rows(oracle, inp, got, oracle.spread_rows(S), (shape, path, splits))
+
+
+def test_head_sharded_config_at_the_shape_of_one_of_eight_ranks(oracle):
+    """B16 H64 S4096 dealt out over 8 GPUs by head gives every rank B16 H8 S4096 (multi_gpu.head_shard): 4096 work items on 148 SMs."""
+    from amdgpu_rustdsl_b200 import fmha_fwd_mxfp8, multi_gpu
+    (h0, h1), (k0, k1) = multi_gpu.head_shard(64, 64, 3, 8)
+    B, H, HK, S, SK = 16, h1 - h0, k1 - k0, 4096, 4096
+    assert (H, HK) == (8, 8)
+    inp = oracle.generate("normal", B, H, S, SK, HK)
+    d = _to_dev(inp)
+    out = torch.full((B, S, H, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ran = fmha_fwd_mxfp8(d["q"], d["k"], d["v"], d["qs"], d["ks"], d["vs"], out)
+    torch.cuda.synchronize()
+    assert ran == ("vs128", 0)
+    got = _bf16_bytes(out)
+    f = oracle.bf16_to_f32(got)
+    assert np.isfinite(f).all() and np.abs(f).max() <= inp.vdescale * 448.0
+    _gate_rows(oracle, inp, got, oracle.spread_rows(S), "head shard B16 H8 S4096")
+
+
+def test_key_range_sharded_config_composed_as_on_eight_gpus(oracle):
+    """B1 H8 Sq8192 Skv131072: eight split-kernel launches over the eight ranks' key ranges into ohat_all[r] / lse_all[r], then the
+    combine kernel with splits = 8, as amdgpu_rustdsl_b200.multi_gpu does across eight processes (there with an NCCL exchange between
+    the two steps, here with the partials already in one memory)."""
+    from amdgpu_rustdsl_b200 import multi_gpu
+    world = 8
+    B, H, HK, S, SK = 1, 8, 8, 8192, 131072
+    inp = oracle.generate("normal", B, H, S, SK, HK)
+    q, qs = torch.from_numpy(inp.q).cuda(), torch.from_numpy(inp.qs).cuda()
+    vs = torch.zeros(1024, dtype=torch.float32, device="cuda")
+    vs[0] = inp.vdescale
+    rows_total = B * S * H
+    ohat_all = torch.full((world, rows_total, 128), float("nan"), dtype=torch.float32, device="cuda")
+    lse_all = torch.full((world, rows_total), float("nan"), dtype=torch.float32, device="cuda")
+    k_all, v_all = torch.from_numpy(inp.k).cuda(), torch.from_numpy(inp.v).cuda()
+    ks_rows = inp.ks[: B * SK * HK * 4].reshape(B, SK, HK * 4)
+    for r in range(world):
+        lo, hi = multi_gpu.kv_range_shard(SK, r, world)
+        assert hi - lo == SK // world
+        ks_local = np.zeros(B * (hi - lo) * HK * 4 + 640 * H * 4, np.uint8)   # the rank's scale rows + the contract's slack
+        ks_local[: B * (hi - lo) * HK * 4] = ks_rows[:, lo:hi].reshape(-1)
+        multi_gpu.local_partials(q, k_all[:, lo:hi].contiguous(), v_all[:, lo:hi].contiguous(), qs, torch.from_numpy(ks_local).cuda(), vs,
+                                 ohat_all[r], lse_all[r])
+    out = torch.full((B, S, H, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    multi_gpu.combine_gathered(ohat_all, lse_all, out, world)
+    torch.cuda.synchronize()
+    assert torch.isfinite(ohat_all).all() and torch.isfinite(lse_all).all()
+    got = _bf16_bytes(out)
+    assert np.isfinite(oracle.bf16_to_f32(got)).all()
+    _gate_rows(oracle, inp, got, oracle.spread_rows(S), "key-range shards x 8")
+    # the same problem through one launch over all keys (one split): the key-range composition only reorders f32 sums
+    ohat1 = torch.empty(1, rows_total, 128, dtype=torch.float32, device="cuda")
+    lse1 = torch.empty(1, rows_total, dtype=torch.float32, device="cuda")
+    multi_gpu.local_partials(q, k_all, v_all, qs, torch.from_numpy(inp.ks).cuda(), vs, ohat1[0], lse1[0])
+    out1 = torch.empty_like(out)
+    multi_gpu.combine_gathered(ohat1, lse1, out1, 1)
+    torch.cuda.synchronize()
+    fa, fb = oracle.bf16_to_f32(_bf16_bytes(out1)).astype(np.float64), oracle.bf16_to_f32(got).astype(np.float64)
+    ulp = 2.0 ** (np.frexp(np.abs(fa).max())[1] - 8)
+    assert np.abs(fa - fb).max() <= ulp and np.abs(fa - fb).mean() <= 1e-4   # the split-vs-unsplit gate of tests/gpu/ref_host.cpp:603-637
+
+
+def test_bounded_wait_gives_up_and_leaves_the_device_usable(oracle, abi):
+    """A one-CTA kernel waits one millisecond for an mbarrier arrival that never comes: the wait must run out, raise the CTA's flag (a
+    second warp leaves its own wait because of it), and the kernel must end by itself. An attention launch before and after gives the
+    same bytes, and the library's status word stays clean (the self-test reports through a word of its own)."""
+    import ctypes as C
+    import time
+    from amdgpu_rustdsl_b200 import device_status, fmha_fwd_mxfp8
+    lib = abi.load()
+    inp = oracle.generate("normal", 1, 2, 512, 1024, 2)
+    d = _to_dev(inp)
+
+    def attend():
+        out = torch.full((1, 512, 2, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+        fmha_fwd_mxfp8(d["q"], d["k"], d["v"], d["qs"], d["ks"], d["vs"], out)
+        torch.cuda.synchronize()
+        return _bf16_bytes(out)
+
+    before = attend()
+    word, ms = C.c_uint32(0xFFFF), C.c_float(-1)
+    t0 = time.perf_counter()
+    rc = lib.fmha_mxfp8_selftest_bounded_wait(1000, None, C.byref(word), C.byref(ms))
+    wall = time.perf_counter() - t0
+    assert rc == 0
+    assert word.value == 3, f"status word {word.value:#x}: bit 0 = wait ran out, bit 1 = second warp saw the flag, bit 2 = a wait succeeded"
+    assert 0.9 <= ms.value < 100.0 and wall < 1.0, (ms.value, wall)
+    assert lib.fmha_mxfp8_selftest_bounded_wait(0, None, C.byref(word), C.byref(ms)) == 6        # refused: no budget
+    assert lib.fmha_mxfp8_selftest_bounded_wait(10**6, None, C.byref(word), C.byref(ms)) == 6    # refused: a second is not a self-test
+    assert device_status() == 0
+    assert np.array_equal(attend(), before)

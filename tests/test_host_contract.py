@@ -142,3 +142,13 @@ def test_launch_refuses_the_unimplemented_v_block_scales(abi):
         g = abi.grid3(*grid)
         raw = (C.c_char * len(buf)).from_buffer(buf)
         assert lib.fmha_mxfp8_launch(kernel, raw, g, None) == 6   # FMHA_MXFP8_E_ARG
+
+
+def test_workspace_keys_never_mix_devices_or_streams():
+    """The kvsplit workspace of the Python entry is per (device, stream): the default stream's handle is 0 on every GPU, so a key
+    without the device would hand one GPU's partial buffer to a launch on another."""
+    torch = pytest.importorskip("torch")
+    from amdgpu_rustdsl_b200 import ops
+    keys = {ops._ws_key(name, torch.device("cuda", d), st) for name in ("ohat", "lse") for d in (0, 1, 7) for st in (0, 0x7F001234)}
+    assert len(keys) == 2 * 3 * 2
+    assert ops._ws_key("ohat", torch.device("cuda", 0), 0) != ops._ws_key("ohat", torch.device("cuda", 1), 0)

@@ -128,3 +128,23 @@ def test_live_reference_harness_scores_the_oracle_output(oracle):
         assert int(m.group(2)) == 0 == st.bad
         assert _close(st.mean_err, m.group(4)) and _close(st.worst_err, m.group(3)) and _close(st.max_ref, m.group(5))
         assert st.mean_err <= 2.0 ** -8 * st.max_ref
+
+
+def test_row_lists_select_the_same_rows_as_the_prefix_form(oracle):
+    """The oracle, the recipe restatement and the gate statistics evaluated on an explicit list of query rows equal the reference's
+    "first REF_ROWS rows" form (tests/gpu/ref_host.cpp:438-471) on those rows: the list only lets the GPU tests reach later query tiles."""
+    import numpy as np
+    inp = oracle.generate("normal", 1, 2, 300, 512, 2)
+    rows = oracle.spread_rows(300)
+    assert rows[0] == 0 and rows[-1] == 299 and 128 in rows and 256 in rows
+    full = oracle.reference(inp, 300)
+    some = oracle.reference(inp, rows)
+    assert np.array_equal(some, full[:, :, rows])
+    assert np.array_equal(oracle.reference(inp, list(range(16))), oracle.reference(inp, 16))
+    assert np.array_equal(oracle.reference(inp, rows, causal=True), oracle.reference(inp, 300, causal=True)[:, :, rows])
+    rec_full, rec_some = oracle.recipe_forward(inp, 300), oracle.recipe_forward(inp, rows)
+    assert np.array_equal(rec_some[:, rows], rec_full[:, rows])
+    a, b = oracle.compare(inp, rec_some, some, rows), oracle.compare(inp, rec_full, full[:, :, rows], rows)
+    assert (a.checked, a.bad, a.worst_err, a.mean_err) == (b.checked, b.bad, b.worst_err, b.mean_err) and a.checked == len(rows) * 2 * 128
+    with pytest.raises(RuntimeError):
+        oracle.reference(inp, [300])
