@@ -54,14 +54,22 @@ constexpr int kKeys = kKeysPerTile; // keys per tile (128)
 constexpr int kStages = 4;          // depth of the K ring and of the V ring (freed separately: K after Q K^T, V after P V)
 // The four service warps get the lowest warp ids, one per scheduler (scheduler = warp % 4). Softmax = warps 4-19: a warp's TMEM lane
 // quadrant is warp % 4, so any four consecutive warps cover the 128 rows.
-constexpr int kMmaWarp = 0, kKProducerWarp = 1, kPvWarp = 2, kVProducerWarp = 3, kFirstSoftmaxWarp = 4;
+constexpr int kMmaWarp = 0, kKProducerWarp = 1, kPvWarp = 2, kVProducerWarp = 3, kFirstSoftmaxWarp = 4, kFirstEpilogueWarp = 12;
 // A softmax thread owns a whole score row of a tile: 128 scores in registers, read from tensor memory once. 4 service + 8 softmax warps;
 // the register file is 16 K registers per scheduler, so three warps per scheduler get 168 registers each.
 constexpr int kCols = 128;                  // score columns per softmax thread
-constexpr int kThreads = 32 * (4 + 8);
-constexpr int kMaxRegs = 168;
-constexpr int kServiceRegs = 80, kSoftmaxRegs = 208;   // after the roles part: 4 * 80 + 8 * 208 = 12 * 165.3
-static_assert(4 * kServiceRegs + 8 * kSoftmaxRegs <= 12 * kMaxRegs && kServiceRegs % 8 == 0 && kSoftmaxRegs % 8 == 0, "register file split");
+constexpr int kThreads = 32 * (4 + 8 + 4);   // 4 service warps, 8 softmax warps, 4 epilogue warps
+// The register file (64 K registers) is dealt out unevenly once the roles part: every thread starts with kMaxRegs, the service and the
+// epilogue warpgroups give most of theirs back and the two softmax warpgroups take them.
+#ifndef MXA_SERVICE_REGS
+#define MXA_SERVICE_REGS 56
+#define MXA_SOFTMAX_REGS 200
+#define MXA_EPILOGUE_REGS 56
+#endif
+constexpr int kMaxRegs = 128;
+constexpr int kServiceRegs = MXA_SERVICE_REGS, kSoftmaxRegs = MXA_SOFTMAX_REGS, kEpilogueRegs = MXA_EPILOGUE_REGS;
+static_assert(4 * kServiceRegs + 8 * kSoftmaxRegs + 4 * kEpilogueRegs <= 16 * kMaxRegs && kServiceRegs % 8 == 0 && kSoftmaxRegs % 8 == 0 && kEpilogueRegs % 8 == 0,
+              "register file split");
 constexpr uint32_t kTileBytes = 128 * 128;   // one e4m3 tile
 constexpr uint32_t kSfBytes = 512;           // 128 rows x 4 scale bytes
 
@@ -94,10 +102,11 @@ struct SmemLayout {
     static constexpr uint32_t sfq = ostage + 2 * 16384;
     static constexpr uint32_t sfk = sfq + 2 * kSfBytes;
     static constexpr uint32_t xref = sfk + kStages * kSfBytes;   // [tile parity 2][row 128] x {reference bits, tile counter}
-    static constexpr uint32_t bars = xref + 2 * 128 * 8;
+    static constexpr uint32_t xfin = xref + 2 * 128 * 8;          // [item parity 2][row 128]: the row's reference after the item's last tile
+    static constexpr uint32_t bars = xfin + 2 * 128 * 4;
     // barriers (8 bytes each): q_full[2], q_empty[2], k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], s_free[2],
-    // p_full[2], o_done[2], o_free
-    static constexpr uint32_t n_bars = 4 + 4 * kStages + 9;
+    // p_full[2], o_done[2], o_free, o_full
+    static constexpr uint32_t n_bars = 4 + 4 * kStages + 10;
     static constexpr uint32_t tmem_slot = bars + 8 * n_bars;
     static constexpr uint32_t abort_flag = tmem_slot + 4;
     static constexpr uint32_t total = abort_flag + 4;
@@ -266,6 +275,7 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     auto bar_p_full = [&](int b) { return bar0 + 8u * (8 + 4 * kStages + b); };
     auto bar_o_done = [&](int b) { return bar0 + 8u * (10 + 4 * kStages + b); };
     const uint32_t bar_o_free = bar0 + 8u * (12 + 4 * kStages);
+    const uint32_t bar_o_full = bar0 + 8u * (13 + 4 * kStages);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + SmemLayout::tmem_slot);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + SmemLayout::abort_flag);
 
@@ -297,7 +307,8 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             mbar_init(bar_v_full(st), 1);
             mbar_init(bar_v_empty(st), 1);
         }
-        mbar_init(bar_o_free, 2 * kRows);
+        mbar_init(bar_o_free, kRows);   // the epilogue warpgroup's 128 threads
+        mbar_init(bar_o_full, 1);
         fence_mbar_init();
     }
     if (threadIdx.x < 256) {
@@ -573,6 +584,7 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         stamp(mma_trace, 3, static_cast<int>(g), 3);
                         tc_commit(bar_v_empty(st));
                         tc_commit(bar_o_done(g & 1u));
+                        if (i == n_tiles - 1) tc_commit(bar_o_full);   // the item's O and L are complete: over to the epilogue warpgroup
                         stamp(mma_trace, 3, static_cast<int>(g), 4);
                     }
                     ++g;
@@ -582,9 +594,9 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         __syncwarp();
     }
-    } else {
+    } else if (warp < kFirstEpilogueWarp) {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
-        // =========================================================== softmax + epilogue ===========================================================
+        // =========================================================== softmax ===========================================================
         // Two warpgroups: wg = parity = which tiles (counter g = parity mod 2) and which S / P buffer. Thread r of a group owns query row r.
         const uint32_t st_id = threadIdx.x - 32u * kFirstSoftmaxWarp;
         const uint32_t wg = st_id >> 7;
@@ -615,15 +627,13 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // the reference the row has after tile g, published by the thread that handled it
         auto ref_slot = [&](uint32_t g) { return xref + 8u * ((g & 1u) * 128u + r); };
 
+        const bool want_fin = kSplit || p.lse_nat != nullptr || cta_traced;   // does anything read the final reference?
         uint32_t g0 = 0, n = 0;   // tile counter at the item's first tile; ordinal of the item
         for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
-            // the tile count, the number of tiles every row sees in full, the row's own key limit and the item's coordinates (for the
-            // epilogue's stores) stay live through the tile loop
+            // the tile count, the number of tiles every row sees in full and the row's own key limit stay live through the tile loop
             int n_tiles, j_full, row_lim;   // row_lim: this row's visible keys, counted from the item's first key
-            uint32_t it_row0, it_head, it_batch, it_split;
             {
                 const Item it = decode_item<kSplit, kCausal>(w, p);
-                it_row0 = it.row0, it_head = it.head, it_batch = it.batch, it_split = it.split;
                 n_tiles = it.n_tiles;
                 row_lim = static_cast<int>(it.key_hi - it.key_lo);
                 int first_lim = row_lim;   // the limit of the item's first row: the tiles below it need no mask
@@ -694,6 +704,9 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 const float old_ref = ref;
                 ref = move ? cand : ref;
                 st_shared_v2(ref_slot(g), __float_as_uint(ref), g);
+                // the item's last tile leaves the row's final reference for the epilogue warpgroup's log-sum-exp (ordered before this
+                // thread's arrive on p_full, which the last P V, and through it the epilogue's o_full, come after)
+                if (want_fin && j == n_tiles - 1) *reinterpret_cast<volatile float*>(smem_gen + SmemLayout::xfin + 4u * ((n & 1u) * 128u + r)) = ref;
                 f = move ? ex2_approx(old_ref - ref) : 1.0f;   // 0 on the first tile (old reference -inf); an exact power of two for integer references
                 stamp(st_trace, par, static_cast<int>(g), 4);
                 // P V of this parity's previous tile must be done before its P columns are overwritten (and, observed in order, this keeps
@@ -747,124 +760,135 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             int j = static_cast<int>((g0 ^ par) & 1u);
             for (; j < j_full; j += 2) tile(j, std::false_type{});
             if (j < n_tiles) tile(j, std::true_type{});
-            // The decision to leave is taken by the whole warpgroup at once (every thread reaches this barrier: a failed wait above only
-            // clears `ok`): the epilogue's named barriers below count all 128 threads, so no warp may go on while a sibling leaves.
-            if (!named_bar_all(1u + wg, 128u, ok)) { ok = false; break; }
-
-            // ---- epilogue: O * v_descale / l; warpgroup wg stores head dims [kOutCols wg, kOutCols wg + kOutCols) ----
-            {
-                constexpr int kOutCols = 64;
-                const float vd = __ldg(p.v_descale);   // issued ahead of the waits below
-                float* ep_trace = (cta_traced && r == 0) ? p.trace : nullptr;   // epilogue stamps: tile index 24 + item ordinal
-                stamp(ep_trace, par, 24 + static_cast<int>(n), 0);
-                const uint32_t g_last = g0 + static_cast<uint32_t>(n_tiles) - 1u;
-                // this parity's last tile of the item first (its barrier is observed phase by phase), then the other parity's
-                const uint32_t g_mine = ((g_last & 1u) == par) ? g_last : g_last - 1u;
-                const uint32_t g_theirs = ((g_last & 1u) == par) ? g_last - 1u : g_last;
-                if (n_tiles > (((g_last & 1u) == par) ? 0 : 1)) ok = mbar_wait(bar_o_done(par), (g_mine >> 1) & 1u, abort_flag);
-                stamp(ep_trace, par, 24 + static_cast<int>(n), 1);
-                if (ok && n_tiles > (((g_last & 1u) == par) ? 1 : 0)) ok = mbar_wait(bar_o_done(par ^ 1u), (g_theirs >> 1) & 1u, abort_flag);
-                stamp(ep_trace, par, 24 + static_cast<int>(n), 2);
-                // the row's final reference goes into the log-sum-exp only: group 0 fetches it, if it did not handle the last tile itself
-                const bool want_lse = wg == 0u && (kSplit || p.lse_nat != nullptr || tracing);
-                if (ok && want_lse && (g_last & 1u) != par) ok = wait_slot(ref_slot(g_last), g_last, ref);
-                if (!named_bar_all(1u + wg, 128u, ok)) { ok = false; break; }   // again uniform over the warpgroup
-                stamp(ep_trace, par, 24 + static_cast<int>(n), 3);
-                tc_fence_after_sync();
-                uint32_t lv;
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(lv) : "r"(t_l) : "memory");
-                uint32_t o[kOutCols];
+            // a failed wait above only clears `ok`; the warp leaves as one
+            if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+            g0 += static_cast<uint32_t>(n_tiles);
+        }
+    } else {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kEpilogueRegs));
+        // =========================================================== epilogue ===========================================================
+        // One warpgroup, thread r = TMEM lane r = query row r of the item. It takes an item's O and L out of tensor memory as soon as the
+        // item's last P V is done (o_full) and hands the columns back (o_free) before it normalises and stores, so that the softmax
+        // warpgroups go straight on with the next item's tiles and the next item's first P V only waits for the read-out.
+        // O * v_descale / l (crates/amdgpu-stage/src/attention/state.rs:79-82) leaves through the two 16 KB staging tiles (128-byte
+        // swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8)) and TMA stores, which also drop the rows past the sequence
+        // (block3.rs:194); a thread owns a row, so direct stores would touch 32 different lines per instruction.
+        const uint32_t r = 32u * (static_cast<uint32_t>(warp) & 3u) + static_cast<uint32_t>(lane);
+        const uint32_t lane_base = (static_cast<uint32_t>(warp & 3) * 32u) << 16;
+        const uint32_t t_o = tmem + kColO + lane_base, t_l = tmem + kColL + lane_base;
+        const uint32_t stg = smem_base + SmemLayout::ostage;
+        const bool issuer = threadIdx.x == 32u * kFirstEpilogueWarp;
+        const bool want_fin = kSplit || p.lse_nat != nullptr || cta_traced;
+        constexpr uint32_t kEpiBar = 1u;   // named barrier of the 128 epilogue threads
+        const float vd = __ldg(p.v_descale);
+        uint32_t n = 0;
+        bool ok = true;
+        for (uint32_t w = blockIdx.x; w < n_items; w += stride, ++n) {
+            const Item it = decode_item<kSplit, kCausal>(w, p);
+            const bool tracing = cta_traced && n == 0;
+            const bool dumping = tracing && !(p.flags & 0x4u);
+            float* ep_trace = (cta_traced && r == 0) ? p.trace : nullptr;   // epilogue stamps: tile index 24 + item ordinal
+            stamp(ep_trace, 0, 24 + static_cast<int>(n), 0);
+            ok = mbar_wait(bar_o_full, n & 1u, abort_flag);
+            if (issuer && n > 0) bulk_wait_group_read0();   // the previous item's stores have read the staging tiles out
+            // one barrier: the staging tiles are free, and the decision to go on is the whole warpgroup's (the named barriers below count
+            // all 128 threads, so no warp may leave while a sibling goes on)
+            if (!named_bar_all(kEpiBar, 128u, ok)) break;
+            tc_fence_after_sync();
+            stamp(ep_trace, 0, 24 + static_cast<int>(n), 1);
+            uint32_t lv;
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(lv) : "r"(t_l) : "memory");
+            const float ref_fin = want_fin ? *reinterpret_cast<volatile float*>(smem_gen + SmemLayout::xfin + 4u * ((n & 1u) * 128u + r)) : 0.0f;
+            tmem_wait_ld();
+            const float l = __uint_as_float(lv);
+            const float fin = vd / l;
+            const uint32_t row = it.row0 + r;
+            if (tracing) {
+                p.trace[32768 + r] = l;
+                p.trace[32768 + 128 + r] = ref_fin;
+            }
+            if (!kSplit) {
+                // bf16 output: four 32-column chunks, all staged before the stores go out; O is free after the last read
 #pragma unroll
-                for (int c = 0; c < kOutCols / 32; ++c) tmem_ld32(tmem + kColO + lane_base + kOutCols * wg + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&o[32 * c]));
-                tmem_wait_ld();
-                tc_fence_before_sync();
-                mbar_arrive(bar_o_free);   // O and L are in registers: the next item's first P V may overwrite them
-                stamp(ep_trace, par, 24 + static_cast<int>(n), 4);
-                Item it;   // what the stores need of the item, kept from the decode at the item's start
-                it.row0 = it_row0, it.head = it_head, it.batch = it_batch, it.split = it_split;
-                stamp(ep_trace, par, 24 + static_cast<int>(n), 5);
-                const float l = __uint_as_float(lv);
-                const float fin = vd / l;   // crates/amdgpu-stage/src/attention/state.rs:79-82
-                const uint32_t row = it.row0 + r;
-                const bool row_ok = row < p.S;   // rows past the sequence are computed on clamped scales and not stored (block3.rs:194)
-                if (tracing && wg == 0) {
-                    p.trace[32768 + r] = l;
-                    p.trace[32768 + 128 + r] = ref;
-                }
-                if (dumping) {
-#pragma unroll
-                    for (int c = 0; c < kOutCols; ++c) p.trace[16384 + r * 128 + kOutCols * wg + c] = __uint_as_float(o[c]);
-                }
-                if (kSplit) {
-                    // The split kernel's f32 partial goes the same way as the bf16 output below: the warpgroup's 128 x 64 f32 tile in two
-                    // halves of 32 columns (128 bytes per row) through its 16 KB staging tile, one TMA store each.
-                    const uint32_t stg = smem_base + SmemLayout::ostage + wg * 16384u;
-                    const bool issuer = (st_id & 127u) == 0u;
-#pragma unroll
-                    for (int hh = 0; hh < 2; ++hh) {
-                        if (n > 0 || hh > 0) {   // the previous store must have read the staging tile out
-                            if (issuer) bulk_wait_group_read0();
-                            named_bar_sync(1u + wg, 128u);
-                        }
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stg + r * 128u + ((static_cast<uint32_t>(c) ^ (r & 7u)) << 4)),
-                                         "f"(__uint_as_float(o[32 * hh + 4 * c]) * fin), "f"(__uint_as_float(o[32 * hh + 4 * c + 1]) * fin),
-                                         "f"(__uint_as_float(o[32 * hh + 4 * c + 2]) * fin), "f"(__uint_as_float(o[32 * hh + 4 * c + 3]) * fin) : "memory");
-                        }
-                        fence_proxy_async_smem();
-                        named_bar_sync(1u + wg, 128u);
-                        if (issuer) {
-                            tma_store_5d(&tm_o, stg, static_cast<int>(kOutCols * wg + 32 * hh), static_cast<int>(it.head), static_cast<int>(it.row0),
-                                         static_cast<int>(it.batch), static_cast<int>(it.split));
-                            bulk_commit_group();
-                        }
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t o[32];
+                    tmem_ld32(t_o + 32 * c, o);
+                    tmem_wait_ld();
+                    if (c == 3) {
+                        tc_fence_before_sync();
+                        mbar_arrive(bar_o_free);   // O and L are out: the next item's first P V may overwrite them
+                        stamp(ep_trace, 0, 24 + static_cast<int>(n), 2);
                     }
-                }
-                if (!kSplit) {
-                    // A thread owns a row, so direct stores would touch 32 different lines per instruction. The warpgroup's 128 x 64 bf16
-                    // tile goes through shared memory (128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8)) and out with
-                    // one TMA store, which also leaves out the rows past the sequence.
-                    const uint32_t stg = smem_base + SmemLayout::ostage + wg * 16384u;
-                    const bool issuer = (st_id & 127u) == 0u;
-                    if (n > 0) {   // the previous item's store must have read the staging tile out
-                        if (issuer) bulk_wait_group_read0();
-                        named_bar_sync(1u + wg, 128u);
-                    }
+                    if (dumping) {
 #pragma unroll
-                    for (int c = 0; c < kOutCols / 8; ++c) {
+                        for (int e = 0; e < 32; ++e) p.trace[16384 + r * 128 + 32 * c + e] = __uint_as_float(o[e]);
+                    }
+                    const uint32_t tile_base = stg + (static_cast<uint32_t>(c) >> 1) * 16384u + r * 128u;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {   // 8 columns = 16 bytes of bf16 per store
                         uint32_t wv[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[8 * c + 2 * e]) * fin, __uint_as_float(o[8 * c + 2 * e + 1]) * fin);
+                            const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[8 * q4 + 2 * e]) * fin, __uint_as_float(o[8 * q4 + 2 * e + 1]) * fin);
                             wv[e] = *reinterpret_cast<const uint32_t*>(&b2);
                         }
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stg + r * 128u + ((static_cast<uint32_t>(c) ^ (r & 7u)) << 4)),
+                        const uint32_t chunk = static_cast<uint32_t>((c & 1) * 4 + q4);
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(tile_base + ((chunk ^ (r & 7u)) << 4)),
                                      "r"(wv[0]), "r"(wv[1]), "r"(wv[2]), "r"(wv[3]) : "memory");
                     }
+                }
+                fence_proxy_async_smem();
+                named_bar_sync(kEpiBar, 128u);
+                if (issuer) {
+                    tma_store_4d(&tm_o, stg, 0, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
+                    tma_store_4d(&tm_o, stg + 16384u, 64, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
+                    bulk_commit_group();
+                }
+            } else {
+                // f32 partial: four pieces of 32 columns (128 bytes per row), alternating between the two staging tiles; a tile is written
+                // again once the store that last used it has read it out
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t o[32];
+                    tmem_ld32(t_o + 32 * c, o);
+                    tmem_wait_ld();
+                    if (c == 3) {
+                        tc_fence_before_sync();
+                        mbar_arrive(bar_o_free);
+                        stamp(ep_trace, 0, 24 + static_cast<int>(n), 2);
+                    }
+                    if (c >= 2) {   // the store of piece c - 2 (all but the newest group) must have read its tile out
+                        if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        named_bar_sync(kEpiBar, 128u);
+                    }
+                    const uint32_t tile_base = stg + static_cast<uint32_t>(c & 1) * 16384u + r * 128u;
+#pragma unroll
+                    for (int q4 = 0; q4 < 8; ++q4) {
+                        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(tile_base + ((static_cast<uint32_t>(q4) ^ (r & 7u)) << 4)),
+                                     "f"(__uint_as_float(o[4 * q4]) * fin), "f"(__uint_as_float(o[4 * q4 + 1]) * fin),
+                                     "f"(__uint_as_float(o[4 * q4 + 2]) * fin), "f"(__uint_as_float(o[4 * q4 + 3]) * fin) : "memory");
+                    }
                     fence_proxy_async_smem();
-                    named_bar_sync(1u + wg, 128u);
+                    named_bar_sync(kEpiBar, 128u);
                     if (issuer) {
-                        tma_store_4d(&tm_o, stg, static_cast<int>(kOutCols * wg), static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
+                        tma_store_5d(&tm_o, stg + static_cast<uint32_t>(c & 1) * 16384u, 32 * c, static_cast<int>(it.head), static_cast<int>(it.row0),
+                                     static_cast<int>(it.batch), static_cast<int>(it.split));
                         bulk_commit_group();
                     }
                 }
-                if (row_ok) {
-                    if (wg == 0) {
-                        const float lse2 = ref - kPOffset + lg2_approx(l);   // log2 of sum_j 2^(s_j)
-                        if (kSplit) {
-                            const size_t prow = static_cast<size_t>(it.split) * p.rows_total + (static_cast<size_t>(it.batch) * p.S + row) * p.H + it.head;
-                            p.lse2[prow] = lse2;
-                        } else if (p.lse_nat != nullptr) {
-                            p.lse_nat[(static_cast<size_t>(it.batch) * p.H + it.head) * p.S + row] = lse2 * 0.6931471805599453f;
-                        }
-                    }
+            }
+            if (row < p.S && want_fin) {   // rows past the sequence are computed on clamped scales and not stored (block3.rs:194)
+                const float lse2 = ref_fin - kPOffset + lg2_approx(l);   // log2 of sum_j 2^(s_j)
+                if (kSplit) {
+                    const size_t prow = static_cast<size_t>(it.split) * p.rows_total + (static_cast<size_t>(it.batch) * p.S + row) * p.H + it.head;
+                    p.lse2[prow] = lse2;
+                } else if (p.lse_nat != nullptr) {
+                    p.lse_nat[(static_cast<size_t>(it.batch) * p.H + it.head) * p.S + row] = lse2 * 0.6931471805599453f;
                 }
             }
-            stamp((cta_traced && r == 0) ? p.trace : nullptr, par, 24 + static_cast<int>(n), 6);
-            g0 += static_cast<uint32_t>(n_tiles);
+            stamp(ep_trace, 0, 24 + static_cast<int>(n), 3);
         }
-        if ((st_id & 127u) == 0u) bulk_wait_group_read0();   // the staging tiles have been read out before the CTA gives its shared memory back
+        if (issuer) bulk_wait_group_read0();   // the staging tiles have been read out before the CTA gives its shared memory back
     }
 
     // ---- teardown ----

@@ -29,7 +29,7 @@ sys.path.insert(0, ROOT)
 from oracle import oracle as O  # noqa: E402
 from tests import contract_cases as CC  # noqa: E402
 
-# B, H, HK, S, SK: the reference's gate shapes that are cheap on the CPU (tools/port_gate.sh:77-78) plus BASELINE config 1
+# B, H, HK, S, SK: the reference's gate shapes that are cheap on the CPU (tools/port_gate.sh:77-78) plus the small B1 H2 S256 case
 SHAPES = [(1, 1, 1, 256, 256), (1, 2, 2, 512, 512), (1, 2, 2, 512, 2048), (3, 3, 3, 768, 1280), (1, 4, 4, 300, 512), (2, 8, 4, 700, 640),
           (1, 16, 4, 256, 1024), (1, 2, 2, 256, 1000), (2, 4, 4, 300, 129), (1, 8, 4, 512, 100), (1, 2, 2, 1024, 1088), (1, 4, 4, 77, 1),
           (1, 2, 1, 200, 1337), (1, 2, 2, 256, 256)]
