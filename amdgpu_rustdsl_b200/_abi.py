@@ -16,6 +16,8 @@ PATH_IDS = {v: k for k, v in PATH_NAMES.items()}
 FLAG_V_BLOCKSCALE = 0x1
 FLAG_EXACT_REBASE = 0x2
 FLAG_CAUSAL = 0x8
+FLAG_F32_PARTIALS = 0x10
+FLAG_NO_TAIL_SPLIT = 0x20
 TRACE_BYTES = 4 * (16384 + 16384 + 256 + 4096 + 2048)
 STATIC_SCRATCH_MAX_ROW_SPLITS = 65536   # FMHA_MXFP8_STATIC_SCRATCH_MAX_ROW_SPLITS
 
@@ -117,6 +119,8 @@ def load():
     lib.fmha_mxfp8_auto.argtypes = [C.POINTER(Problem), C.c_int, C.c_uint32, C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_uint32), C.c_char_p, C.c_size_t]
     lib.fmha_mxfp8_kvsplit_static_scratch.restype = C.c_int
     lib.fmha_mxfp8_kvsplit_static_scratch.argtypes = [C.POINTER(Problem), C.c_uint32, C.c_void_p, C.c_char_p, C.c_size_t]
+    lib.fmha_mxfp8_combine_f32.restype = C.c_int
+    lib.fmha_mxfp8_combine_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]
     lib.fmha_mxfp8_quantize_qk.restype = C.c_int
     lib.fmha_mxfp8_quantize_qk.argtypes = [C.c_void_p, C.c_uint64, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.fmha_mxfp8_quantize_v.restype = C.c_int
@@ -136,7 +140,7 @@ def load():
 EXPORTS = (
     "fmha_mxfp8_kernel_name", "fmha_mxfp8_kernarg_size", "fmha_mxfp8_workgroup_size", "fmha_mxfp8_validate", "fmha_mxfp8_grid",
     "fmha_mxfp8_launch", "fmha_mxfp8_dispatch", "fmha_mxfp8_auto", "fmha_mxfp8_device_status", "fmha_mxfp8_trace_attach",
-    "fmha_mxfp8_mma_issue_ceiling", "fmha_mxfp8_selftest_bounded_wait", "fmha_mxfp8_kvsplit_static_scratch", "fmha_mxfp8_quantize_qk", "fmha_mxfp8_quantize_v",
+    "fmha_mxfp8_mma_issue_ceiling", "fmha_mxfp8_selftest_bounded_wait", "fmha_mxfp8_kvsplit_static_scratch", "fmha_mxfp8_quantize_qk", "fmha_mxfp8_quantize_v", "fmha_mxfp8_combine_f32",
 )
 
 

@@ -3,9 +3,10 @@
 // Reference: crates/amdgpu-kernels/src/fmha/io.rs:164-185 (kernel), crates/amdgpu-tile/src/epilogue.rs:89-167 (combine_splits).
 // Each thread owns 8 consecutive output elements of one row and walks the splits once with an online maximum:
 //   m' = max(m, lse_s); a = 2^(m - m'); w = 2^(lse_s - m'); den = den*a + w; acc_k = acc_k*a + w*Ohat_s[k]; out = acc/den -> bf16.
-// Partials here are f32 (the workspace contract sizes them for f32: tests/gpu/generated/..._kvsplit_abi.h:196), so one thread
-// reads 32 bytes per split as two 16-byte loads and writes one 16-byte store; a warp covers two whole rows (1 KiB per split).
-// HBM-bound: bytes = splits*rows*(512 + 4) + rows*256.
+// Partials are f16 like the reference's (crates/amdgpu-kernels/src/fmha/io.rs:83-85: half-precision Ohat inside an allocation the
+// contract sizes for f32, tests/gpu/generated/..._kvsplit_abi.h:196): one thread reads 16 bytes per split and writes one 16-byte store.
+// A second instantiation reads f32 partials (two 16-byte loads per split), for partials that were exchanged between GPUs.
+// HBM-bound: bytes = splits*rows*(256 + 4) + rows*256 (f16), splits*rows*(512 + 4) + rows*256 (f32).
 #include "kernels.h"
 
 #include <cuda_bf16.h>
@@ -26,9 +27,21 @@ __device__ __forceinline__ float4 ld_stream(const float4* p) {
     return v;
 }
 
+__device__ __forceinline__ uint4 ld_stream_u4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float2 h2_to_f2(uint32_t h2) {
+    float2 f;
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.f32.f16 %0, lo;\n\tcvt.f32.f16 %1, hi;\n\t}" : "=f"(f.x), "=f"(f.y) : "r"(h2));
+    return f;
+}
+
+// kF32: the partial rows are f32 (512 bytes per row; partials that crossed GPUs), else f16 (256 bytes per row, the reference's format).
+template <bool kF32>
 __global__ void __launch_bounds__(256)
-kvsplit_combine_kernel(const float* __restrict__ ohat, const float* __restrict__ lse2, uint8_t* __restrict__ out,
-                            uint32_t rows_total, uint32_t splits) {
+kvsplit_combine_kernel(const void* __restrict__ ohat, const float* __restrict__ lse2, uint8_t* __restrict__ out, uint32_t rows_total, uint32_t splits) {
     const uint64_t ngroups = static_cast<uint64_t>(rows_total) * 16u;   // 16 groups of 8 elements per row
     for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < ngroups; t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
         const uint64_t row = t >> 4;
@@ -39,13 +52,21 @@ kvsplit_combine_kernel(const float* __restrict__ ohat, const float* __restrict__
         for (uint32_t s = 0; s < splits; ++s) {
             const uint64_t prow = static_cast<uint64_t>(s) * rows_total + row;
             const float ls = __ldg(lse2 + prow);
-            const float4* src = reinterpret_cast<const float4*>(ohat + (static_cast<uint64_t>(s) * rows_total * 16u + t) * 8u);
-            const float4 v0 = ld_stream(src), v1 = ld_stream(src + 1);
+            float v[8];
+            if (kF32) {
+                const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(ohat) + (static_cast<uint64_t>(s) * rows_total * 16u + t) * 8u);
+                const float4 v0 = ld_stream(src), v1 = ld_stream(src + 1);
+                v[0] = v0.x; v[1] = v0.y; v[2] = v0.z; v[3] = v0.w; v[4] = v1.x; v[5] = v1.y; v[6] = v1.z; v[7] = v1.w;
+            } else {
+                const uint4 h = ld_stream_u4(reinterpret_cast<const uint4*>(ohat) + (static_cast<uint64_t>(s) * rows_total * 16u + t));
+                const float2 a0 = h2_to_f2(h.x), a1 = h2_to_f2(h.y), a2 = h2_to_f2(h.z), a3 = h2_to_f2(h.w);
+                v[0] = a0.x; v[1] = a0.y; v[2] = a1.x; v[3] = a1.y; v[4] = a2.x; v[5] = a2.y; v[6] = a3.x; v[7] = a3.y;
+            }
             const float mn = fmaxf(m, ls);
             const float a = ex2f(m - mn), w = ex2f(ls - mn);
             den = den * a + w;
-            acc[0] = acc[0] * a + w * v0.x; acc[1] = acc[1] * a + w * v0.y; acc[2] = acc[2] * a + w * v0.z; acc[3] = acc[3] * a + w * v0.w;
-            acc[4] = acc[4] * a + w * v1.x; acc[5] = acc[5] * a + w * v1.y; acc[6] = acc[6] * a + w * v1.z; acc[7] = acc[7] * a + w * v1.w;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] = acc[k] * a + w * v[k];
             m = mn;
         }
         const float rd = 1.0f / den;
@@ -61,14 +82,15 @@ kvsplit_combine_kernel(const float* __restrict__ ohat, const float* __restrict__
 
 }  // namespace
 
-cudaError_t launch_combine(const float* ohat, const float* lse2, uint8_t* out, uint32_t rows_total, uint32_t splits, cudaStream_t stream) {
+cudaError_t launch_combine(const void* ohat, bool f32_partials, const float* lse2, uint8_t* out, uint32_t rows_total, uint32_t splits, cudaStream_t stream) {
     const uint64_t ngroups = static_cast<uint64_t>(rows_total) * 16u;
     uint64_t blocks = (ngroups + 255u) / 256u;
     // cap the grid at a few waves of 148 SMs x 8 resident blocks; the grid-stride loop covers the rest
     const uint64_t cap = 148u * 8u * 4u;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    kvsplit_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(ohat, lse2, out, rows_total, splits);
+    if (f32_partials) kvsplit_combine_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(ohat, lse2, out, rows_total, splits);
+    else kvsplit_combine_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(ohat, lse2, out, rows_total, splits);
     return cudaGetLastError();
 }
 

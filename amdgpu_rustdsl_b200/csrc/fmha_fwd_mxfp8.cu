@@ -41,6 +41,8 @@
 #include <cuda_bf16.h>
 
 #include <atomic>
+#include <cstdlib>
+#include <mutex>
 #include <type_traits>
 #include <cuda_fp8.h>
 
@@ -73,7 +75,8 @@ static_assert(4 * kServiceRegs + 8 * kSoftmaxRegs + 4 * kEpilogueRegs <= 16 * kM
 constexpr uint32_t kTileBytes = 128 * 128;   // one e4m3 tile
 constexpr uint32_t kSfBytes = 512;           // 128 rows x 4 scale bytes
 
-constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256, kColL = 384, kColP0 = 400, kColP1 = 432, kColSfQ = 464, kColSfK0 = 468, kColSfK1 = 472;
+constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256, kColL = 384, kColP0 = 400, kColP1 = 432, kColSfQ = 464, kColSfK0 = 468, kColSfK1 = 472,
+                   kColSfP = 476, kColSfV = 480;   // V block scales (extension): P's constant factors [476,480), V's factors [480,484) + the ones columns' [484,488)
 constexpr uint32_t kTmemCols = 512;
 
 // P = 2^(s - ref + kPOffset): the row's reference maps to 2^kPOffset.
@@ -88,6 +91,8 @@ constexpr float kPOffset = 5.0f;
 constexpr float kLazyThreshold = 3.5f;
 constexpr float kFollowWindow = 11.0f;
 constexpr uint32_t kFlagCausal = 0x8u;   // FMHA_MXFP8_FLAG_CAUSAL: selects the kCausal instantiations
+constexpr uint32_t kFlagF32Partials = 0x10u;   // FMHA_MXFP8_FLAG_F32_PARTIALS: the split kernel's partial rows are f32, not f16
+constexpr uint32_t kFlagNoTailSplit = 0x20u;   // FMHA_MXFP8_FLAG_NO_TAIL_SPLIT: never cut the last round's items in two
 
 struct SmemLayout {
     // all tile buffers are 1024-byte aligned (128-byte swizzle atom = 8 rows x 128 B)
@@ -101,12 +106,18 @@ struct SmemLayout {
     static constexpr uint32_t ostage = ones + 4096;
     static constexpr uint32_t sfq = ostage + 2 * 16384;
     static constexpr uint32_t sfk = sfq + 2 * kSfBytes;
-    static constexpr uint32_t xref = sfk + kStages * kSfBytes;   // [tile parity 2][row 128] x {reference bits, tile counter}
-    static constexpr uint32_t xfin = xref + 2 * 128 * 8;          // [item parity 2][row 128]: the row's reference after the item's last tile
-    static constexpr uint32_t bars = xfin + 2 * 128 * 4;
+    // [tile counter % 4][row 128] x {reference bits, tile counter}. Four slots per row, not two: a softmax warpgroup goes from an item's
+    // last tile straight on to the next item's first, which reads no reference, so it may publish tile g while the other group has yet to
+    // read what tile g - 2 left for its tile g - 1
+    static constexpr uint32_t sfv = sfk + kStages * kSfBytes;    // V block scales of a key tile (extension), same 32 x 16-byte pattern as the K scales
+    static constexpr uint32_t sf_one = sfv + kStages * kSfBytes;  // 512 bytes of E8M0 1.0: the factors of P and of the ones columns
+    static constexpr uint32_t xref = sf_one + kSfBytes;
+    static constexpr uint32_t xfin = xref + 4 * 128 * 8;          // [item parity 2][row 128]: the row's reference after the item's last tile
+    static constexpr uint32_t xstat = xfin + 2 * 128 * 4;         // [row 128] x {row sum, reference} of the partner's half item (launches as pairs)
+    static constexpr uint32_t bars = xstat + 128 * 8;
     // barriers (8 bytes each): q_full[2], q_empty[2], k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], s_free[2],
-    // p_full[2], o_done[2], o_free, o_full
-    static constexpr uint32_t n_bars = 4 + 4 * kStages + 10;
+    // p_full[2], o_done[2], o_free, o_full, ref_ready[4], peer_rdy, peer_data
+    static constexpr uint32_t n_bars = 4 + 4 * kStages + 16;
     static constexpr uint32_t tmem_slot = bars + 8 * n_bars;
     static constexpr uint32_t abort_flag = tmem_slot + 4;
     static constexpr uint32_t total = abort_flag + 4;
@@ -193,13 +204,19 @@ __device__ __forceinline__ void scale_tmem32(uint32_t taddr, float f) {
 // One unit of work of the persistent kernel: 128 query rows of one (batch, head) against the key range of one split.
 struct Item {
     uint32_t row0, head, batch, split, kv_head, key_lo, key_hi;
+    uint32_t half;   // 0: the item's whole key range; 1 / 2: its first / second half, to be merged with the other CTA of the cluster
     int n_tiles;
 };
 
-template <bool kSplit, bool kCausal>
+template <bool kSplit, bool kCausal, bool kPair>
 __device__ __forceinline__ Item decode_item(uint32_t w, const AttnParams& p) {
     // w = (z * H + head) * n_qtiles + q tile: neighbouring CTAs work on neighbouring row blocks of one head, whose K / V they share in L2
     Item it;
+    it.half = 0;
+    if (kPair && w >= p.tail_base) {   // a unit of the cut last round: half (w - tail_base) % 2 of item tail_base + (w - tail_base) / 2
+        it.half = 1u + ((w - p.tail_base) & 1u);
+        w = p.tail_base + ((w - p.tail_base) >> 1);
+    }
     uint32_t x = w % p.n_qtiles, yz = w / p.n_qtiles;
     constexpr bool causal = kCausal && !kSplit;
     if (causal) {
@@ -237,6 +254,16 @@ __device__ __forceinline__ Item decode_item(uint32_t w, const AttnParams& p) {
     // causal (crates/amdgpu-stage/src/attention/attn3.rs:298-306): row i sees the keys below min(i + SK - S + 1, SK); the item's last row decides
     if (causal) it.key_hi = min(p.SK, it.row0 + kRows + (p.SK - p.S));
     it.n_tiles = (it.key_hi > it.key_lo) ? static_cast<int>((it.key_hi - it.key_lo + kKeys - 1) / kKeys) : 0;
+    if (it.half != 0u) {   // whole tiles [0, ceil(n / 2)) to the first half, the rest (and a ragged end) to the second
+        const int first = (it.n_tiles + 1) / 2;
+        if (it.half == 1u) {
+            it.key_hi = it.key_lo + static_cast<uint32_t>(first) * kKeys;
+            it.n_tiles = first;
+        } else {
+            it.key_lo += static_cast<uint32_t>(first) * kKeys;
+            it.n_tiles -= first;
+        }
+    }
     return it;
 }
 
@@ -248,7 +275,7 @@ __device__ __forceinline__ Item decode_item(uint32_t w, const AttnParams& p) {
 // epilogue of the item before has read O out (o_free).
 // kTrace = false compiles every diagnostic (tile dumps, time stamps) out of the tile loop: the production launches use that variant.
 // kLazy: the long-sequence softmax recipe. kCausal: the causal mask (never with kSplit).
-template <bool kSplit, bool kTrace, bool kLazy, bool kCausal>
+template <bool kSplit, bool kTrace, bool kLazy, bool kCausal, bool kPair, bool kVbs>
 __global__ void __maxnreg__(kMaxRegs)
 mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const AttnParams p) {
@@ -276,11 +303,15 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     auto bar_o_done = [&](int b) { return bar0 + 8u * (10 + 4 * kStages + b); };
     const uint32_t bar_o_free = bar0 + 8u * (12 + 4 * kStages);
     const uint32_t bar_o_full = bar0 + 8u * (13 + 4 * kStages);
+    // pairs: "this CTA's exchange area is free" (one arrival, from the partner with the first half) and "the partner's half item has
+    // landed in this CTA's exchange area" (128 arrivals, from the partner with the second half)
+    const uint32_t bar_peer_rdy = bar0 + 8u * (18 + 4 * kStages), bar_peer_data = bar0 + 8u * (19 + 4 * kStages);
+    auto bar_ref_ready = [&](uint32_t g) { return bar0 + 8u * (14 + 4 * kStages + (g & 3u)); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + SmemLayout::tmem_slot);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + SmemLayout::abort_flag);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t n_items = p.n_items, stride = gridDim.x;
+    const uint32_t n_items = p.n_work, stride = gridDim.x;   // the work units this grid walks (whole items, and halves of the last round's)
     // kLazy: the long-sequence recipe, chosen by the launcher from the whole sequence's tile count, also in a split (block3.rs:180-184)
     constexpr bool lazy = kLazy;
     constexpr float thr = lazy ? kLazyThreshold : -kFollowWindow;
@@ -304,17 +335,25 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         for (int st = 0; st < kStages; ++st) {
             mbar_init(bar_k_full(st), 2);
             mbar_init(bar_k_empty(st), 1);
-            mbar_init(bar_v_full(st), 1);
+            mbar_init(bar_v_full(st), kVbs ? 2 : 1);   // with V block scales: the TMA's expect-tx arrive + the arrive that follows the scale bytes
             mbar_init(bar_v_empty(st), 1);
         }
         mbar_init(bar_o_free, kRows);   // the epilogue warpgroup's 128 threads
         mbar_init(bar_o_full, 1);
+        for (uint32_t i = 0; i < 4; ++i) mbar_init(bar_ref_ready(i), kRows);
+        mbar_init(bar_peer_rdy, 1);
+        mbar_init(bar_peer_data, kRows);
         fence_mbar_init();
+    }
+    if (kVbs && threadIdx.x >= 256 && threadIdx.x < 384) {
+        reinterpret_cast<uint32_t*>(smem_gen + SmemLayout::sf_one)[threadIdx.x - 256] = 0x7F7F7F7Fu;
+        fence_proxy_async_smem();
     }
     if (threadIdx.x < 256) {
         for (int i = 0; i < 4; ++i) reinterpret_cast<uint32_t*>(smem_gen + SmemLayout::ones)[threadIdx.x + 256 * i] = 0x38383838u;
-        // the 256 reference hand-over slots start with a tile counter no tile has
+        // the 512 reference hand-over slots start with a tile counter no tile has
         reinterpret_cast<uint2*>(smem_gen + SmemLayout::xref)[threadIdx.x] = make_uint2(0u, 0xFFFFFFFFu);
+        reinterpret_cast<uint2*>(smem_gen + SmemLayout::xref)[threadIdx.x + 256] = make_uint2(0u, 0xFFFFFFFFu);
         fence_proxy_async_smem();
     }
     if (warp == kMmaWarp) {
@@ -330,6 +369,18 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    // launched as pairs (the last round's items are cut in two): the partner's barriers must exist before anything can arrive on them
+    // Every thread arrives on the cluster's barrier here and waits for it only where it first touches the partner (the epilogue
+    // warpgroup, the score MMA warp) or, failing that, at the end; by then the partner has long arrived, so nobody stands still for it.
+    constexpr bool paired = kPair;
+    bool cluster_joined = !paired;
+    if (paired) asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    auto join_cluster = [&]() {
+        if (!cluster_joined) {
+            asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+            cluster_joined = true;
+        }
+    };
     // nothing above touches global memory; everything below may read what the previous grid in the stream wrote
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) stamp(cta_traced ? p.trace : nullptr, 2, 30, 2);   // setup done
@@ -364,7 +415,7 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             auto enter_item = [&](ScaleCursor& c) {
                 c.live = c.w < n_items;
                 if (!c.live) return;
-                const Item it = decode_item<kSplit, kCausal>(c.w, p);
+                const Item it = decode_item<kSplit, kCausal, kPair>(c.w, p);
                 c.ptr = p.k_descale + static_cast<size_t>(it.batch) * p.ks_batch_stride + (static_cast<size_t>(it.key_lo + lane) * p.HK + it.kv_head) * 4u;
                 c.keys_left = static_cast<int>(p.SK - it.key_lo) - lane;
                 c.tiles_left = it.n_tiles;
@@ -400,7 +451,7 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             };
             // The CTA's first copies (Q tile and first K tile, first V tile of its first item) go out before anything else of the role's set-up.
             if (blockIdx.x < n_items && elect_one_sync()) {
-                const Item it = decode_item<kSplit, kCausal>(blockIdx.x, p);
+                const Item it = decode_item<kSplit, kCausal, kPair>(blockIdx.x, p);
                 if (kIsK) {
                     mbar_arrive_expect_tx(bar_q_full(0), kTileBytes);
                     tma_load_4d(q_smem, &tm_q, bar_q_full(0), 0, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
@@ -418,7 +469,7 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             enter_item(cs);
             if (kPar) advance(cs);   // this warp's first tile is the CTA's second
             uint32_t wq[4] = {0u, 0u, 0u, 0u}, w0[4], w1[4];
-            if (kIsK && blockIdx.x < n_items) load_q_scales(decode_item<kSplit, kCausal>(blockIdx.x, p), wq);
+            if (kIsK && blockIdx.x < n_items) load_q_scales(decode_item<kSplit, kCausal, kPair>(blockIdx.x, p), wq);
             load_and_advance(cs, w0);
             load_and_advance(cs, w1);
 
@@ -426,7 +477,7 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             int st = 0;
             bool ok = true;
             for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
-                const Item it = decode_item<kSplit, kCausal>(w, p);
+                const Item it = decode_item<kSplit, kCausal, kPair>(w, p);
                 const uint32_t qb = n & 1u;
                 if (kIsK) {
                     // the Q buffer was last used two items ago
@@ -442,11 +493,20 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     __syncwarp();
                     if (elect_one_sync()) mbar_arrive(bar_q_full(qb));
                     ++q_issued;
-                    if (w + stride < n_items) load_q_scales(decode_item<kSplit, kCausal>(w + stride, p), wq);   // the next item's Q scales, a whole item ahead
+                    if (w + stride < n_items) load_q_scales(decode_item<kSplit, kCausal, kPair>(w + stride, p), wq);   // the next item's Q scales, a whole item ahead
                 }
                 float* k_trace = cta_traced ? p.trace : nullptr;   // stamps are indexed by the running tile counter
                 int key = static_cast<int>(it.key_lo);
                 for (int j = 0; j < it.n_tiles; ++j, key += kKeys) {
+                    uint32_t vsc[4] = {0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu};   // key blocks past the sequence: data is zero-filled, any finite scale does
+                    if (kVbs && !kIsK) {   // issued first, used after the waits below
+                        const uint32_t nblk = (p.SK + 31u) / 32u, blk0 = static_cast<uint32_t>(key) / 32u;
+#pragma unroll
+                        for (uint32_t kb = 0; kb < 4u; ++kb) {
+                            if (blk0 + kb < nblk)
+                                vsc[kb] = __ldg(reinterpret_cast<const uint32_t*>(p.v_blockscale + ((static_cast<size_t>(it.batch) * nblk + blk0 + kb) * p.HK + it.kv_head) * 128u) + lane);
+                        }
+                    }
                     const bool own_scales = (g & 1u) == kPar;
                     // K: the stage (tile and scale bytes) is free once Q K^T of the tile that held it is done
                     if ((kIsK || own_scales) && g >= static_cast<uint32_t>(kStages)) ok = mbar_wait(bar_k_empty(st), ph ^ 1u, abort_flag);
@@ -475,6 +535,24 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                             stamp(k_trace, 3, static_cast<int>(g), 6);
                             mbar_arrive_expect_tx(bar_v_full(st), kTileBytes);
                             tma_load_4d(v_smem + st * kTileBytes, &tm_v, bar_v_full(st), 0, static_cast<int>(it.kv_head), key, static_cast<int>(it.batch));
+                        }
+                        if (kVbs) {
+                            // V block scales (extension): E8M0 [batch][key / 32][kv head][128 columns]. The tile's four key blocks are four rows of
+                            // 128 bytes; lane l holds columns 4l .. 4l+3 of each (vsc, loaded at the top of the iteration), transposes them to
+                            // one word per column (byte = key block) and writes word n to [n % 32][n / 32], the layout tcgen05.cp spreads
+                            // over the lane quadrants.
+                            const uint32_t a0 = __byte_perm(vsc[0], vsc[1], 0x5140), a1 = __byte_perm(vsc[0], vsc[1], 0x7362);
+                            const uint32_t b0 = __byte_perm(vsc[2], vsc[3], 0x5140), b1 = __byte_perm(vsc[2], vsc[3], 0x7362);
+                            const uint32_t t[4] = {__byte_perm(a0, b0, 0x5410), __byte_perm(a0, b0, 0x7632), __byte_perm(a1, b1, 0x5410), __byte_perm(a1, b1, 0x7632)};
+                            uint32_t* sfv_dst = reinterpret_cast<uint32_t*>(smem_gen + SmemLayout::sfv + st * kSfBytes);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const uint32_t n = 4u * static_cast<uint32_t>(lane) + static_cast<uint32_t>(i);
+                                sfv_dst[(n & 31u) * 4u + (n >> 5)] = t[i];
+                            }
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                            if (elect_one_sync()) mbar_arrive(bar_v_full(st));
                         }
                     }
                     ++g;
@@ -513,9 +591,17 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             int st = 0;
             bool ok = true;
             for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
-                const int n_tiles = decode_item<kSplit, kCausal>(w, p).n_tiles;
+                const Item qk_it = decode_item<kSplit, kCausal, kPair>(w, p);
+                const int n_tiles = qk_it.n_tiles;
                 const uint32_t qb = n & 1u;
                 float* mma_trace = cta_traced ? p.trace : nullptr;
+                // first half of a cut item: once its last score tile is done the K ring is idle for good, and the partner may push its
+                // half there (the commit below arrives on the partner's barrier)
+                uint32_t partner_rdy = 0u;
+                if (kPair && qk_it.half == 1u) {
+                    join_cluster();
+                    partner_rdy = map_to_cta(bar_peer_rdy, 1u);
+                }
                 ok = mbar_wait(bar_q_full(qb), (n >> 1) & 1u, abort_flag);
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -544,6 +630,7 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         tc_commit(bar_s_full(g & 1u));
                         tc_commit(bar_k_empty(st));
                         if (j == n_tiles - 1) tc_commit(bar_q_empty(qb));   // the Q buffer can take the item after next
+                        if (kPair && partner_rdy != 0u && j == n_tiles - 1) tc_commit(partner_rdy);
                         stamp(mma_trace, 2, static_cast<int>(g), 5);
                     }
                     ++g;
@@ -557,11 +644,19 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         {
             // P V with N = 144: head dims 0..127 from the V tile, 16 more columns from the tile of ones (O | L are adjacent in TMEM)
             const uint32_t idesc_pv = idesc_f8_dense(128, 144, 0, 1);
+            // V block scales (extension): the same MMA as kind::mxf8f6f4.block_scale, P's factors a constant 1.0, V's one E8M0 per 32 keys and column
+            const uint32_t idesc_pv_bs = idesc_mxf8_block_scaled(128, 144, 0, 1, 0, 0);
+            const uint32_t t_sfp = tmem + kColSfP, t_sfv = tmem + kColSfV;
+            if (kVbs && elect_one_sync()) {   // the constant factors, once: P's four columns and the ones columns' (rows 128..143 of the B factors)
+                const uint64_t d1 = make_smem_desc(smem_base + SmemLayout::sf_one, 0, 128, kSwizzleNone);
+                tmem_cp_sf(t_sfp, d1);
+                tmem_cp_sf(t_sfv + 4, d1);
+            }
             uint32_t g = 0, n = 0, ph = 0;
             int st = 0;
             bool ok = true;
             for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
-                const int n_tiles = decode_item<kSplit, kCausal>(w, p).n_tiles;
+                const int n_tiles = decode_item<kSplit, kCausal, kPair>(w, p).n_tiles;
                 float* mma_trace = cta_traced ? p.trace : nullptr;
                 // an item's first tile overwrites O and L, which the epilogue of the item before must have read out
                 if (n > 0) ok = mbar_wait(bar_o_free, (n - 1u) & 1u, abort_flag);
@@ -579,7 +674,14 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                             // MN-major B: 8-key groups 1024 B apart; the second 128-byte-wide atom (columns 128..) is the tile of ones
                             const uint32_t v_addr = v_smem + st * kTileBytes + kb * 4096;
                             const uint64_t dv = make_smem_desc(v_addr, ones_smem - v_addr, 1024, kSwizzle128B);
-                            mma_f8_ts(tmem + kColO, t_p + 8 * kb, dv, idesc_pv, (i > 0 || kb > 0) ? 1u : 0u);
+                            if (kVbs) {
+                                if (kb == 0) tmem_cp_sf(t_sfv, make_smem_desc(smem_base + SmemLayout::sfv + st * kSfBytes, 0, 128, kSwizzleNone));
+                                const uint32_t id = idesc_pv_bs | (static_cast<uint32_t>(kb) << 29) | (static_cast<uint32_t>(kb) << 4);
+                                mma_mxf8_ts(tmem + kColO, t_p + 8 * kb, dv, id, t_sfp + (static_cast<uint32_t>(kb) << 30), t_sfv + (static_cast<uint32_t>(kb) << 30),
+                                            (i > 0 || kb > 0) ? 1u : 0u);
+                            } else {
+                                mma_f8_ts(tmem + kColO, t_p + 8 * kb, dv, idesc_pv, (i > 0 || kb > 0) ? 1u : 0u);
+                            }
                         }
                         stamp(mma_trace, 3, static_cast<int>(g), 3);
                         tc_commit(bar_v_empty(st));
@@ -615,25 +717,25 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             uint2 o = ld_shared_v2(slot);
             if (o.y != g) {
                 const long long t0 = clock64();
-                while (true) {
+                for (uint32_t spins = 1;; ++spins) {
                     o = ld_shared_v2(slot);
                     if (o.y == g) break;
-                    if (*abort_flag != 0u || clock64() - t0 > kWaitBudgetCycles) { *abort_flag = 1u; return false; }
+                    if ((spins & 15u) == 0u && (*abort_flag != 0u || clock64() - t0 > kWaitBudgetCycles)) { *abort_flag = 1u; return false; }
                 }
             }
             out = __uint_as_float(o.x);
             return true;
         };
         // the reference the row has after tile g, published by the thread that handled it
-        auto ref_slot = [&](uint32_t g) { return xref + 8u * ((g & 1u) * 128u + r); };
+        auto ref_slot = [&](uint32_t g) { return xref + 8u * ((g & 3u) * 128u + r); };
 
-        const bool want_fin = kSplit || p.lse_nat != nullptr || cta_traced;   // does anything read the final reference?
+        const bool want_fin = kSplit || p.lse_nat != nullptr || cta_traced || kPair;   // does anything read the final reference?
         uint32_t g0 = 0, n = 0;   // tile counter at the item's first tile; ordinal of the item
         for (uint32_t w = blockIdx.x; ok && w < n_items; w += stride, ++n) {
             // the tile count, the number of tiles every row sees in full and the row's own key limit stay live through the tile loop
             int n_tiles, j_full, row_lim;   // row_lim: this row's visible keys, counted from the item's first key
             {
-                const Item it = decode_item<kSplit, kCausal>(w, p);
+                const Item it = decode_item<kSplit, kCausal, kPair>(w, p);
                 n_tiles = it.n_tiles;
                 row_lim = static_cast<int>(it.key_hi - it.key_lo);
                 int first_lim = row_lim;   // the limit of the item's first row: the tiles below it need no mask
@@ -697,13 +799,24 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 // read, and the new reference is published before the rescale factor is worked out.
                 const float cand = lazy ? ceilf(mt) : mt;   // where the reference goes if it moves
                 const float mt_thr = mt - thr;
+                // (tile g - 1's 128 threads have all published: a parked wait on their barrier, then the row's own slot)
+#ifdef MXA_REF_MBAR
+                if (j > 0) {
+                    if (!mbar_wait(bar_ref_ready(g - 1u), ((g - 1u) >> 2) & 1u, abort_flag)) ok = false;
+                    ref = __uint_as_float(ld_shared_v2(ref_slot(g - 1u)).x);
+                }
+#else
                 if (ok && j > 0 && !wait_slot(ref_slot(g - 1u), g - 1u, ref)) ok = false;
+#endif
                 // the reference moves when this tile's maximum passes it by more than the threshold (negative for short sequences: it then
                 // also follows the tile maximum down, and f > 1 scales O and L up)
                 const bool move = mt_thr > ref;
                 const float old_ref = ref;
                 ref = move ? cand : ref;
                 st_shared_v2(ref_slot(g), __float_as_uint(ref), g);
+#ifdef MXA_REF_MBAR
+                mbar_arrive(bar_ref_ready(g));
+#endif
                 // the item's last tile leaves the row's final reference for the epilogue warpgroup's log-sum-exp (ordered before this
                 // thread's arrive on p_full, which the last P V, and through it the epilogue's o_full, come after)
                 if (want_fin && j == n_tiles - 1) *reinterpret_cast<volatile float*>(smem_gen + SmemLayout::xfin + 4u * ((n & 1u) * 128u + r)) = ref;
@@ -778,37 +891,87 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const uint32_t t_o = tmem + kColO + lane_base, t_l = tmem + kColL + lane_base;
         const uint32_t stg = smem_base + SmemLayout::ostage;
         const bool issuer = threadIdx.x == 32u * kFirstEpilogueWarp;
-        const bool want_fin = kSplit || p.lse_nat != nullptr || cta_traced;
+        const bool want_fin = kSplit || p.lse_nat != nullptr || cta_traced || kPair;
+        // Half items (the cut last round; a half item is a CTA's last unit, so its K / V rings are idle once its last P V is done): the CTA
+        // with the first half tells its partner when its K ring is free (the commit of its last score tile arrives on the partner's
+        // barrier); the partner pushes its unnormalised O (f32), row sums and references there with distributed-shared-memory stores and
+        // arrives on the first half's barrier; the first half merges and stores. Both references are integers (long-sequence recipe), so the rescale factors
+        // are exact powers of two.
+        // exchange area = the K ring (64 KB): row r at r * 512 bytes, its 16-byte chunk c at position c ^ (r % 8) within each group of 8
+        const uint32_t xch_row = smem_base + SmemLayout::k + r * 512u;
+        const uint32_t xch_stat = smem_base + SmemLayout::xstat + r * 8u;
+        static_assert(128u * 512u <= kStages * kTileBytes, "the exchange area is the K ring");
+        auto xch_off = [&](int c, int q4) { return static_cast<uint32_t>(c) * 128u + ((static_cast<uint32_t>(q4) ^ (r & 7u)) << 4); };
         constexpr uint32_t kEpiBar = 1u;   // named barrier of the 128 epilogue threads
-        const float vd = __ldg(p.v_descale);
+        const float vd = kVbs ? 1.0f : __ldg(p.v_descale);   // with V block scales the factors are in the MMA and there is no scalar descale
         uint32_t n = 0;
         bool ok = true;
         for (uint32_t w = blockIdx.x; w < n_items; w += stride, ++n) {
-            const Item it = decode_item<kSplit, kCausal>(w, p);
+            const Item it = decode_item<kSplit, kCausal, kPair>(w, p);
             const bool tracing = cta_traced && n == 0;
             const bool dumping = tracing && !(p.flags & 0x4u);
-            float* ep_trace = (cta_traced && r == 0) ? p.trace : nullptr;   // epilogue stamps: tile index 24 + item ordinal
-            stamp(ep_trace, 0, 24 + static_cast<int>(n), 0);
+            float* ep_trace = (cta_traced && r == 0 && n < 6) ? p.trace : nullptr;   // epilogue stamps: P V role's row, tile index 24 + item ordinal, slots 0, 1, 5, 7
+            stamp(ep_trace, 3, 24 + static_cast<int>(n), 0);
             ok = mbar_wait(bar_o_full, n & 1u, abort_flag);
             if (issuer && n > 0) bulk_wait_group_read0();   // the previous item's stores have read the staging tiles out
             // one barrier: the staging tiles are free, and the decision to go on is the whole warpgroup's (the named barriers below count
             // all 128 threads, so no warp may leave while a sibling goes on)
             if (!named_bar_all(kEpiBar, 128u, ok)) break;
             tc_fence_after_sync();
-            stamp(ep_trace, 0, 24 + static_cast<int>(n), 1);
+            stamp(ep_trace, 3, 24 + static_cast<int>(n), 1);
             uint32_t lv;
             asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(lv) : "r"(t_l) : "memory");
             const float ref_fin = want_fin ? *reinterpret_cast<volatile float*>(smem_gen + SmemLayout::xfin + 4u * ((n & 1u) * 128u + r)) : 0.0f;
             tmem_wait_ld();
-            const float l = __uint_as_float(lv);
+            float l = __uint_as_float(lv);
+            float ref_out = ref_fin;
+            if (kPair && it.half == 2u) {
+                // second half: wait for the partner's exchange area, push O, l and the reference, one arrive per thread on its barrier
+                join_cluster();
+                ok = mbar_wait_cluster(bar_peer_rdy, 0u, abort_flag);
+                if (!named_bar_all(kEpiBar, 128u, ok)) break;
+                const uint32_t dst_row = map_to_cta(xch_row, 0u);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t o[32];
+                    tmem_ld32(t_o + 32 * c, o);
+                    tmem_wait_ld();
+                    if (c == 3) {
+                        tc_fence_before_sync();
+                        mbar_arrive(bar_o_free);
+                    }
+#pragma unroll
+                    for (int q4 = 0; q4 < 8; ++q4) {
+                        asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst_row + xch_off(c, q4)),
+                                     "r"(o[4 * q4]), "r"(o[4 * q4 + 1]), "r"(o[4 * q4 + 2]), "r"(o[4 * q4 + 3]) : "memory");
+                    }
+                }
+                asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(map_to_cta(xch_stat, 0u)), "f"(l), "f"(ref_fin) : "memory");
+                mbar_arrive_remote(map_to_cta(bar_peer_data, 0u));
+                continue;
+            }
+            float fa = 1.0f, fb = 0.0f;   // weights of the own and of the partner's half in a merge
+            if (kPair && it.half == 1u) {
+                join_cluster();
+                ok = mbar_wait_cluster(bar_peer_data, 0u, abort_flag);
+                if (!named_bar_all(kEpiBar, 128u, ok)) break;
+                float2 ps;   // {l, reference} of the partner's half
+                asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(ps.x), "=f"(ps.y) : "r"(xch_stat) : "memory");
+                ref_out = fmaxf(ref_fin, ps.y);
+                fa = ex2_approx(ref_fin - ref_out);
+                fb = ex2_approx(ps.y - ref_out);
+                l = l * fa + ps.x * fb;
+            }
             const float fin = vd / l;
             const uint32_t row = it.row0 + r;
             if (tracing) {
                 p.trace[32768 + r] = l;
-                p.trace[32768 + 128 + r] = ref_fin;
+                p.trace[32768 + 128 + r] = ref_out;
             }
-            if (!kSplit) {
-                // bf16 output: four 32-column chunks, all staged before the stores go out; O is free after the last read
+            const bool half_out = !kSplit || (p.flags & kFlagF32Partials) == 0u;   // 16-bit rows (bf16 output, f16 partial) or f32 partial rows
+            if (half_out) {
+                // bf16 output, or the split kernel's f16 partial (the reference's partial format, block3.rs:291-356): four 32-column
+                // chunks, all staged before the stores go out; O is free after the last read
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t o[32];
@@ -817,11 +980,23 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     if (c == 3) {
                         tc_fence_before_sync();
                         mbar_arrive(bar_o_free);   // O and L are out: the next item's first P V may overwrite them
-                        stamp(ep_trace, 0, 24 + static_cast<int>(n), 2);
+                        stamp(ep_trace, 3, 24 + static_cast<int>(n), 5);
                     }
                     if (dumping) {
 #pragma unroll
                         for (int e = 0; e < 32; ++e) p.trace[16384 + r * 128 + 32 * c + e] = __uint_as_float(o[e]);
+                    }
+                    if (kPair && it.half == 1u) {
+#pragma unroll
+                        for (int q4 = 0; q4 < 8; ++q4) {
+                            float4 pb;
+                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(pb.x), "=f"(pb.y), "=f"(pb.z), "=f"(pb.w)
+                                         : "r"(xch_row + xch_off(c, q4)) : "memory");
+                            o[4 * q4] = __float_as_uint(__uint_as_float(o[4 * q4]) * fa + pb.x * fb);
+                            o[4 * q4 + 1] = __float_as_uint(__uint_as_float(o[4 * q4 + 1]) * fa + pb.y * fb);
+                            o[4 * q4 + 2] = __float_as_uint(__uint_as_float(o[4 * q4 + 2]) * fa + pb.z * fb);
+                            o[4 * q4 + 3] = __float_as_uint(__uint_as_float(o[4 * q4 + 3]) * fa + pb.w * fb);
+                        }
                     }
                     const uint32_t tile_base = stg + (static_cast<uint32_t>(c) >> 1) * 16384u + r * 128u;
 #pragma unroll
@@ -829,8 +1004,13 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         uint32_t wv[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[8 * q4 + 2 * e]) * fin, __uint_as_float(o[8 * q4 + 2 * e + 1]) * fin);
-                            wv[e] = *reinterpret_cast<const uint32_t*>(&b2);
+                            const float a = __uint_as_float(o[8 * q4 + 2 * e]) * fin, b = __uint_as_float(o[8 * q4 + 2 * e + 1]) * fin;
+                            if (kSplit) {
+                                asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(wv[e]) : "f"(b), "f"(a));
+                            } else {
+                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(a, b);
+                                wv[e] = *reinterpret_cast<const uint32_t*>(&b2);
+                            }
                         }
                         const uint32_t chunk = static_cast<uint32_t>((c & 1) * 4 + q4);
                         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(tile_base + ((chunk ^ (r & 7u)) << 4)),
@@ -840,8 +1020,13 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 fence_proxy_async_smem();
                 named_bar_sync(kEpiBar, 128u);
                 if (issuer) {
-                    tma_store_4d(&tm_o, stg, 0, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
-                    tma_store_4d(&tm_o, stg + 16384u, 64, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
+                    if (kSplit) {
+                        tma_store_5d(&tm_o, stg, 0, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch), static_cast<int>(it.split));
+                        tma_store_5d(&tm_o, stg + 16384u, 64, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch), static_cast<int>(it.split));
+                    } else {
+                        tma_store_4d(&tm_o, stg, 0, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
+                        tma_store_4d(&tm_o, stg + 16384u, 64, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
+                    }
                     bulk_commit_group();
                 }
             } else {
@@ -855,7 +1040,19 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     if (c == 3) {
                         tc_fence_before_sync();
                         mbar_arrive(bar_o_free);
-                        stamp(ep_trace, 0, 24 + static_cast<int>(n), 2);
+                        stamp(ep_trace, 3, 24 + static_cast<int>(n), 5);
+                    }
+                    if (kPair && it.half == 1u) {
+#pragma unroll
+                        for (int q4 = 0; q4 < 8; ++q4) {
+                            float4 pb;
+                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(pb.x), "=f"(pb.y), "=f"(pb.z), "=f"(pb.w)
+                                         : "r"(xch_row + xch_off(c, q4)) : "memory");
+                            o[4 * q4] = __float_as_uint(__uint_as_float(o[4 * q4]) * fa + pb.x * fb);
+                            o[4 * q4 + 1] = __float_as_uint(__uint_as_float(o[4 * q4 + 1]) * fa + pb.y * fb);
+                            o[4 * q4 + 2] = __float_as_uint(__uint_as_float(o[4 * q4 + 2]) * fa + pb.z * fb);
+                            o[4 * q4 + 3] = __float_as_uint(__uint_as_float(o[4 * q4 + 3]) * fa + pb.w * fb);
+                        }
                     }
                     if (c >= 2) {   // the store of piece c - 2 (all but the newest group) must have read its tile out
                         if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
@@ -878,7 +1075,7 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 }
             }
             if (row < p.S && want_fin) {   // rows past the sequence are computed on clamped scales and not stored (block3.rs:194)
-                const float lse2 = ref_fin - kPOffset + lg2_approx(l);   // log2 of sum_j 2^(s_j)
+                const float lse2 = ref_out - kPOffset + lg2_approx(l);   // log2 of sum_j 2^(s_j)
                 if (kSplit) {
                     const size_t prow = static_cast<size_t>(it.split) * p.rows_total + (static_cast<size_t>(it.batch) * p.S + row) * p.H + it.head;
                     p.lse2[prow] = lse2;
@@ -886,7 +1083,7 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     p.lse_nat[(static_cast<size_t>(it.batch) * p.H + it.head) * p.S + row] = lse2 * 0.6931471805599453f;
                 }
             }
-            stamp(ep_trace, 0, 24 + static_cast<int>(n), 3);
+            stamp(ep_trace, 3, 24 + static_cast<int>(n), 7);
         }
         if (issuer) bulk_wait_group_read0();   // the staging tiles have been read out before the CTA gives its shared memory back
     }
@@ -894,6 +1091,11 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     // ---- teardown ----
     tc_fence_before_sync();
     __syncthreads();
+    // a pair stays together to the end: the partner may still be reading this CTA's exchange area or arriving on its barrier
+    if (paired) {
+        join_cluster();
+        asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+    }
     if (threadIdx.x == 0) stamp(cta_traced ? p.trace : nullptr, 2, 30, 1);   // all roles done
     if (threadIdx.x == 0 && *abort_flag != 0u) atomicOr(p.status, 1u);
     if (warp == kMmaWarp) {
@@ -906,34 +1108,54 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
                              uint32_t B, bool split, uint32_t rows_per_cta, cudaStream_t stream) {
     (void)rows_per_cta;   // both logical block heights run as 128-row CTAs
     using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
-    // [causal][recipe][trace][split]; the causal mask has no split form
-    static const Kernel kernels[16] = {mxfp8_prefill_kernel<false, false, false, false>, mxfp8_prefill_kernel<true, false, false, false>,
-                                       mxfp8_prefill_kernel<false, true, false, false>,  mxfp8_prefill_kernel<true, true, false, false>,
-                                       mxfp8_prefill_kernel<false, false, true, false>,  mxfp8_prefill_kernel<true, false, true, false>,
-                                       mxfp8_prefill_kernel<false, true, true, false>,   mxfp8_prefill_kernel<true, true, true, false>,
-                                       mxfp8_prefill_kernel<false, false, false, true>,  nullptr,
-                                       mxfp8_prefill_kernel<false, true, false, true>,   nullptr,
-                                       mxfp8_prefill_kernel<false, false, true, true>,   nullptr,
-                                       mxfp8_prefill_kernel<false, true, true, true>,    nullptr};
+    // The instantiations: [causal][recipe][trace][split] (the causal mask has no split form); behind them the variants for launches as pairs
+    // of CTAs (long-sequence recipe, no mask): [trace][split]; behind those the variants with V block scales (no mask, no trace):
+    // [pair][recipe][split], pairs only with the long-sequence recipe.
+#define MXA_K(split, trace, lazy, causal, pair, vbs) mxfp8_prefill_kernel<split, trace, lazy, causal, pair, vbs>
+    static const Kernel kernels[28] = {
+        MXA_K(false, false, false, false, false, false), MXA_K(true, false, false, false, false, false), MXA_K(false, true, false, false, false, false),
+        MXA_K(true, true, false, false, false, false),   MXA_K(false, false, true, false, false, false), MXA_K(true, false, true, false, false, false),
+        MXA_K(false, true, true, false, false, false),   MXA_K(true, true, true, false, false, false),   MXA_K(false, false, false, true, false, false),
+        nullptr,                                         MXA_K(false, true, false, true, false, false),  nullptr,
+        MXA_K(false, false, true, true, false, false),   nullptr,                                        MXA_K(false, true, true, true, false, false),
+        nullptr,
+        MXA_K(false, false, true, false, true, false),   MXA_K(true, false, true, false, true, false),   MXA_K(false, true, true, false, true, false),
+        MXA_K(true, true, true, false, true, false),
+        MXA_K(false, false, false, false, false, true),  MXA_K(true, false, false, false, false, true),  MXA_K(false, false, true, false, false, true),
+        MXA_K(true, false, true, false, false, true),    nullptr,                                        nullptr,
+        MXA_K(false, false, true, false, true, true),    MXA_K(true, false, true, false, true, true)};
+#undef MXA_K
+    constexpr int kKernels = 28;
     constexpr int kMaxDevices = 64;
     // per-device set-up done lazily from whichever thread launches first: plain flags would be a data race, and both steps are idempotent
-    static std::atomic<bool> attr_done[kMaxDevices][16];   // the shared-memory attribute is per device
+    static std::atomic<bool> attr_done[kMaxDevices][kKernels];   // the shared-memory attribute is per device
     static std::atomic<int> sm_count[kMaxDevices];
+    static std::atomic<int> pair_capacity[kMaxDevices][kKernels];   // -1 = not asked yet (set below on first use)
+    static std::once_flag pair_init;
+    std::call_once(pair_init, [] {
+        for (auto& d : pair_capacity) for (auto& x : d) x.store(-1, std::memory_order_relaxed);
+    });
     // the long-sequence recipe from 4 key tiles of the whole sequence on (crates/amdgpu-stage/src/attention/state.rs:73-77), unless the
     // caller asks for the exact one; each recipe is its own instantiation, which halves the code of the tile loop
     const bool lazy_recipe = (p.SK + kKeys - 1) / kKeys >= 4 && !(p.flags & 0x2u);
     const bool causal = (p.flags & kFlagCausal) != 0u;
     if (causal && split) return cudaErrorInvalidValue;
-    const int which = (split ? 1 : 0) + (p.trace != nullptr ? 2 : 0) + (lazy_recipe ? 4 : 0) + (causal ? 8 : 0);
+    const bool vbs = p.v_blockscale != nullptr;
+    if (vbs && (causal || p.trace != nullptr)) return cudaErrorInvalidValue;   // V block scales: no mask, no diagnostics
+    int which = vbs ? 20 + (split ? 1 : 0) + (lazy_recipe ? 2 : 0) : (split ? 1 : 0) + (p.trace != nullptr ? 2 : 0) + (lazy_recipe ? 4 : 0) + (causal ? 8 : 0);
+    const int which_pair = vbs ? 26 + (split ? 1 : 0) : 16 + (split ? 1 : 0) + (p.trace != nullptr ? 2 : 0);   // only for the long-sequence recipe without a mask
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
-    if (!attr_done[dev][which].load(std::memory_order_acquire)) {
-        e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernels[which]), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return e;
-        attr_done[dev][which].store(true, std::memory_order_release);
-    }
+    auto ensure_attr = [&](int k) -> cudaError_t {
+        if (attr_done[dev][k].load(std::memory_order_acquire)) return cudaSuccess;
+        const cudaError_t ea = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernels[k]), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (ea == cudaSuccess) attr_done[dev][k].store(true, std::memory_order_release);
+        return ea;
+    };
+    e = ensure_attr(which);
+    if (e != cudaSuccess) return e;
     int sms = sm_count[dev].load(std::memory_order_relaxed);
     if (sms == 0) {
         int n = 0;
@@ -943,23 +1165,77 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
         sm_count[dev].store(sms, std::memory_order_relaxed);
     }
     // Persistent launch: one CTA per SM (a CTA takes all of an SM's tensor memory and nearly all of its shared memory), each walking the
-    // work items blockIdx.x, blockIdx.x + gridDim.x, ...
+    // work units blockIdx.x, blockIdx.x + gridDim.x, ...
     AttnParams q = p;
     q.n_qtiles = (p.S + kRows - 1) / kRows;
     const unsigned long long items = 1ull * q.n_qtiles * p.H * B * (split ? p.splits : 1u);
-    if (items == 0 || items > 0xFFFFFFFFull) return cudaErrorInvalidValue;
+    if (items == 0 || items > 0x7FFFFFFFull) return cudaErrorInvalidValue;
     q.n_items = static_cast<uint32_t>(items);
-    const uint32_t ctas = q.n_items < static_cast<uint32_t>(sms) ? q.n_items : static_cast<uint32_t>(sms);
+    q.n_work = q.n_items;
+    q.tail_base = q.n_items;
+    q.tail_split = 0u;
+    uint32_t ctas = q.n_items < static_cast<uint32_t>(sms) ? q.n_items : static_cast<uint32_t>(sms);
+    // The last round. n_items = rounds * grid + tail: when the tail fills at most half of the grid, its items would keep a few CTAs busy
+    // for a whole item while the rest idle. They are then cut in two key ranges each, the grid is launched as clusters of two CTAs, and
+    // each pair merges its two halves through distributed shared memory (no workspace). Long-sequence recipe only (integer references
+    // merge exactly), no causal mask (its items differ in length and are balanced by their order), at least 4 key tiles per half.
+    const uint32_t ntiles_total = (p.SK + kKeys - 1) / kKeys;
+    uint32_t min_tiles = ntiles_total;
+    if (split) {
+        const uint32_t tps = (ntiles_total + p.splits - 1) / p.splits;
+        min_tiles = ntiles_total - (p.splits - 1u) * tps;   // the last split's share
+    }
+    const uint32_t even_sms = static_cast<uint32_t>(sms) & ~1u;
+    if (lazy_recipe && !causal && min_tiles >= 8u && even_sms >= 2u && !(p.flags & kFlagNoTailSplit)) {
+        const uint32_t rounds = q.n_items / even_sms, tail = q.n_items - rounds * even_sms;
+        if (tail > 0u && 2u * tail <= even_sms) {
+            const uint32_t grid = rounds > 0u ? even_sms : 2u * tail;
+            e = ensure_attr(which_pair);
+            if (e != cudaSuccess) return e;
+            int max_clusters = pair_capacity[dev][which_pair].load(std::memory_order_relaxed);
+            if (max_clusters < 0) {   // how many pairs of CTAs of this kernel the device holds at once (asked once per device and kernel)
+                cudaLaunchConfig_t probe = {};
+                probe.gridDim = dim3(even_sms, 1, 1);
+                probe.blockDim = dim3(kThreads, 1, 1);
+                probe.dynamicSmemBytes = kSmemBytes;
+                cudaLaunchAttribute pa[1];
+                pa[0].id = cudaLaunchAttributeClusterDimension;
+                pa[0].val.clusterDim.x = 2; pa[0].val.clusterDim.y = 1; pa[0].val.clusterDim.z = 1;
+                probe.attrs = pa;
+                probe.numAttrs = 1;
+                int n = 0;
+                if (cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void*>(kernels[which_pair]), &probe) != cudaSuccess) { n = 0; (void)cudaGetLastError(); }
+                max_clusters = n;
+                pair_capacity[dev][which_pair].store(n, std::memory_order_relaxed);
+            }
+            if (static_cast<uint32_t>(max_clusters) * 2u >= grid) {
+                q.tail_split = 1u;
+                q.tail_base = rounds * even_sms;
+                q.n_work = q.tail_base + 2u * tail;
+                ctas = grid;
+                which = which_pair;
+                if (getenv("MXA_DEBUG_PAIR_NOSPLIT")) {   // TEMPORARY measurement aid
+                    q.tail_base = q.n_items; q.n_work = q.n_items;
+                    ctas = q.n_items < even_sms ? ((q.n_items + 1u) & ~1u) : even_sms;
+                }
+            }
+        }
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas, 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // overlap this grid's launch and set-up with the tail of the grid before it
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (q.tail_split != 0u) {
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 2; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
     return cudaLaunchKernelEx(&cfg, kernels[which], tm_q, tm_k, tm_v, tm_o, q);
 }
 

@@ -181,16 +181,17 @@ int make_out_map(CUtensorMap* m, void* base, uint64_t seq, uint64_t heads, uint6
     return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r);
 }
 
-// The split kernel's f32 partials [splits][B*S*H rows][128] as a 5-D map (head dim, head, row, batch, split) with a 128-row x 32-column
-// box (128 bytes), 128-byte swizzle: half of one warpgroup's share of a partial tile.
-int make_partial_map(CUtensorMap* m, void* base, uint64_t seq, uint64_t heads, uint64_t batches, uint64_t splits) {
+// The split kernel's partials [splits][B*S*H rows][128] as a 5-D map (head dim, head, row, batch, split), 128-byte swizzle: f16 rows of
+// 256 bytes with a 128-row x 64-column box, or f32 rows of 512 bytes with a 128-row x 32-column box (either box is 128 bytes wide).
+int make_partial_map(CUtensorMap* m, void* base, uint64_t seq, uint64_t heads, uint64_t batches, uint64_t splits, bool f32) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return -static_cast<int>(cudaErrorSymbolNotFound);
+    const uint64_t rb = f32 ? 512 : 256;
     const cuuint64_t dims[5] = {128, heads, seq, batches, splits};
-    const cuuint64_t strides[4] = {512, heads * 512, seq * heads * 512, batches * seq * heads * 512};
-    const cuuint32_t box[5] = {32, 1, 128, 1, 1};
+    const cuuint64_t strides[4] = {rb, heads * rb, seq * heads * rb, batches * seq * heads * rb};
+    const cuuint32_t box[5] = {f32 ? 32u : 64u, 1, 128, 1, 1};
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-    const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    const CUresult r = enc(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r);
 }
@@ -225,7 +226,9 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
     p.qs_batch_stride = a->s_descale_q_Bs;
     p.ks_batch_stride = a->s_descale_k_Bs;
     p.flags = a->ext_flags;
-    if (p.flags & FMHA_MXFP8_FLAG_V_BLOCKSCALE) return FMHA_MXFP8_E_ARG;   // per-32-key V scales are declared in the ABI but no kernel implements them
+    // V block scales (extension): a pointer is needed, and the mask and the diagnostics have no variant with them
+    if ((p.flags & FMHA_MXFP8_FLAG_V_BLOCKSCALE) && (a->ext_ptr_v_blockscale == nullptr || (p.flags & FMHA_MXFP8_FLAG_CAUSAL) || g_trace.load(std::memory_order_relaxed) != nullptr))
+        return FMHA_MXFP8_E_ARG;
     if ((p.flags & FMHA_MXFP8_FLAG_CAUSAL) && (split || p.SK < p.S)) return FMHA_MXFP8_E_ARG;   // causal: unsplit kernels, SK >= S
     p.v_blockscale = (p.flags & FMHA_MXFP8_FLAG_V_BLOCKSCALE) ? static_cast<const uint8_t*>(a->ext_ptr_v_blockscale) : nullptr;
     p.lse_nat = split ? nullptr : static_cast<float*>(a->ext_ptr_lse);
@@ -243,7 +246,7 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
         if (static_cast<uint64_t>(p.splits - 1) * tps >= ntiles) return FMHA_MXFP8_E_KA_RANGE;
         p.split_log2 = log2_u32(p.splits);
         p.rows_total = s->kvs_rows_total;
-        p.ohat = static_cast<float*>(s->ptr_ohat);
+        p.ohat = s->ptr_ohat;
         p.lse2 = static_cast<float*>(s->ptr_lse);
         B = grid[2] / p.splits;
     }
@@ -259,7 +262,7 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
         r = make_out_map(&to, a->ptr_o, p.S, p.H, B, a->s_o_Hs, a->s_o_Seqs, a->s_o_Bs);
     } else {
         if (static_cast<uint64_t>(p.rows_total) != static_cast<uint64_t>(B) * p.S * p.H) return FMHA_MXFP8_E_KA_IS;
-        r = make_partial_map(&to, p.ohat, p.S, p.H, B, p.splits);
+        r = make_partial_map(&to, p.ohat, p.S, p.H, B, p.splits, (p.flags & FMHA_MXFP8_FLAG_F32_PARTIALS) != 0u);
     }
     if (r) return r;
     const cudaError_t e = b200mx::launch_attention(tq, tk, tv, to, p, B, split, kernel == FMHA_MXFP8_T128 ? 128u : 256u, stream);
@@ -329,8 +332,9 @@ int fmha_mxfp8_launch(int kernel, const void* args, const uint32_t grid[3], void
     if (kernel == FMHA_MXFP8_COMBINE8H) {
         const fmha_mxfp8_combine_args* c = static_cast<const fmha_mxfp8_combine_args*>(args);
         if (c->d != 128 || c->rows_total == 0 || c->splits == 0) return FMHA_MXFP8_E_KA_RANGE;
-        const cudaError_t e = b200mx::launch_combine(static_cast<const float*>(c->ptr_ohat), static_cast<const float*>(c->ptr_lse),
-                                                   static_cast<uint8_t*>(c->ptr_out), c->rows_total, c->splits, st);
+        // half-precision partials, as the reference's combine8h reads them (crates/amdgpu-kernels/src/fmha/io.rs:161-185)
+        const cudaError_t e = b200mx::launch_combine(c->ptr_ohat, false, static_cast<const float*>(c->ptr_lse), static_cast<uint8_t*>(c->ptr_out), c->rows_total,
+                                                     c->splits, st);
         return e == cudaSuccess ? 0 : -static_cast<int>(e);
     }
     if (!grid) return FMHA_MXFP8_E_ARG;
@@ -435,6 +439,13 @@ int fmha_mxfp8_auto(const fmha_mxfp8_problem* pr, int path, uint32_t splits, voi
     r = fmha_mxfp8_launch(FMHA_MXFP8_COMBINE8H, &c, cgrid, stream);
     if (r) return fail(err, cap, r, "combine launch failed");
     return 0;
+}
+
+int fmha_mxfp8_combine_f32(const void* ohat, const void* lse, void* out, uint32_t rows_total, uint32_t splits, void* stream) {
+    if (!ohat || !lse || !out || rows_total == 0 || splits == 0) return FMHA_MXFP8_E_ARG;
+    if ((reinterpret_cast<uintptr_t>(ohat) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u) || (reinterpret_cast<uintptr_t>(lse) & 3u)) return FMHA_MXFP8_E_ARG;
+    const cudaError_t e = b200mx::launch_combine(ohat, true, static_cast<const float*>(lse), static_cast<uint8_t*>(out), rows_total, splits, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }
 
 int fmha_mxfp8_quantize_qk(const void* x_bf16, uint64_t rows, float mul, void* out_e4m3, void* out_scales, void* stream) {

@@ -13,7 +13,7 @@ constexpr int kKeysPerTile = 128;
 struct AttnParams {
     // outputs
     uint8_t* o;            // bf16 [B,S,H,128] (unsplit)
-    float* ohat;           // f32 [splits][rows_total][128] (split)
+    void* ohat;            // f16 [splits][rows_total][128], or f32 with FMHA_MXFP8_FLAG_F32_PARTIALS (split)
     float* lse2;           // f32 [splits][rows_total], base-2 (split)
     float* lse_nat;        // optional f32 [B,H,S], natural log (unsplit), may be null
     // scale inputs
@@ -27,7 +27,11 @@ struct AttnParams {
     uint32_t qs_batch_stride, ks_batch_stride;  // bytes
     uint32_t splits, split_log2, rows_total;
     uint32_t flags;
-    uint32_t n_qtiles, n_items;   // work decomposition of the persistent kernel, filled in by launch_attention
+    // work decomposition of the persistent kernel, filled in by launch_attention: n_items work items (128 query rows of one (batch, head
+    // [, split])); the CTAs walk work units 0 .. n_work-1. Units below tail_base are whole items. With tail_split the items of the last,
+    // partly filled round are cut in two key ranges each: unit tail_base + 2 i + h is half h of item tail_base + i, and the two CTAs of a
+    // cluster take the two halves of one item and merge them through distributed shared memory
+    uint32_t n_qtiles, n_items, n_work, tail_base, tail_split;
     // diagnostics
     float* trace;          // may be null
     uint32_t* status;      // device status word
@@ -35,11 +39,11 @@ struct AttnParams {
 
 // rows_per_cta is 128 (t128) or 256 (vs128 / kvsplit): the logical block height of the reference's grids.
 // tm_o: the target of the kernel's TMA stores: the bf16 output as a 4-D map with a 128-row x 64-column box (unsplit kernels), or the
-// f32 partials as a 5-D map with a 128-row x 32-column box (split kernel)
+// partials as a 5-D map (split kernel): f16 with a 128-row x 64-column box, or f32 with a 128-row x 32-column box
 cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnParams& p,
                              uint32_t B, bool split, uint32_t rows_per_cta, cudaStream_t stream);
 
-cudaError_t launch_combine(const float* ohat, const float* lse2, uint8_t* out, uint32_t rows_total, uint32_t splits, cudaStream_t stream);
+cudaError_t launch_combine(const void* ohat, bool f32_partials, const float* lse2, uint8_t* out, uint32_t rows_total, uint32_t splits, cudaStream_t stream);
 
 // Quantisers in front of the path (quantize.cu): bf16 -> e4m3 + E8M0 per 32 head-dim elements (Q with `mul` folded in, K), bf16 -> e4m3 +
 // one f32 descale (V; `descale` needs 8 bytes: [0] the result, [1] scratch).

@@ -27,8 +27,23 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// A failed try_wait parks the thread until the phase completes or a time limit passes; the limit is the hardware's own unless a hint
+// (nanoseconds) is given. With the hint a waiting role issues a handful of instructions per wait instead of spinning on the issue slots
+// that the arithmetic warps of the same scheduler need.
+#ifndef MXA_WAIT_HINT_NS
+#define MXA_WAIT_HINT_NS 0
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
+#if MXA_WAIT_HINT_NS > 0
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "n"(MXA_WAIT_HINT_NS)
+        : "memory");
+#else
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -36,6 +51,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok)
         : "r"(bar), "r"(parity)
         : "memory");
+#endif
     return ok != 0;
 }
 // Non-blocking poll (try_wait may suspend the thread for a hardware time slice; test_wait never does).
@@ -50,9 +66,10 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Clock budget of one wait (SM cycles). ~2 s at 1.9 GHz: far above any legitimate wait in these kernels
-// (a whole launch takes well under 100 ms), small enough that a protocol bug ends by itself.
-constexpr long long kWaitBudgetCycles = 4000000000LL;
+// Clock budget of one wait (SM cycles), about 0.2 s at 1.9 GHz. Every wait in these kernels is for the same CTA's other roles to move
+// on by one tile or one item (microseconds), so this is far above any legitimate wait and still small enough that a protocol bug ends
+// by itself quickly.
+constexpr long long kWaitBudgetCycles = 400000000LL;
 
 // Waits for the phase with the given parity. Returns false when the budget (SM cycles) ran out or when another thread of the CTA
 // already flagged a failure (`*abort_flag != 0`, a shared-memory word). A failed try_wait has already been parked by the hardware
@@ -69,6 +86,63 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             return false;
         }
     }
+}
+
+// ----------------------------------------------------------------------------------------------- thread-block cluster (pairs of CTAs)
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+    uint32_t n;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n));
+    return n;
+}
+// the address of `local_addr` (a shared::cta address) in the shared memory of CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+    uint32_t ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(rank));
+    return ra;
+}
+// arrive on an mbarrier of another CTA of the cluster; everything this thread wrote before is visible to who acquires at cluster scope
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded like mbar_wait, acquiring at cluster scope (the arrivals come from the other CTA of the pair)
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, long long budget = kWaitBudgetCycles) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t spins = 1;; ++spins) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((spins & 7u) != 0u) continue;
+        if (*abort_flag != 0u) return false;
+        if (clock64() - t0 > budget) {
+            *abort_flag = 1u;
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ float4 ld_cluster_v4(uint32_t cluster_addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ float2 ld_cluster_v2(uint32_t cluster_addr) {
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(cluster_addr) : "memory");
+    return v;
+}
+// Barrier over all threads of all CTAs of the cluster (a hardware barrier without a time limit: only used where every thread of both
+// CTAs is certain to arrive, i.e. at points that every bounded wait before them leads to).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // One lane of a converged warp (always the same one for the full mask). The warp roles that issue tcgen05 / TMA instructions run

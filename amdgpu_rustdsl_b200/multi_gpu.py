@@ -54,7 +54,8 @@ def local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, l
     if stream is None:
         stream = torch.cuda.current_stream(q.device).cuda_stream
     rows_total = B * S * H
-    a = fill_common(_abi.KvSplitArgs(), q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, B, S, H, SKl, HK)
+    # f32 partials: these travel between GPUs before they are combined
+    a = fill_common(_abi.KvSplitArgs(), q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, B, S, H, SKl, HK, flags=_abi.FLAG_F32_PARTIALS)
     a.ptr_o = None
     a.ptr_ohat, a.ptr_lse, a.kvs_splits, a.kvs_rows_total = ohat.data_ptr(), lse.data_ptr(), 1, rows_total
     sizes = _abi.BufferSizes(ptr_q=_nbytes(q), ptr_k=_nbytes(k_local), ptr_v=_nbytes(v_local), ptr_o=B * S * H * 256, ptr_q_descale=_nbytes(q_scale),
@@ -65,18 +66,22 @@ def local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, l
 
 
 def combine_gathered(ohat_all, lse_all, out, world: int, *, stream=None, check=True):
-    """The combine kernel over the gathered partials: ohat_all f32 [world, rows_total, 128], lse_all f32 [world, rows_total] -> bf16 out."""
+    """The combine kernel over the gathered f32 partials: ohat_all f32 [world, rows_total, 128], lse_all f32 [world, rows_total] -> bf16 out."""
+    import ctypes as C
     import torch
     from . import _abi
-    from .ops import _check_launch, _nbytes
     lib = _abi.load()
     rows_total = out.numel() // D
     if stream is None:
         stream = torch.cuda.current_stream(out.device).cuda_stream
-    c = _abi.CombineArgs(ptr_ohat=ohat_all.data_ptr(), ptr_lse=lse_all.data_ptr(), ptr_out=out.data_ptr(), rows_total=rows_total, d=D, splits=world)
-    sizes = _abi.BufferSizes(ptr_ohat=_nbytes(ohat_all), ptr_lse=_nbytes(lse_all), ptr_out=_nbytes(out))
+    if ohat_all.dtype != torch.float32 or lse_all.dtype != torch.float32 or out.dtype != torch.bfloat16:
+        raise ValueError("combine_gathered: f32 partials and log-sum-exps, bf16 output")
+    if check and (ohat_all.numel() < world * rows_total * D or lse_all.numel() < world * rows_total):
+        raise ValueError("combine_gathered: partial buffers smaller than world x rows_total")
     with torch.cuda.device(out.device):
-        _check_launch(lib, _abi.COMBINE8H, c, sizes, _abi.grid3(max(1, math.ceil(rows_total * D / 2048)), 1, 1), None, stream, check)
+        rc = lib.fmha_mxfp8_combine_f32(ohat_all.data_ptr(), lse_all.data_ptr(), out.data_ptr(), rows_total, world, C.c_void_p(stream))
+    if rc:
+        raise RuntimeError(f"fmha_mxfp8_combine_f32 failed with code {rc}")
 
 
 def exchange_partials(ohat, lse, ohat_all, lse_all, group=None):

@@ -54,6 +54,19 @@ enum fmha_mxfp8_error {
  * shape dispatch says.
  */
 #define FMHA_MXFP8_FLAG_CAUSAL 0x8u
+/*
+ * The kvsplit kernel writes its partials as f32 [splits][rows][128] instead of the default f16 (extension; for partials that travel
+ * between GPUs before they are combined). The reference's partials are f16 in an allocation sized for f32
+ * (crates/amdgpu-kernels/src/fmha/io.rs:83-85); either form fits the contract's `ptr_ohat` extent. Pair it with
+ * fmha_mxfp8_combine_f32; fmha_mxfp8_launch(COMBINE8H) reads f16 partials, like the reference's combine8h.
+ */
+#define FMHA_MXFP8_FLAG_F32_PARTIALS 0x10u
+/*
+ * Launch detail (extension): when the last round of work items fills at most half of the SMs, the kernels cut those items in two key
+ * ranges and let pairs of CTAs (a cluster of two) merge the halves through distributed shared memory. This flag keeps every item
+ * whole. Results agree to f32 summation order either way.
+ */
+#define FMHA_MXFP8_FLAG_NO_TAIL_SPLIT 0x20u
 
 #pragma pack(push, 1)
 /*
@@ -188,7 +201,7 @@ typedef struct fmha_mxfp8_kvsplit_args {
     uint8_t _pad25[12];
     uint32_t s_descale_k_Hs;
     uint8_t _pad26[12];
-    void* ptr_ohat;              /* 0x270 f32 partial O, [splits][rows_total][128], normalised per split */
+    void* ptr_ohat;              /* 0x270 partial O [splits][rows_total][128], normalised per split: f16 (f32 with FMHA_MXFP8_FLAG_F32_PARTIALS); sized for f32 either way */
     void* ptr_lse;               /* 0x278 f32 base-2 log-sum-exp, [splits][rows_total] */
     uint32_t kvs_splits;         /* 0x280 2, 4 or 8 (1 is accepted) */
     uint32_t kvs_rows_total;     /* 0x284 B*S*H */
@@ -299,6 +312,15 @@ int fmha_mxfp8_auto(const fmha_mxfp8_problem* prob, int path, uint32_t splits, v
  */
 #define FMHA_MXFP8_STATIC_SCRATCH_MAX_ROW_SPLITS 65536u
 int fmha_mxfp8_kvsplit_static_scratch(const fmha_mxfp8_problem* prob, uint32_t splits, void* stream, char* err, size_t cap);
+
+/*
+ * The combine kernel over f32 partials: ohat f32 [splits][rows_total][128], lse f32 [splits][rows_total] (base 2) -> out bf16
+ * [rows_total][128]. Same arithmetic as the combine8h kernel behind fmha_mxfp8_launch (crates/amdgpu-tile/src/epilogue.rs:117-146), which
+ * reads f16 partials like the reference; this entry is for partials written with FMHA_MXFP8_FLAG_F32_PARTIALS, e.g. after they have been
+ * exchanged between GPUs (`splits` = number of key ranges). No counterpart in the reference, which has one GPU and f16 partials only.
+ * ohat and out 16-byte aligned. Returns 0, FMHA_MXFP8_E_ARG, or minus a cudaError_t.
+ */
+int fmha_mxfp8_combine_f32(const void* ohat, const void* lse, void* out, uint32_t rows_total, uint32_t splits, void* stream);
 
 /*
  * The quantisers in front of the path: bf16 activations -> the MXFP8 operands the attention kernels take. The reference has no device

@@ -174,26 +174,36 @@ def test_split_vs_unsplit_ulp_gate(oracle):
 
 
 def test_combine_kernel_against_cpu_restatement(oracle, abi):
-    """The combine kernel alone, through fmha_mxfp8_launch: random partials with wide log-sum-exp spread, ragged row counts, 1..8 splits.
-    Same arithmetic as crates/amdgpu-tile/src/epilogue.rs:117-146, so the bf16 words agree except where ex2.approx moves a rounding."""
+    """The combine kernel alone: random partials with wide log-sum-exp spread, ragged row counts, 1..8 splits. Through fmha_mxfp8_launch
+    with f16 partials (the reference's combine8h format, crates/amdgpu-kernels/src/fmha/io.rs:161-185) inside the f32-sized allocation the
+    contract declares, and through fmha_mxfp8_combine_f32 with f32 partials. Same arithmetic as crates/amdgpu-tile/src/epilogue.rs:117-146,
+    so the bf16 words agree except where ex2.approx moves a rounding."""
     lib = abi.load()
     rng = np.random.default_rng(3)
     for rows, splits in ((1, 1), (77, 2), (4096, 4), (1000, 8), (65536, 8)):
         ohat = rng.standard_normal((splits, rows, 128)).astype(np.float32)
         lse = (rng.standard_normal((splits, rows)) * 6).astype(np.float32)
-        d_o, d_l = torch.from_numpy(ohat).cuda(), torch.from_numpy(lse).cuda()
-        out = torch.zeros(rows, 128, dtype=torch.bfloat16, device="cuda")
-        a = abi.CombineArgs(ptr_ohat=d_o.data_ptr(), ptr_lse=d_l.data_ptr(), ptr_out=out.data_ptr(), rows_total=rows, d=128, splits=splits)
-        sz = abi.BufferSizes(ptr_ohat=ohat.nbytes, ptr_lse=lse.nbytes, ptr_out=rows * 256)
-        g = abi.grid3(0, 0, 0)
-        assert lib.fmha_mxfp8_grid(abi.COMBINE8H, C.byref(a), None, g) == 0
-        assert lib.fmha_mxfp8_validate(abi.COMBINE8H, C.byref(a), C.byref(sz), g, None, None, 0) == 0
-        assert lib.fmha_mxfp8_launch(abi.COMBINE8H, C.byref(a), g, None) == 0
-        torch.cuda.synchronize()
-        got = oracle.bf16_to_f32(out.view(torch.int16).cpu().numpy().view(np.uint16))
-        want = oracle.bf16_to_f32(oracle.combine_f32(ohat, lse, rows, splits))
-        assert np.abs(got - want).max() <= 2.0 ** -7 * max(1.0, np.abs(want).max())
-        assert (got != want).mean() < 0.02
+        d_l = torch.from_numpy(lse).cuda()
+        for f32 in (False, True):
+            part = ohat if f32 else ohat.astype(np.float16)
+            buf = torch.zeros(splits * rows * 512, dtype=torch.uint8, device="cuda")   # the contract's extent, whatever the partial format
+            buf[: part.nbytes] = torch.from_numpy(part.view(np.uint8).reshape(-1)).cuda()
+            out = torch.zeros(rows, 128, dtype=torch.bfloat16, device="cuda")
+            if f32:
+                assert lib.fmha_mxfp8_combine_f32(buf.data_ptr(), d_l.data_ptr(), out.data_ptr(), rows, splits, None) == 0
+            else:
+                a = abi.CombineArgs(ptr_ohat=buf.data_ptr(), ptr_lse=d_l.data_ptr(), ptr_out=out.data_ptr(), rows_total=rows, d=128, splits=splits)
+                sz = abi.BufferSizes(ptr_ohat=buf.numel(), ptr_lse=lse.nbytes, ptr_out=rows * 256)
+                g = abi.grid3(0, 0, 0)
+                assert lib.fmha_mxfp8_grid(abi.COMBINE8H, C.byref(a), None, g) == 0
+                assert lib.fmha_mxfp8_validate(abi.COMBINE8H, C.byref(a), C.byref(sz), g, None, None, 0) == 0
+                assert lib.fmha_mxfp8_launch(abi.COMBINE8H, C.byref(a), g, None) == 0
+            torch.cuda.synchronize()
+            got = oracle.bf16_to_f32(out.view(torch.int16).cpu().numpy().view(np.uint16))
+            want = oracle.bf16_to_f32(oracle.combine_f32(part.astype(np.float32), lse, rows, splits))
+            assert np.abs(got - want).max() <= 2.0 ** -7 * max(1.0, np.abs(want).max()), (rows, splits, f32)
+            assert (got != want).mean() < 0.02, (rows, splits, f32)
+    assert lib.fmha_mxfp8_combine_f32(None, d_l.data_ptr(), d_l.data_ptr(), 1, 1, None) == 6
 
 
 def test_fmha_mxfp8_auto_entry_point(oracle, abi):
