@@ -19,6 +19,7 @@ FLAG_CAUSAL = 0x8
 FLAG_F32_PARTIALS = 0x10
 FLAG_NO_TAIL_SPLIT = 0x20
 TRACE_BYTES = 4 * (16384 + 16384 + 256 + 4096 + 2048)
+PEER_HANDLE_BYTES, PEER_MAX_GPUS, PEER_PLAN_BYTES = 64, 8, 1152
 STATIC_SCRATCH_MAX_ROW_SPLITS = 65536   # FMHA_MXFP8_STATIC_SCRATCH_MAX_ROW_SPLITS
 
 ERROR_CLASSES = {1: "GV-HOST-EXTENT", 2: "GV-HOST-KA-RANGE", 3: "GV-HOST-KA-IS", 4: "GV-HOST-GRID", 5: "GV-HOST-SYM", 6: "ARG", 7: "DEVICE"}
@@ -30,7 +31,7 @@ def _pad(n, i):
 
 _COMMON = [
     ("ptr_o", C.c_void_p), _pad(8, 0), ("ptr_q", C.c_void_p), _pad(8, 1), ("ptr_k", C.c_void_p), _pad(8, 2), ("ptr_v", C.c_void_p),
-    _pad(8, "3a"), ("ext_ptr_lse", C.c_void_p), ("ext_ptr_v_blockscale", C.c_void_p), _pad(8, "3b"), ("ext_flags", C.c_uint32), _pad(4, "3c"),
+    ("ext_ptr_peer_plan", C.c_void_p), ("ext_ptr_lse", C.c_void_p), ("ext_ptr_v_blockscale", C.c_void_p), _pad(8, "3b"), ("ext_flags", C.c_uint32), _pad(4, "3c"),
     ("s_seq_len", C.c_uint32), _pad(12, 4), ("s_Seqs", C.c_uint32), _pad(28, 5), ("s_Hs", C.c_uint32), _pad(12, 6), ("s_Bs", C.c_uint32), _pad(12, 7),
     ("s_gqa", C.c_uint32), _pad(12, 8), ("s_k_Seqs", C.c_uint32), _pad(12, 9), ("s_k_Hs", C.c_uint32), _pad(12, 10), ("s_k_Bs", C.c_uint32), _pad(44, 11),
     ("s_kv_seq_len", C.c_uint32), _pad(44, 12), ("s_q_head_num", C.c_uint32), _pad(12, 13), ("s_v_Seqs", C.c_uint32), _pad(12, 14),
@@ -78,6 +79,7 @@ class Problem(C.Structure):
 
 
 assert C.sizeof(AttnArgs) == 656 and C.sizeof(KvSplitArgs) == 648 and C.sizeof(CombineArgs) == 36
+assert AttnArgs.ext_ptr_peer_plan.offset == 0x38 and KvSplitArgs.ext_ptr_peer_plan.offset == 0x38
 assert AttnArgs.s_seq_len.offset == 0x60 and AttnArgs.ptr_q_descale.offset == 0x200 and AttnArgs.abi_tail.offset == 0x280
 assert KvSplitArgs.ptr_ohat.offset == 0x270 and KvSplitArgs.kvs_rows_total.offset == 0x284
 
@@ -121,6 +123,21 @@ def load():
     lib.fmha_mxfp8_kvsplit_static_scratch.argtypes = [C.POINTER(Problem), C.c_uint32, C.c_void_p, C.c_char_p, C.c_size_t]
     lib.fmha_mxfp8_combine_f32.restype = C.c_int
     lib.fmha_mxfp8_combine_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]
+    vpp = C.POINTER(C.c_void_p)
+    lib.fmha_mxfp8_peer_alloc.restype = C.c_int
+    lib.fmha_mxfp8_peer_alloc.argtypes = [C.c_size_t, vpp, C.c_void_p]
+    lib.fmha_mxfp8_peer_open.restype = C.c_int
+    lib.fmha_mxfp8_peer_open.argtypes = [C.c_void_p, vpp]
+    lib.fmha_mxfp8_peer_close.restype = C.c_int
+    lib.fmha_mxfp8_peer_close.argtypes = [C.c_void_p]
+    lib.fmha_mxfp8_peer_free.restype = C.c_int
+    lib.fmha_mxfp8_peer_free.argtypes = [C.c_void_p]
+    lib.fmha_mxfp8_peer_plan_build.restype = C.c_int
+    lib.fmha_mxfp8_peer_plan_build.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, vpp, vpp, C.c_void_p, C.c_void_p]
+    lib.fmha_mxfp8_combine_f32_scatter.restype = C.c_int
+    lib.fmha_mxfp8_combine_f32_scatter.argtypes = [C.c_void_p, C.c_void_p, vpp, C.c_uint32, C.c_uint64, C.c_uint32, C.c_uint32, C.c_void_p]
+    lib.fmha_mxfp8_copy_async.restype = C.c_int
+    lib.fmha_mxfp8_copy_async.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
     lib.fmha_mxfp8_quantize_qk.restype = C.c_int
     lib.fmha_mxfp8_quantize_qk.argtypes = [C.c_void_p, C.c_uint64, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.fmha_mxfp8_quantize_v.restype = C.c_int
@@ -140,7 +157,8 @@ def load():
 EXPORTS = (
     "fmha_mxfp8_kernel_name", "fmha_mxfp8_kernarg_size", "fmha_mxfp8_workgroup_size", "fmha_mxfp8_validate", "fmha_mxfp8_grid",
     "fmha_mxfp8_launch", "fmha_mxfp8_dispatch", "fmha_mxfp8_auto", "fmha_mxfp8_device_status", "fmha_mxfp8_trace_attach",
-    "fmha_mxfp8_mma_issue_ceiling", "fmha_mxfp8_selftest_bounded_wait", "fmha_mxfp8_kvsplit_static_scratch", "fmha_mxfp8_quantize_qk", "fmha_mxfp8_quantize_v", "fmha_mxfp8_combine_f32",
+    "fmha_mxfp8_mma_issue_ceiling", "fmha_mxfp8_selftest_bounded_wait", "fmha_mxfp8_kvsplit_static_scratch", "fmha_mxfp8_quantize_qk", "fmha_mxfp8_quantize_v", "fmha_mxfp8_combine_f32", "fmha_mxfp8_peer_alloc", "fmha_mxfp8_peer_open", "fmha_mxfp8_peer_close", "fmha_mxfp8_peer_free",
+    "fmha_mxfp8_peer_plan_build", "fmha_mxfp8_combine_f32_scatter", "fmha_mxfp8_copy_async",
 )
 
 

@@ -38,10 +38,12 @@ __device__ __forceinline__ float2 h2_to_f2(uint32_t h2) {
     return f;
 }
 
+// kScatter: the bf16 rows go to several output buffers (this GPU's and its peers': the all-gather of the row slices done by the stores).
 // kF32: the partial rows are f32 (512 bytes per row; partials that crossed GPUs), else f16 (256 bytes per row, the reference's format).
-template <bool kF32>
+template <bool kF32, bool kScatter = false>
 __global__ void __launch_bounds__(256)
-kvsplit_combine_kernel(const void* __restrict__ ohat, const float* __restrict__ lse2, uint8_t* __restrict__ out, uint32_t rows_total, uint32_t splits) {
+kvsplit_combine_kernel(const void* __restrict__ ohat, const float* __restrict__ lse2, uint8_t* __restrict__ out, uint32_t rows_total, uint32_t splits,
+                       const OutPointers outs = OutPointers{}) {
     const uint64_t ngroups = static_cast<uint64_t>(rows_total) * 16u;   // 16 groups of 8 elements per row
     for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < ngroups; t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
         const uint64_t row = t >> 4;
@@ -76,11 +78,25 @@ kvsplit_combine_kernel(const void* __restrict__ ohat, const float* __restrict__ 
             const __nv_bfloat162 b2 = __floats2bfloat162_rn(acc[2 * e] * rd, acc[2 * e + 1] * rd);
             wv[e] = *reinterpret_cast<const uint32_t*>(&b2);
         }
-        *reinterpret_cast<uint4*>(out + t * 16u) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+        if (kScatter) {
+            for (uint32_t i = 0; i < outs.n; ++i) *reinterpret_cast<uint4*>(outs.out[i] + t * 16u) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+        } else {
+            *reinterpret_cast<uint4*>(out + t * 16u) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+        }
     }
 }
 
 }  // namespace
+
+cudaError_t launch_combine_scatter(const void* ohat, const float* lse2, const OutPointers& outs, uint32_t rows, uint32_t splits, cudaStream_t stream) {
+    const uint64_t ngroups = static_cast<uint64_t>(rows) * 16u;
+    uint64_t blocks = (ngroups + 255u) / 256u;
+    const uint64_t cap = 148u * 8u * 4u;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    kvsplit_combine_kernel<true, true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(ohat, lse2, nullptr, rows, splits, outs);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_combine(const void* ohat, bool f32_partials, const float* lse2, uint8_t* out, uint32_t rows_total, uint32_t splits, cudaStream_t stream) {
     const uint64_t ngroups = static_cast<uint64_t>(rows_total) * 16u;

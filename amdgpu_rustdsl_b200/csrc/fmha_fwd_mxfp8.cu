@@ -41,7 +41,6 @@
 #include <cuda_bf16.h>
 
 #include <atomic>
-#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 #include <cuda_fp8.h>
@@ -112,8 +111,10 @@ struct SmemLayout {
     static constexpr uint32_t sfv = sfk + kStages * kSfBytes;    // V block scales of a key tile (extension), same 32 x 16-byte pattern as the K scales
     static constexpr uint32_t sf_one = sfv + kStages * kSfBytes;  // 512 bytes of E8M0 1.0: the factors of P and of the ones columns
     static constexpr uint32_t xref = sf_one + kSfBytes;
-    static constexpr uint32_t xfin = xref + 4 * 128 * 8;          // [item parity 2][row 128]: the row's reference after the item's last tile
-    static constexpr uint32_t xstat = xfin + 2 * 128 * 4;         // [row 128] x {row sum, reference} of the partner's half item (launches as pairs)
+    // [item ordinal % 4][row 128]: the row's reference after the item's last tile, for the epilogue warpgroup. Four slots and a write
+    // behind the wait for this parity's previous P V: with one-tile items a softmax group is otherwise two items ahead of the epilogue
+    static constexpr uint32_t xfin = xref + 4 * 128 * 8;
+    static constexpr uint32_t xstat = xfin + 4 * 128 * 4;         // [row 128] x {row sum, reference} of the partner's half item (launches as pairs)
     static constexpr uint32_t bars = xstat + 128 * 8;
     // barriers (8 bytes each): q_full[2], q_empty[2], k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], s_free[2],
     // p_full[2], o_done[2], o_free, o_full, ref_ready[4], peer_rdy, peer_data
@@ -817,15 +818,16 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #ifdef MXA_REF_MBAR
                 mbar_arrive(bar_ref_ready(g));
 #endif
-                // the item's last tile leaves the row's final reference for the epilogue warpgroup's log-sum-exp (ordered before this
-                // thread's arrive on p_full, which the last P V, and through it the epilogue's o_full, come after)
-                if (want_fin && j == n_tiles - 1) *reinterpret_cast<volatile float*>(smem_gen + SmemLayout::xfin + 4u * ((n & 1u) * 128u + r)) = ref;
                 f = move ? ex2_approx(old_ref - ref) : 1.0f;   // 0 on the first tile (old reference -inf); an exact power of two for integer references
                 stamp(st_trace, par, static_cast<int>(g), 4);
                 // P V of this parity's previous tile must be done before its P columns are overwritten (and, observed in order, this keeps
                 // the phase parity of the other parity's barrier below unambiguous)
                 if (!pv_seen && k > 0 && !mbar_wait(bar_o_done(par), (k - 1u) & 1u, abort_flag)) ok = false;
                 stamp(st_trace, par, static_cast<int>(g), 5);
+                // The item's last tile leaves the row's final reference for the epilogue warpgroup's log-sum-exp: before this thread's arrive
+                // on p_full (which the last P V, and through it the epilogue's o_full, come after), and behind the wait above: P V of tile
+                // g - 2 is done, so P V of g - 3 is, so the epilogue has taken the item four back out (o_free) and read its slot
+                if (want_fin && j == n_tiles - 1) *reinterpret_cast<volatile float*>(smem_gen + SmemLayout::xfin + 4u * ((n & 3u) * 128u + r)) = ref;
                 if (__builtin_expect(j > 0 && __any_sync(0xFFFFFFFFu, move), 0)) {
                     // O holds P V of all the item's tiles before j once the other parity's last P V is done; P V of tile j cannot start before this thread's arrive below
                     if (!mbar_wait(bar_o_done(par ^ 1u), ((g - 1u) >> 1) & 1u, abort_flag)) ok = false;
@@ -921,7 +923,7 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             stamp(ep_trace, 3, 24 + static_cast<int>(n), 1);
             uint32_t lv;
             asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(lv) : "r"(t_l) : "memory");
-            const float ref_fin = want_fin ? *reinterpret_cast<volatile float*>(smem_gen + SmemLayout::xfin + 4u * ((n & 1u) * 128u + r)) : 0.0f;
+            const float ref_fin = want_fin ? *reinterpret_cast<volatile float*>(smem_gen + SmemLayout::xfin + 4u * ((n & 3u) * 128u + r)) : 0.0f;
             tmem_wait_ld();
             float l = __uint_as_float(lv);
             float ref_out = ref_fin;
@@ -1031,7 +1033,16 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 }
             } else {
                 // f32 partial: four pieces of 32 columns (128 bytes per row), alternating between the two staging tiles; a tile is written
-                // again once the store that last used it has read it out
+                // again once the store that last used it has read it out. With a routing plan the rows go to the GPU that combines them
+                // (its receive slot of this GPU), else to this launch's own partial buffer.
+                const CUtensorMap* omap = &tm_o;
+                int o_row = static_cast<int>(it.row0), o_split = static_cast<int>(it.split);
+                if (kSplit && p.peer != nullptr) {
+                    const uint32_t dest = it.row0 / p.peer->dest_rows;
+                    omap = &p.peer->maps[dest];
+                    o_row = static_cast<int>(it.row0 - dest * p.peer->dest_rows);
+                    o_split = static_cast<int>(p.peer->rank);
+                }
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t o[32];
@@ -1068,15 +1079,17 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     fence_proxy_async_smem();
                     named_bar_sync(kEpiBar, 128u);
                     if (issuer) {
-                        tma_store_5d(&tm_o, stg + static_cast<uint32_t>(c & 1) * 16384u, 32 * c, static_cast<int>(it.head), static_cast<int>(it.row0),
-                                     static_cast<int>(it.batch), static_cast<int>(it.split));
+                        tma_store_5d(omap, stg + static_cast<uint32_t>(c & 1) * 16384u, 32 * c, static_cast<int>(it.head), o_row, static_cast<int>(it.batch), o_split);
                         bulk_commit_group();
                     }
                 }
             }
             if (row < p.S && want_fin) {   // rows past the sequence are computed on clamped scales and not stored (block3.rs:194)
                 const float lse2 = ref_out - kPOffset + lg2_approx(l);   // log2 of sum_j 2^(s_j)
-                if (kSplit) {
+                if (kSplit && p.peer != nullptr) {
+                    const uint32_t dest = it.row0 / p.peer->dest_rows, n_rows = p.peer->dest_rows * p.H;
+                    p.peer->lse[dest][static_cast<size_t>(p.peer->rank) * n_rows + static_cast<size_t>(row - dest * p.peer->dest_rows) * p.H + it.head] = lse2;
+                } else if (kSplit) {
                     const size_t prow = static_cast<size_t>(it.split) * p.rows_total + (static_cast<size_t>(it.batch) * p.S + row) * p.H + it.head;
                     p.lse2[prow] = lse2;
                 } else if (p.lse_nat != nullptr) {
@@ -1178,7 +1191,8 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
     // The last round. n_items = rounds * grid + tail: when the tail fills at most half of the grid, its items would keep a few CTAs busy
     // for a whole item while the rest idle. They are then cut in two key ranges each, the grid is launched as clusters of two CTAs, and
     // each pair merges its two halves through distributed shared memory (no workspace). Long-sequence recipe only (integer references
-    // merge exactly), no causal mask (its items differ in length and are balanced by their order), at least 4 key tiles per half.
+    // merge exactly), no causal mask (its items differ in length and are balanced by their order), and only for items of at least
+    // kMinTilesForPairs key tiles: a launch as pairs and the merge cost about 7-9 us (measured), which half an item has to outweigh.
     const uint32_t ntiles_total = (p.SK + kKeys - 1) / kKeys;
     uint32_t min_tiles = ntiles_total;
     if (split) {
@@ -1186,7 +1200,8 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
         min_tiles = ntiles_total - (p.splits - 1u) * tps;   // the last split's share
     }
     const uint32_t even_sms = static_cast<uint32_t>(sms) & ~1u;
-    if (lazy_recipe && !causal && min_tiles >= 8u && even_sms >= 2u && !(p.flags & kFlagNoTailSplit)) {
+    constexpr uint32_t kMinTilesForPairs = 48u;
+    if (lazy_recipe && !causal && min_tiles >= kMinTilesForPairs && even_sms >= 2u && !(p.flags & kFlagNoTailSplit)) {
         const uint32_t rounds = q.n_items / even_sms, tail = q.n_items - rounds * even_sms;
         if (tail > 0u && 2u * tail <= even_sms) {
             const uint32_t grid = rounds > 0u ? even_sms : 2u * tail;
@@ -1214,10 +1229,6 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
                 q.n_work = q.tail_base + 2u * tail;
                 ctas = grid;
                 which = which_pair;
-                if (getenv("MXA_DEBUG_PAIR_NOSPLIT")) {   // TEMPORARY measurement aid
-                    q.tail_base = q.n_items; q.n_work = q.n_items;
-                    ctas = q.n_items < even_sms ? ((q.n_items + 1u) & ~1u) : even_sms;
-                }
             }
         }
     }

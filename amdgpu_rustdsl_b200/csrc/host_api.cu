@@ -17,7 +17,7 @@ static_assert(sizeof(fmha_mxfp8_kvsplit_args) == 648, "kvsplit kernarg size");
 static_assert(sizeof(fmha_mxfp8_combine_args) == 36, "combine kernarg size");
 #define OFFCHK(T, f, o) static_assert(offsetof(T, f) == (o), #T "." #f " offset")
 OFFCHK(fmha_mxfp8_attn_args, ptr_o, 0x000); OFFCHK(fmha_mxfp8_attn_args, ptr_q, 0x010); OFFCHK(fmha_mxfp8_attn_args, ptr_k, 0x020);
-OFFCHK(fmha_mxfp8_attn_args, ptr_v, 0x030); OFFCHK(fmha_mxfp8_attn_args, ext_ptr_lse, 0x040); OFFCHK(fmha_mxfp8_attn_args, ext_ptr_v_blockscale, 0x048);
+OFFCHK(fmha_mxfp8_attn_args, ptr_v, 0x030); OFFCHK(fmha_mxfp8_attn_args, ext_ptr_peer_plan, 0x038); OFFCHK(fmha_mxfp8_attn_args, ext_ptr_lse, 0x040); OFFCHK(fmha_mxfp8_attn_args, ext_ptr_v_blockscale, 0x048);
 OFFCHK(fmha_mxfp8_attn_args, ext_flags, 0x058); OFFCHK(fmha_mxfp8_attn_args, s_seq_len, 0x060); OFFCHK(fmha_mxfp8_attn_args, s_Seqs, 0x070);
 OFFCHK(fmha_mxfp8_attn_args, s_Hs, 0x090); OFFCHK(fmha_mxfp8_attn_args, s_Bs, 0x0A0); OFFCHK(fmha_mxfp8_attn_args, s_gqa, 0x0B0);
 OFFCHK(fmha_mxfp8_attn_args, s_k_Seqs, 0x0C0); OFFCHK(fmha_mxfp8_attn_args, s_k_Hs, 0x0D0); OFFCHK(fmha_mxfp8_attn_args, s_k_Bs, 0x0E0);
@@ -247,6 +247,9 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
         p.split_log2 = log2_u32(p.splits);
         p.rows_total = s->kvs_rows_total;
         p.ohat = s->ptr_ohat;
+        // the partial rows go to the GPUs that combine them (extension): f32 partials, one batch element, no V block scales
+        p.peer = static_cast<const b200mx::PeerPlan*>(a->ext_ptr_peer_plan);
+        if (p.peer != nullptr && (!(p.flags & FMHA_MXFP8_FLAG_F32_PARTIALS) || grid[2] != s->kvs_splits || s->kvs_splits != 1u)) return FMHA_MXFP8_E_ARG;
         p.lse2 = static_cast<float*>(s->ptr_lse);
         B = grid[2] / p.splits;
     }
@@ -272,6 +275,9 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
 }  // namespace
 
 namespace b200mx {
+int encode_partial_map_f32(CUtensorMap* m, void* base, uint64_t seq, uint64_t heads, uint64_t batches, uint64_t splits) {
+    return make_partial_map(m, base, seq, heads, batches, splits, true);
+}
 __device__ uint32_t g_status_word = 0;
 uint32_t* device_status_word() {
     void* p = nullptr;

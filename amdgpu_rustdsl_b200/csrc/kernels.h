@@ -9,6 +9,23 @@ namespace b200mx {
 // Keys per K / V tile of the attention kernel = rows of the K and V tensor maps' boxes.
 constexpr int kKeysPerTile = 128;
 
+constexpr int kMaxPeerGpus = 8;
+
+// Device-resident routing plan of a key-range-sharded launch (peer_exchange.cu): where the rows of this GPU's f32 partial go.
+// Destination d combines the query rows [d * dest_rows, (d + 1) * dest_rows); its receive buffer is f32 [source GPU][dest_rows][H][128]
+// (maps[d]: the same 5-D map as a local partial, source GPU in the place of the split) and f32 [source GPU][dest_rows * H] (lse[d]).
+struct alignas(128) PeerPlan {
+    CUtensorMap maps[kMaxPeerGpus];
+    float* lse[kMaxPeerGpus];
+    uint32_t world, rank, dest_rows, pad;
+};
+
+// bf16 output buffers of the GPUs a combine stores its rows to (already advanced to the rows' offset)
+struct OutPointers {
+    uint8_t* out[kMaxPeerGpus];
+    uint32_t n;
+};
+
 // Everything one attention launch needs, already decoded from the packed kernel arguments.
 struct AttnParams {
     // outputs
@@ -21,6 +38,7 @@ struct AttnParams {
     const uint8_t* k_descale;   // E8M0 [B,SK,HK,4]
     const float* v_descale;     // one f32
     const uint8_t* v_blockscale;  // extension: E8M0 [B,ceil(SK/32),HK,128], may be null
+    const PeerPlan* peer;         // extension (split kernel, f32 partials, B = 1): store the partial rows to the GPUs that combine them; may be null
     // shape
     uint32_t S, SK, H, HK, gqa_shift;
     uint32_t o_row_stride, o_batch_stride;    // bytes
@@ -43,6 +61,7 @@ struct AttnParams {
 cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnParams& p,
                              uint32_t B, bool split, uint32_t rows_per_cta, cudaStream_t stream);
 
+cudaError_t launch_combine_scatter(const void* ohat, const float* lse2, const OutPointers& outs, uint32_t rows, uint32_t splits, cudaStream_t stream);
 cudaError_t launch_combine(const void* ohat, bool f32_partials, const float* lse2, uint8_t* out, uint32_t rows_total, uint32_t splits, cudaStream_t stream);
 
 // Quantisers in front of the path (quantize.cu): bf16 -> e4m3 + E8M0 per 32 head-dim elements (Q with `mul` folded in, K), bf16 -> e4m3 +

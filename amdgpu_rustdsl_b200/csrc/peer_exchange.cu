@@ -1,0 +1,101 @@
+// Key-range sharding across the GPUs of one node without a collective for the partials: every GPU's split kernel stores the rows of
+// its f32 partial straight into the memory of the GPU that will combine them (TMA tile stores and plain stores to peer memory over
+// NVLink, as the tiles come out of tensor memory, so the transfer runs under the remaining compute), and every GPU's combine kernel
+// stores its bf16 row slice into every GPU's output buffer. Between the two kernels, and after the second, the ranks only need a barrier.
+// The reference has no multi-GPU code; the algebra is its KV-split one with "split = GPU" (crates/amdgpu-stage/src/components.rs:58-74,
+// crates/amdgpu-tile/src/epilogue.rs:117-146).
+//
+// This file holds the host side: device buffers that other processes of the node can map (CUDA IPC; one process per GPU), and the
+// device-resident plan (one tensor map and one log-sum-exp pointer per destination GPU) that the split kernel reads.
+// No TMA load ever touches peer memory here, with or without multicast: peers are only written to.
+#include "../../include/fmha_mxfp8_abi.h"
+#include "kernels.h"
+
+#include <cstring>
+
+namespace b200mx {
+int encode_partial_map_f32(CUtensorMap* m, void* base, uint64_t seq, uint64_t heads, uint64_t batches, uint64_t splits);   // host_api.cu
+}
+
+extern "C" {
+
+int fmha_mxfp8_peer_alloc(size_t bytes, void** dev_ptr, void* handle64) {
+    if (!dev_ptr || !handle64 || bytes == 0) return FMHA_MXFP8_E_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == FMHA_MXFP8_PEER_HANDLE_BYTES, "IPC handle size");
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) return -static_cast<int>(e);
+    e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) { cudaFree(p); return -static_cast<int>(e); }
+    std::memcpy(handle64, &h, sizeof h);
+    *dev_ptr = p;
+    return 0;
+}
+
+int fmha_mxfp8_peer_open(const void* handle64, void** dev_ptr) {
+    if (!handle64 || !dev_ptr) return FMHA_MXFP8_E_ARG;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle64, sizeof h);
+    const cudaError_t e = cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+int fmha_mxfp8_peer_close(void* dev_ptr) {
+    if (!dev_ptr) return FMHA_MXFP8_E_ARG;
+    const cudaError_t e = cudaIpcCloseMemHandle(dev_ptr);
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+int fmha_mxfp8_peer_free(void* dev_ptr) {
+    if (!dev_ptr) return FMHA_MXFP8_E_ARG;
+    const cudaError_t e = cudaFree(dev_ptr);
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+int fmha_mxfp8_peer_plan_build(uint32_t world, uint32_t rank, uint32_t H, uint32_t S, void* const* ohat_recv, void* const* lse_recv, void* plan_dev, void* stream) {
+    if (world < 2 || world > FMHA_MXFP8_PEER_MAX_GPUS || rank >= world || H == 0 || S == 0 || !ohat_recv || !lse_recv || !plan_dev) return FMHA_MXFP8_E_ARG;
+    // a 128-row block of queries must belong to one destination: whole blocks per GPU
+    if (S % world != 0 || (S / world) % 128u != 0) return FMHA_MXFP8_E_ARG;
+    if (reinterpret_cast<uintptr_t>(plan_dev) & 127u) return FMHA_MXFP8_E_ARG;
+    static_assert(sizeof(b200mx::PeerPlan) == FMHA_MXFP8_PEER_PLAN_BYTES, "plan size");
+    b200mx::PeerPlan plan;
+    std::memset(&plan, 0, sizeof plan);
+    plan.world = world;
+    plan.rank = rank;
+    plan.dest_rows = S / world;
+    for (uint32_t d = 0; d < world; ++d) {
+        if (!ohat_recv[d] || !lse_recv[d]) return FMHA_MXFP8_E_ARG;
+        // destination d's receive buffer: f32 [source GPU][its S / world query rows][H][128]
+        const int r = b200mx::encode_partial_map_f32(&plan.maps[d], ohat_recv[d], plan.dest_rows, H, 1, world);
+        if (r) return r;
+        plan.lse[d] = static_cast<float*>(lse_recv[d]);
+    }
+    const cudaError_t e = cudaMemcpyAsync(plan_dev, &plan, sizeof plan, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return -static_cast<int>(e);
+    const cudaError_t e2 = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));   // `plan` lives on this stack frame
+    return e2 == cudaSuccess ? 0 : -static_cast<int>(e2);
+}
+
+int fmha_mxfp8_combine_f32_scatter(const void* ohat, const void* lse, void* const* outs, uint32_t n_outs, uint64_t row_offset, uint32_t rows, uint32_t splits,
+                                   void* stream) {
+    if (!ohat || !lse || !outs || n_outs == 0 || n_outs > FMHA_MXFP8_PEER_MAX_GPUS || rows == 0 || splits == 0) return FMHA_MXFP8_E_ARG;
+    b200mx::OutPointers op;
+    std::memset(&op, 0, sizeof op);
+    for (uint32_t i = 0; i < n_outs; ++i) {
+        if (!outs[i] || (reinterpret_cast<uintptr_t>(outs[i]) & 15u)) return FMHA_MXFP8_E_ARG;
+        op.out[i] = static_cast<uint8_t*>(outs[i]) + row_offset * 256u;
+    }
+    op.n = n_outs;
+    const cudaError_t e = b200mx::launch_combine_scatter(ohat, static_cast<const float*>(lse), op, rows, splits, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+int fmha_mxfp8_copy_async(void* dst, const void* src, size_t bytes, void* stream) {
+    if (!dst || !src) return FMHA_MXFP8_E_ARG;
+    const cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+}  // extern "C"

@@ -41,7 +41,7 @@ def kv_range_shard(SK: int, rank: int, world: int):
     return lo, hi
 
 
-def local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, lse, *, stream=None, check=True):
+def local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, lse, *, stream=None, check=True, peer_plan=None):
     """One rank's contribution to a key-range-sharded forward: the split kernel with splits = 1 over the local keys, writing the
     normalised f32 partial O [rows_total,128] and base-2 log-sum-exp [rows_total] of all queries."""
     import ctypes as C
@@ -60,6 +60,11 @@ def local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, l
     a.ptr_ohat, a.ptr_lse, a.kvs_splits, a.kvs_rows_total = ohat.data_ptr(), lse.data_ptr(), 1, rows_total
     sizes = _abi.BufferSizes(ptr_q=_nbytes(q), ptr_k=_nbytes(k_local), ptr_v=_nbytes(v_local), ptr_o=B * S * H * 256, ptr_q_descale=_nbytes(q_scale),
                              ptr_k_descale=_nbytes(k_scale_local), ptr_v_descale=_nbytes(v_scale), ptr_ohat=_nbytes(ohat), ptr_lse=_nbytes(lse))
+    if peer_plan is not None:
+        # the partial rows go to the GPUs that combine them (fmha_mxfp8_peer_plan_build): ohat / lse are not written and only stand in
+        # for the contract's pointer fields; their extents are not this launch's concern
+        a.ext_ptr_peer_plan = peer_plan
+        sizes.ptr_ohat, sizes.ptr_lse = rows_total * 512, rows_total * 4
     syms = _abi.Symbols(B=B, HK=HK, KL=0)
     with torch.cuda.device(q.device):
         _check_launch(lib, _abi.KVSPLIT, a, sizes, _abi.grid3(math.ceil(S / 256), H, B), syms, stream, check)
@@ -140,25 +145,178 @@ def fmha_fwd_mxfp8_kv_sharded(q, k_local, v_local, q_scale, k_scale_local, v_sca
     combine_gathered(ws["ohat_all"], ws["lse_all"], out, world)
 
 
+class PeerBuffers:
+    """One device allocation per rank that every process of the node maps (CUDA IPC through the library's fmha_mxfp8_peer_* entries), cut
+    into this rank's receive slots for the partials [world][n][128] f32, for their log-sum-exps [world][n] f32, and a whole bf16 output
+    [rows_total][128] that every rank's combine stores its row slice into. `ptr[r]` is rank r's allocation as mapped here."""
+
+    def __init__(self, rows_total: int, world: int, rank: int, device, group=None):
+        """Collective over `group`: every rank allocates, the ranks agree that all succeeded, exchange the handles, map each other's
+        buffers and agree again. `ok` tells whether the buffers are usable on every rank; a rank never stops half way through the
+        collectives, whatever failed locally."""
+        import ctypes as C
+        import torch
+        import torch.distributed as dist
+        from . import _abi
+        self.lib = lib = _abi.load()
+        self.world, self.rank, self.device = world, rank, device
+        n = rows_total // world
+        self.n = n
+        al = lambda x: (x + 255) // 256 * 256   # noqa: E731
+        self.off_lse = al(world * n * D * 4)
+        self.off_out = self.off_lse + al(world * n * 4)
+        self.bytes = self.off_out + al(rows_total * D * 2)
+        self.own = C.c_void_p()
+        handle = (C.c_ubyte * _abi.PEER_HANDLE_BYTES)()
+        self.ptr, self.opened, self.error = [None] * world, [], None
+
+        def agree(flag):
+            t = torch.tensor([1 if flag else 0], dtype=torch.int32, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+            return int(t.item()) == 1
+
+        with torch.cuda.device(device):
+            rc = lib.fmha_mxfp8_peer_alloc(self.bytes, C.byref(self.own), handle)
+            if rc:
+                self.error = f"fmha_mxfp8_peer_alloc failed with code {rc}"
+                self.own = None
+            self.ok = agree(rc == 0)
+            if not self.ok:
+                return
+            handles = [None] * world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            good = True
+            for r in range(world):
+                if r == rank:
+                    self.ptr[r] = self.own.value
+                    continue
+                hp = (C.c_ubyte * _abi.PEER_HANDLE_BYTES).from_buffer_copy(handles[r])
+                q = C.c_void_p()
+                rc = lib.fmha_mxfp8_peer_open(hp, C.byref(q))
+                if rc:
+                    self.error = f"fmha_mxfp8_peer_open(rank {r}) failed with code {rc}"
+                    good = False
+                    break
+                self.ptr[r] = q.value
+                self.opened.append(q.value)
+            self.ok = agree(good)
+
+    def close(self, group=None):
+        """Unmap the peers' buffers, wait for every rank to have done so, free the own one."""
+        import ctypes as C
+        import torch
+        import torch.distributed as dist
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=group)   # no rank is still storing into another's buffer
+            for q in self.opened:
+                self.lib.fmha_mxfp8_peer_close(C.c_void_p(q))
+            self.opened = []
+            dist.barrier(group=group)
+            if self.own is not None and self.own.value:
+                self.lib.fmha_mxfp8_peer_free(self.own)
+                self.own = None
+
+
 class KvShardedPlan:
     """Workspaces and schedule of the key-range-sharded forward for one problem size on one rank (`world` = 1 runs the same two
-    kernels without an exchange). `forward` runs a step; `timed_stages` runs steps with CUDA events between the stages."""
+    kernels without an exchange). `forward` runs a step; `timed_stages` runs steps with CUDA events between the stages.
 
-    def __init__(self, rows_total: int, world: int, device, group=None):
+    transport "peer" (one batch element, S / world a multiple of 128 rows): the split kernel stores each row block of its f32 partial
+    straight into the memory of the GPU that combines it, as the block leaves tensor memory (no collective moves partials; the transfer
+    runs under the remaining compute); barrier; every GPU's combine stores its bf16 row slice into every GPU's output; barrier.
+    transport "nccl": split kernel -> all-to-all of the partial row slices -> combine of the own slice -> all-gather of the bf16 slices
+    (or, when the rows do not divide, an all-gather of the whole partials)."""
+
+    def __init__(self, rows_total: int, world: int, device, group=None, transport: str = "auto", B: int = 1, S: int = 0, H: int = 0):
+        import torch
         self.rows_total, self.world, self.device, self.group = rows_total, world, device, group
-        self.ws = kv_sharded_workspace(rows_total, world, device, sliced=True)
+        self.transport = "none" if world == 1 else "nccl"
+        self.peer = None
+        if world > 1 and transport in ("auto", "peer"):
+            ok = B == 1 and S > 0 and H > 0 and S * H == rows_total and S % world == 0 and (S // world) % 128 == 0
+            if ok:
+                self._setup_peer(S, H)
+            elif transport == "peer":
+                raise ValueError("the peer transport needs one batch element and S / world a multiple of 128")
+        self.ws = kv_sharded_workspace(rows_total, world, device, sliced=True) if self.transport != "peer" else {
+            "ohat": torch.empty(1, dtype=torch.float32, device=device), "lse": torch.empty(1, dtype=torch.float32, device=device)}
         self.sliced = "ohat_recv" in self.ws
+
+    def _setup_peer(self, S, H):
+        """All ranks try; the transport is used only if every rank succeeded (a rank that cannot map its peers must not leave the others
+        storing into its memory)."""
+        import ctypes as C
+        import torch
+        import torch.distributed as dist
+        from . import _abi
+        rank = dist.get_rank(self.group)
+        self.peer = PeerBuffers(self.rows_total, self.world, rank, self.device, self.group)
+        good, err = self.peer.ok, self.peer.error
+        if good:
+            try:
+                self.plan_dev = torch.zeros(_abi.PEER_PLAN_BYTES + 128, dtype=torch.uint8, device=self.device)
+                self.plan_ptr = (self.plan_dev.data_ptr() + 127) // 128 * 128
+                pb = self.peer
+                ohat = (C.c_void_p * self.world)(*[pb.ptr[r] for r in range(self.world)])
+                lse = (C.c_void_p * self.world)(*[pb.ptr[r] + pb.off_lse for r in range(self.world)])
+                with torch.cuda.device(self.device):
+                    rc = pb.lib.fmha_mxfp8_peer_plan_build(self.world, rank, H, S, ohat, lse, C.c_void_p(self.plan_ptr), None)
+                if rc:
+                    raise RuntimeError(f"fmha_mxfp8_peer_plan_build failed with code {rc}")
+                self.outs = (C.c_void_p * self.world)(*[pb.ptr[r] + pb.off_out for r in range(self.world)])
+                self.flag = torch.zeros(1, dtype=torch.float32, device=self.device)
+            except Exception as e:   # noqa: BLE001
+                good, err = False, repr(e)
+        t = torch.tensor([1 if good else 0], dtype=torch.int32, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group)
+        if int(t.item()) == 1:
+            self.transport = "peer"
+        else:
+            self.peer_error = err or "another rank could not set the peer buffers up"
+            self.peer.close(self.group)
+            self.peer = None
 
     def describe(self) -> str:
         if self.world == 1:
             return "one rank: split kernel over all keys + combine (splits = 1), no exchange"
+        if self.transport == "peer":
+            return ("key-range shards: the split kernel stores its f32 partial row blocks into the combining GPU's memory over NVLink as they leave tensor memory "
+                    "-> barrier -> every GPU's combine stores its bf16 row slice into every GPU's output -> barrier (no collective moves data)")
         if self.sliced:
             return "key-range shards: split kernel -> NCCL all-to-all of the f32 partial row slices and their log-sum-exps -> combine of the own slice -> NCCL all-gather of the bf16 slices"
         return "key-range shards: split kernel -> NCCL all-gather of the f32 partials -> combine of all rows"
 
+    def _barrier(self):
+        """The ranks line up on the stream: an all-reduce of one float (what follows on the stream starts after every rank got here)."""
+        import torch.distributed as dist
+        dist.all_reduce(self.flag, group=self.group)
+
     def stages(self, q, k_local, v_local, q_scale, k_scale_local, v_scale, out):
         """The step as a list of (name, callable) in stream order."""
         ws, world = self.ws, self.world
+        if self.transport == "peer":
+            import ctypes as C
+            import torch
+            pb = self.peer
+            stream = lambda: C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)   # noqa: E731
+
+            def combine():
+                with torch.cuda.device(self.device):
+                    rc = pb.lib.fmha_mxfp8_combine_f32_scatter(C.c_void_p(pb.own.value), C.c_void_p(pb.own.value + pb.off_lse), self.outs, world,
+                                                               pb.rank * pb.n, pb.n, world, stream())
+                if rc:
+                    raise RuntimeError(f"fmha_mxfp8_combine_f32_scatter failed with code {rc}")
+
+            def take_output():
+                with torch.cuda.device(self.device):
+                    rc = pb.lib.fmha_mxfp8_copy_async(C.c_void_p(out.data_ptr()), C.c_void_p(pb.own.value + pb.off_out), self.rows_total * D * 2, stream())
+                if rc:
+                    raise RuntimeError(f"fmha_mxfp8_copy_async failed with code {rc}")
+
+            return [("split_kernel_storing_to_peers", lambda: local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ws["ohat"], ws["lse"], check=False,
+                                                                            peer_plan=self.plan_ptr)),
+                    ("barrier", self._barrier), ("combine_storing_to_peers", combine), ("barrier_2", self._barrier), ("copy_out", take_output)]
         st = [("split_kernel", lambda: local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ws["ohat"], ws["lse"], check=False))]
         if world == 1:
             st.append(("combine", lambda: combine_gathered(ws["ohat"].view(1, self.rows_total, D), ws["lse"].view(1, self.rows_total), out, 1, check=False)))
@@ -198,4 +356,9 @@ class KvShardedPlan:
         return {name: statistics.median(v) for name, v in acc.items()}
 
     def close(self):
+        import torch
+        torch.cuda.synchronize(self.device)
+        if self.peer is not None:
+            self.peer.close(self.group)
+            self.peer = None
         self.ws = None

@@ -62,9 +62,9 @@ enum fmha_mxfp8_error {
  */
 #define FMHA_MXFP8_FLAG_F32_PARTIALS 0x10u
 /*
- * Launch detail (extension): when the last round of work items fills at most half of the SMs, the kernels cut those items in two key
- * ranges and let pairs of CTAs (a cluster of two) merge the halves through distributed shared memory. This flag keeps every item
- * whole. Results agree to f32 summation order either way.
+ * Launch detail (extension): when the last round of work items fills at most half of the SMs and an item has at least 48 key tiles, the
+ * kernels cut those items in two key ranges and let pairs of CTAs (a cluster of two) merge the halves through distributed shared
+ * memory. This flag keeps every item whole. Results agree to f32 summation order either way.
  */
 #define FMHA_MXFP8_FLAG_NO_TAIL_SPLIT 0x20u
 
@@ -82,7 +82,7 @@ typedef struct fmha_mxfp8_attn_args {
     void* ptr_k;                 /* 0x020 e4m3 K [B,SK,HK,128] */
     uint8_t _pad2[8];
     void* ptr_v;                 /* 0x030 e4m3 V [B,SK,HK,128] */
-    uint8_t _pad3a[8];
+    void* ext_ptr_peer_plan;     /* 0x038 kvsplit only (ignored here): see fmha_mxfp8_peer_plan_build */
     void* ext_ptr_lse;           /* 0x040 optional f32 [B,H,S] natural-log LSE output; NULL = not written */
     void* ext_ptr_v_blockscale;  /* 0x048 optional E8M0 [B,ceil(SK/32),HK,128] V block scales (FMHA_MXFP8_FLAG_V_BLOCKSCALE) */
     uint8_t _pad3b[8];           /* 0x050 the vendor ABI's f32 softmax scale; never read (the scale is folded into Q) */
@@ -149,7 +149,7 @@ typedef struct fmha_mxfp8_kvsplit_args {
     void* ptr_k;
     uint8_t _pad2[8];
     void* ptr_v;
-    uint8_t _pad3a[8];
+    void* ext_ptr_peer_plan;     /* 0x038 optional: a device plan from fmha_mxfp8_peer_plan_build; the partial rows then go to other GPUs */
     void* ext_ptr_lse;           /* unused by kvsplit */
     void* ext_ptr_v_blockscale;
     uint8_t _pad3b[8];
@@ -321,6 +321,35 @@ int fmha_mxfp8_kvsplit_static_scratch(const fmha_mxfp8_problem* prob, uint32_t s
  * ohat and out 16-byte aligned. Returns 0, FMHA_MXFP8_E_ARG, or minus a cudaError_t.
  */
 int fmha_mxfp8_combine_f32(const void* ohat, const void* lse, void* out, uint32_t rows_total, uint32_t splits, void* stream);
+
+/*
+ * Key-range sharding over the GPUs of one node (one process per GPU) without a collective for the partials. None of this has a
+ * counterpart in the reference, which is single-GPU; the algebra is its KV split with "split = GPU"
+ * (crates/amdgpu-stage/src/components.rs:58-74, crates/amdgpu-tile/src/epilogue.rs:117-146).
+ *   peer_alloc / peer_open / peer_close / peer_free: a device buffer other processes of the node can map (CUDA IPC): alloc returns the
+ *       pointer and a 64-byte handle to pass to the peers, which open (and later close) it; the owner frees it after the peers closed.
+ *   peer_plan_build: GPU d of `world` combines the query rows [d * S / world, (d + 1) * S / world) (S / world a multiple of 128, one batch
+ *       element). ohat_recv[d] / lse_recv[d] are GPU d's receive buffers as mapped into this process (this GPU's own for d == rank):
+ *       f32 [world][S / world][H][128] and f32 [world][S / world * H]. Writes FMHA_MXFP8_PEER_PLAN_BYTES to `plan_dev` (device memory,
+ *       128-byte aligned), to be passed as ext_ptr_peer_plan of a kvsplit launch with kvs_splits = 1 and FMHA_MXFP8_FLAG_F32_PARTIALS: that
+ *       launch stores row block x of its partial to slot [rank] of the receive buffers of GPU x * 128 / (S / world) (TMA tile stores and
+ *       plain stores to peer memory; ptr_ohat / ptr_lse are then not written). The ranks must barrier before combining.
+ *   combine_f32_scatter: the f32 combine over `rows` rows of `splits` partials, each bf16 row stored to all `n_outs` output buffers at
+ *       row `row_offset` (the all-gather of the row slices done by the combine's stores). The ranks must barrier before reading.
+ *   copy_async: cudaMemcpyAsync device to device (for hosts that hold raw pointers only).
+ * Return 0, FMHA_MXFP8_E_ARG, or minus a cudaError_t.
+ */
+#define FMHA_MXFP8_PEER_HANDLE_BYTES 64
+#define FMHA_MXFP8_PEER_MAX_GPUS 8
+#define FMHA_MXFP8_PEER_PLAN_BYTES 1152
+int fmha_mxfp8_peer_alloc(size_t bytes, void** dev_ptr, void* handle64);
+int fmha_mxfp8_peer_open(const void* handle64, void** dev_ptr);
+int fmha_mxfp8_peer_close(void* dev_ptr);
+int fmha_mxfp8_peer_free(void* dev_ptr);
+int fmha_mxfp8_peer_plan_build(uint32_t world, uint32_t rank, uint32_t H, uint32_t S, void* const* ohat_recv, void* const* lse_recv, void* plan_dev, void* stream);
+int fmha_mxfp8_combine_f32_scatter(const void* ohat, const void* lse, void* const* outs, uint32_t n_outs, uint64_t row_offset, uint32_t rows, uint32_t splits,
+                                   void* stream);
+int fmha_mxfp8_copy_async(void* dst, const void* src, size_t bytes, void* stream);
 
 /*
  * The quantisers in front of the path: bf16 activations -> the MXFP8 operands the attention kernels take. The reference has no device

@@ -259,7 +259,14 @@ def test_headline_shapes_at_full_size(oracle, shape, path, splits):
     assert np.isfinite(f).all() and np.abs(f).max() <= inp.vdescale * 448.0
     dev.vs[0] = 2.0 * inp.vdescale
     _, out2 = dev.run(path, splits)
-    assert np.array_equal(oracle.bf16_to_f32(out2), 2.0 * f)
+    f2 = oracle.bf16_to_f32(out2)
+    if s == 0:
+        assert np.array_equal(f2, 2.0 * f)
+    else:
+        # the split kernel rounds its partials to f16 (the reference's partial format): a power of two commutes with that rounding except
+        # in f16's subnormal range (|x| < 6.1e-5), so a few elements may land one bf16 step away
+        d = np.abs(f2 - 2.0 * f)
+        assert (d > 0).mean() < 1e-3 and (d <= np.abs(2.0 * f) * 2.0 ** -7 + 1e-30).all(), ((d > 0).mean(), d.max())
 
 
 def test_stress_repeated_split_launches(oracle):

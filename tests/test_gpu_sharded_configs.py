@@ -49,8 +49,10 @@ def _gate_rows(oracle, inp, out, rows, tag):
 
 @pytest.mark.parametrize("shape,path,splits", [((4, 8, 8, 2048, 2048), "auto", None), ((1, 8, 8, 8192, 8192), "kvsplit", 8), ((1, 8, 8, 8192, 8192), "auto", None),
                                                ((2, 4, 4, 1024, 1024), "auto", None), ((1, 8, 8, 2048, 2048), "auto", None), ((1, 2, 2, 1024, 1088), "vs128", None),
-                                               ((2, 8, 4, 700, 640), "vs128", None), ((3, 3, 3, 768, 1280), "t128", None), ((1, 2, 1, 200, 1337), "kvsplit", 2)],
-                         ids=["config2", "config3-split8", "B1H8S8192-auto", "B2H4S1024", "B1H8S2048-kvsplit4", "B1H2S1024SK1088", "B2H8S700-gqa2", "B3H3S768", "B1H2S200SK1337-gqa2"])
+                                               ((2, 8, 4, 700, 640), "vs128", None), ((3, 3, 3, 768, 1280), "t128", None), ((1, 2, 1, 200, 1337), "kvsplit", 2),
+                                               ((1, 2, 2, 300, 6200), "vs128", None), ((1, 4, 2, 1024, 16384), "kvsplit", 2)],
+                         ids=["config2", "config3-split8", "B1H8S8192-auto", "B2H4S1024", "B1H8S2048-kvsplit4", "B1H2S1024SK1088", "B2H8S700-gqa2", "B3H3S768", "B1H2S200SK1337-gqa2",
+                              "B1H2S300SK6200-pairs-ragged", "B1H4S1024SK16384-kvsplit2-pairs"])
 def test_rows_spread_over_every_query_tile(oracle, shape, path, splits):
     from amdgpu_rustdsl_b200 import fmha_fwd_mxfp8
     B, H, HK, S, SK = shape
@@ -62,6 +64,28 @@ def test_rows_spread_over_every_query_tile(oracle, shape, path, splits):
     got = _bf16_bytes(out)
     assert np.isfinite(oracle.bf16_to_f32(got)).all(), "every row of the output must be written"
     _gate_rows(oracle, inp, got, oracle.spread_rows(S), (shape, path, splits))
+
+
+@pytest.mark.parametrize("shape,path,splits", [((1, 8, 8, 8192, 8192), "vs128", None), ((1, 2, 2, 300, 6200), "t128", None), ((1, 4, 2, 1024, 16384), "kvsplit", 2)],
+                         ids=["B1H8S8192", "B1H2S300SK6200-ragged", "B1H4S1024SK16384-kvsplit2"])
+def test_last_round_cut_in_two_agrees_with_whole_items(oracle, shape, path, splits):
+    """Shapes whose last round of work items fills at most half of the SMs (and whose items are long) run that round as halves merged by
+    pairs of CTAs through distributed shared memory. With FMHA_MXFP8_FLAG_NO_TAIL_SPLIT every item stays whole: the two results may
+    differ by f32 summation order only, i.e. within the reference's split-vs-unsplit bound (tests/gpu/ref_host.cpp:603-637)."""
+    from amdgpu_rustdsl_b200 import _abi, fmha_fwd_mxfp8
+    B, H, HK, S, SK = shape
+    inp = oracle.generate("normal", B, H, S, SK, HK)
+    d = _to_dev(inp)
+    res = []
+    for flags in (0, _abi.FLAG_NO_TAIL_SPLIT):
+        out = torch.full((B, S, H, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+        fmha_fwd_mxfp8(d["q"], d["k"], d["v"], d["qs"], d["ks"], d["vs"], out, path=path, splits=splits, flags=flags)
+        torch.cuda.synchronize()
+        res.append(oracle.bf16_to_f32(_bf16_bytes(out)).astype(np.float64))
+    assert np.isfinite(res[0]).all() and np.isfinite(res[1]).all()
+    ulp = 2.0 ** (np.frexp(np.abs(res[1]).max())[1] - 8)
+    diff = np.abs(res[0] - res[1])
+    assert diff.max() <= ulp and diff.mean() <= 1e-4, (diff.max() / ulp, diff.mean())
 
 
 def test_head_sharded_config_at_the_shape_of_one_of_eight_ranks(oracle):
