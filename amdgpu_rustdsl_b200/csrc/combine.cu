@@ -1,7 +1,7 @@
 // fmha_fwd_hd128_mxfp8_v3_kvsplit_combine8h: merges the per-split partials of the KV-split attention into bf16 O.
 //
 // Reference: crates/amdgpu-kernels/src/fmha/io.rs:164-185 (kernel), crates/amdgpu-tile/src/epilogue.rs:89-167 (combine_splits).
-// Each thread owns 8 consecutive output elements of one row and walks the splits once with an online maximum:
+// Each thread owns 8 or 16 consecutive output elements of one row and walks the splits once with an online maximum:
 //   m' = max(m, lse_s); a = 2^(m - m'); w = 2^(lse_s - m'); den = den*a + w; acc_k = acc_k*a + w*Ohat_s[k]; out = acc/den -> bf16.
 // Partials are f16 like the reference's (crates/amdgpu-kernels/src/fmha/io.rs:83-85: half-precision Ohat inside an allocation the
 // contract sizes for f32, tests/gpu/generated/..._kvsplit_abi.h:196): one thread reads 16 bytes per split and writes one 16-byte store.
@@ -40,48 +40,63 @@ __device__ __forceinline__ float2 h2_to_f2(uint32_t h2) {
 
 // kScatter: the bf16 rows go to several output buffers (this GPU's and its peers': the all-gather of the row slices done by the stores).
 // kF32: the partial rows are f32 (512 bytes per row; partials that crossed GPUs), else f16 (256 bytes per row, the reference's format).
+// One thread owns kE consecutive outputs of a row: 8 with f32 partials (two 16-byte loads per split), 16 with f16 partials (also two
+// 16-byte loads per split: the same bytes in flight per thread, which is what keeps HBM busy).
 template <bool kF32, bool kScatter = false>
 __global__ void __launch_bounds__(256)
 kvsplit_combine_kernel(const void* __restrict__ ohat, const float* __restrict__ lse2, uint8_t* __restrict__ out, uint32_t rows_total, uint32_t splits,
                        const OutPointers outs = OutPointers{}) {
-    const uint64_t ngroups = static_cast<uint64_t>(rows_total) * 16u;   // 16 groups of 8 elements per row
+    constexpr int kE = kF32 ? 8 : 16;
+    constexpr uint32_t kGroupsPerRow = 128 / kE;
+    const uint64_t ngroups = static_cast<uint64_t>(rows_total) * kGroupsPerRow;
     for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < ngroups; t += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
-        const uint64_t row = t >> 4;
+        const uint64_t row = t / kGroupsPerRow;
         float m = -1.0e30f, den = 0.0f;
-        float acc[8];
+        float acc[kE];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
+        for (int k = 0; k < kE; ++k) acc[k] = 0.0f;
         for (uint32_t s = 0; s < splits; ++s) {
             const uint64_t prow = static_cast<uint64_t>(s) * rows_total + row;
             const float ls = __ldg(lse2 + prow);
-            float v[8];
+            float v[kE];
             if (kF32) {
-                const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(ohat) + (static_cast<uint64_t>(s) * rows_total * 16u + t) * 8u);
+                const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(ohat) + (static_cast<uint64_t>(s) * ngroups + t) * 8u);
                 const float4 v0 = ld_stream(src), v1 = ld_stream(src + 1);
                 v[0] = v0.x; v[1] = v0.y; v[2] = v0.z; v[3] = v0.w; v[4] = v1.x; v[5] = v1.y; v[6] = v1.z; v[7] = v1.w;
             } else {
-                const uint4 h = ld_stream_u4(reinterpret_cast<const uint4*>(ohat) + (static_cast<uint64_t>(s) * rows_total * 16u + t));
-                const float2 a0 = h2_to_f2(h.x), a1 = h2_to_f2(h.y), a2 = h2_to_f2(h.z), a3 = h2_to_f2(h.w);
-                v[0] = a0.x; v[1] = a0.y; v[2] = a1.x; v[3] = a1.y; v[4] = a2.x; v[5] = a2.y; v[6] = a3.x; v[7] = a3.y;
+                const uint4* src = reinterpret_cast<const uint4*>(ohat) + (static_cast<uint64_t>(s) * ngroups + t) * 2u;
+                const uint4 h0 = ld_stream_u4(src), h1 = ld_stream_u4(src + 1);
+                const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float2 f = h2_to_f2(hw[k]);
+                    v[2 * k] = f.x;
+                    v[2 * k + 1] = f.y;
+                }
             }
             const float mn = fmaxf(m, ls);
             const float a = ex2f(m - mn), w = ex2f(ls - mn);
             den = den * a + w;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] = acc[k] * a + w * v[k];
+            for (int k = 0; k < kE; ++k) acc[k] = acc[k] * a + w * v[k];
             m = mn;
         }
         const float rd = 1.0f / den;
-        uint32_t wv[4];
+        uint32_t wv[kE / 2];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
+        for (int e = 0; e < kE / 2; ++e) {
             const __nv_bfloat162 b2 = __floats2bfloat162_rn(acc[2 * e] * rd, acc[2 * e + 1] * rd);
             wv[e] = *reinterpret_cast<const uint32_t*>(&b2);
         }
-        if (kScatter) {
-            for (uint32_t i = 0; i < outs.n; ++i) *reinterpret_cast<uint4*>(outs.out[i] + t * 16u) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-        } else {
-            *reinterpret_cast<uint4*>(out + t * 16u) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+#pragma unroll
+        for (int h = 0; h < kE / 8; ++h) {
+            const uint4 o4 = make_uint4(wv[4 * h], wv[4 * h + 1], wv[4 * h + 2], wv[4 * h + 3]);
+            const uint64_t off = (t * (kE / 8) + h) * 16u;
+            if (kScatter) {
+                for (uint32_t i = 0; i < outs.n; ++i) *reinterpret_cast<uint4*>(outs.out[i] + off) = o4;
+            } else {
+                *reinterpret_cast<uint4*>(out + off) = o4;
+            }
         }
     }
 }
@@ -99,7 +114,7 @@ cudaError_t launch_combine_scatter(const void* ohat, const float* lse2, const Ou
 }
 
 cudaError_t launch_combine(const void* ohat, bool f32_partials, const float* lse2, uint8_t* out, uint32_t rows_total, uint32_t splits, cudaStream_t stream) {
-    const uint64_t ngroups = static_cast<uint64_t>(rows_total) * 16u;
+    const uint64_t ngroups = static_cast<uint64_t>(rows_total) * (f32_partials ? 16u : 8u);
     uint64_t blocks = (ngroups + 255u) / 256u;
     // cap the grid at a few waves of 148 SMs x 8 resident blocks; the grid-stride loop covers the rest
     const uint64_t cap = 148u * 8u * 4u;

@@ -1,7 +1,7 @@
 // The KV-split path with its partials in a fixed device array instead of a caller-supplied workspace.
 //
-// Who needs this: the split kernel and the combine kernel talk to each other through scratch memory (f32 partial outputs and one
-// base-2 log-sum-exp per row and split). The regular entry points make the caller bring that memory. Some callers have nowhere to
+// Who needs this: the split kernel and the combine kernel talk to each other through scratch memory (partial outputs, f16 rows in an
+// area the contract sizes for f32, and one base-2 log-sum-exp per row and split). The regular entry points make the caller bring that memory. Some callers have nowhere to
 // get it from at the moment of the call: a serving loop whose device memory was handed out in full to its own pools at start-up, a
 // callback or a thread that must not enter the CUDA allocator because cudaMalloc / cudaFree synchronise the whole device and take
 // driver locks, a host runtime that plans all its buffers ahead of time and learns the split count only at dispatch. For them the
@@ -10,8 +10,11 @@
 //
 // Limits and rules, all consequences of the array being one fixed object per device:
 //   * size: splits * B * S * H  <=  kMaxRowSplits. Larger problems are refused before anything is launched.
-//   * the first call on a device looks the array's address up (cudaGetSymbolAddress, which may load the module). Make that call
-//     during start-up, outside any stream capture; later calls on that device only read the cached address.
+//   * the first call on a device looks the array's address up (cudaGetSymbolAddress, which may load the module), and the first launch of
+//     each kernel variant on a device sets that kernel's shared-memory attribute and may load its code. Which variant a call uses
+//     depends on the problem: fewer than 512 keys or not (the two softmax recipes), and whether a trace buffer is attached. So make one
+//     call of each kind you will use during start-up, outside any stream capture. After that a call only looks up two symbol addresses
+//     (this array's is cached; the status word's is asked for by every launch), encodes four tensor maps on the host and launches.
 //   * every call on a device uses the same bytes. Two calls that can overlap in time (different streams, or different host threads
 //     on streams that are not ordered against each other) race on the partials and both get garbage. Order them.
 //   * nothing in the array has to start at zero or survive between calls: each call's split kernel writes every (split, row)

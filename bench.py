@@ -569,9 +569,10 @@ def run_sharded(R, wl):
     clocks = sampler.stop() if sampler else None
     ms = statistics.median(win) / per_window
     res = {"workload": f"{wl}: B{B} H{H} HK{HK} Sq{S} Skv{SK}", "per_rank": f"H{Hl} HK{HKl} Skv{SKl}", "value": flops(B, H, S, SK) / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-           "ms_per_step": ms, "per_window": per_window, "windows_ms": win, "scaling": "strong",
+           "ms_per_step": ms, "per_window": per_window, "windows_ms": win, "scaling": W["scaling"],
            "roofline_frac_per_gpu": flops(B, Hl, S, SKl) / (ms * 1e-3) / 1e12 / R.peak,
-           "clocks": clocks, "parallelism": ("heads dealt out over the ranks, no collective" if wl == "c4" else W["plan"].describe())}
+           "clocks": clocks, "parallelism": ("heads dealt out over the ranks, no collective" if wl == "c4" else W["plan"].describe() if wl == "c5"
+                                             else f"one GPU: {W['ran'][0]} with {W['ran'][1]} splits (f16 partials) + combine")}
     if wl == "c5":
         stages = W["plan"].timed_stages(s["q"], s["k"], s["v"], s["qs"], s["ks"], s["vs"], s["out"], reps=5)
         res["stages_ms"] = {k: R.max_over_ranks(v) for k, v in stages.items()}
@@ -621,6 +622,12 @@ def main():
             except Exception as e:   # a failure here must not take the headline with it, and every rank has to reach the next collective
                 sharded[w] = {"error": f"{type(e).__name__}: {e}"}
                 R.torch.cuda.synchronize()
+    if wl == "c2" and not args.no_sharded and R.world == 1:
+        # the forced 8-way key split of B1 H8 S8192 on one GPU (split kernel + combine in one window), beside the headline
+        try:
+            sharded["c3"] = run_sharded(R, "c3")
+        except Exception as e:
+            sharded["c3"] = {"error": f"{type(e).__name__}: {e}"}
     status = device_status()
 
     if R.rank != 0:

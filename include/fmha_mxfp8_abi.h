@@ -304,7 +304,8 @@ int fmha_mxfp8_auto(const fmha_mxfp8_problem* prob, int path, uint32_t splits, v
  * synchronises the device. The call allocates nothing and calls no allocating routine.
  *   - Limit: splits * B * S * H <= FMHA_MXFP8_STATIC_SCRATCH_MAX_ROW_SPLITS (32 MiB of partials + 256 KiB of log-sum-exps per
  *     device); beyond it the call returns FMHA_MXFP8_E_EXTENT with a message and launches nothing.
- *   - The first call on a device resolves the array's address (cudaGetSymbolAddress; may load the module): make it at start-up,
+ *   - The first call on a device resolves the array's address (cudaGetSymbolAddress; may load the module), and the first launch of a
+ *     kernel variant on a device sets its shared-memory attribute: make one call per recipe you will use (SK < 512 or not) at start-up,
  *     before any stream capture.
  *   - All calls on a device share the one array: calls that may overlap in time race on it and must be ordered by the caller.
  *   - Nothing in the array needs clearing: every partial the combine reads is written by the split kernel of the same call.

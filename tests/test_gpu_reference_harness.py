@@ -64,12 +64,12 @@ def test_harness_scores_the_dispatched_path_on_normal_data(oracle, shape):
                                        ((1, 8, 2048, 2048, 1), {"REF_SPLIT": "2", "REF_SPLIT_FORCE": "1"}), ((1, 2, 200, 1337, 2), {"REF_ROWS_PER_BLOCK": "256", "REF_NO_AUTO_SPLIT": "1"})],
                          ids=["split8-forced", "t128-forced", "split2-forced", "vs128-forced"])
 def test_harness_forced_paths_and_palette_data(shape, env):
-    """ACC64-style forced paths through the harness's own knobs, on its default (palette) data: the dispatched slot may not count more
-    bad elements than the 256-row slot plus the allowance the palette data needs (see test_gpu_parity._bad_allowance), and the
-    mean errors of the two slots agree to 10 %."""
+    """ACC64-style forced paths through the harness's own knobs, on its default (palette) data: the forced slot may not count more bad
+    elements than the 256-row slot (both are this library's kernels here, so no allowance), and the mean errors of the two slots agree
+    to 10 %."""
     r, st = run_harness(shape, "lcg", 64, env)
     assert st["our"]["checked"] == st["vendor"]["checked"]
-    assert st["our"]["bad"] <= st["vendor"]["bad"] + -(-st["our"]["checked"] * 5 // 10000), st
+    assert st["our"]["bad"] <= st["vendor"]["bad"], st
     assert st["our"]["mean"] <= 1.10 * st["vendor"]["mean"], st
     if "REF_SPLIT" in env:
         # the harness's split-vs-unsplit gate (ref_host.cpp:603-637: worst element within 1 bf16 ULP of max|O|, mean difference 1e-4).

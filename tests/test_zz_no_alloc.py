@@ -49,9 +49,13 @@ def test_static_scratch_entry_matches_the_workspace_entry_twice(oracle, abi, sha
     for call in range(2):
         got_t = torch.full((B, S, H, 128), float("nan"), dtype=torch.bfloat16, device=dev)
         pr2 = _problem(abi, inp, q, k, v, qs, ks, vs, got_t)
+        torch.cuda.synchronize()
+        free_before, used_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
         rc = lib.fmha_mxfp8_kvsplit_static_scratch(C.byref(pr2), splits, None, err, 256)
         assert rc == 0, (call, err.value)
         torch.cuda.synchronize()
+        if call == 1:   # the warmed-up call takes no device memory from the driver or from torch
+            assert torch.cuda.mem_get_info()[0] == free_before and torch.cuda.memory_allocated() == used_before
         assert np.array_equal(_bytes(got_t), want), f"call {call} differs from the workspace entry"
 
     from amdgpu_rustdsl_b200 import device_status
