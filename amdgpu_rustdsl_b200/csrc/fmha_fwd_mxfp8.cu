@@ -169,12 +169,6 @@ __device__ __forceinline__ uint32_t fast_p_bits(uint32_t s, float c) {
     asm("fma.rn.sat.f32 %0, %1, 0f3D000000, %2;" : "=f"(t) : "f"(__uint_as_float(s)), "f"(c));   // s / 32 + c
     return __float_as_uint(t + 32768.0f);
 }
-// One P word of the long-sequence conversion: keys 0 and 1 from the exp2 unit, keys 2 and 3 from the FMA pipe.
-__device__ __forceinline__ uint32_t p_word_hybrid(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t s3, float sh, float c) {
-    const uint32_t lo = cvt_e4m3x2(ex2_approx(__uint_as_float(s0) + sh), ex2_approx(__uint_as_float(s1) + sh));
-    const uint32_t hi = __byte_perm(fast_p_bits(s2, c), fast_p_bits(s3, c), 0x0040);
-    return __byte_perm(lo, hi, 0x5410);
-}
 __device__ __forceinline__ void st_shared_v2(uint32_t addr, uint32_t a, uint32_t b) {
     asm volatile("st.volatile.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
@@ -848,12 +842,25 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 const float cf = (kPOffset + 7.0f - kFastBias - ref) * 0.03125f;
                 uint32_t pw[kCols / 4];
                 if (lazy) {
+                    // Software pipeline over the 32 words, in place in the score registers: word c's exp2 (two values) and bit-built values
+                    // (two) are started kConvDepth words before they are converted and packed, so that a thread always has that many
+                    // independent chains in flight without holding more than the score row itself (+2 % on the headline shape over one word
+                    // at a time; depths 4, 16 and 32 and scheduling points between the words were slower).
+                    constexpr int kConvDepth = 8;
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        // a scheduling point every eight words: without them the converting warp keeps its scheduler for long stretches
-                        // and the service warp that shares it falls behind (2-3 %)
-                        if (c % 8 == 4) __syncwarp();
-                        pw[c] = p_word_hybrid(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3], sh, cf);
+                    for (int c = 0; c < 32 + kConvDepth; ++c) {
+                        if (c < 32) {
+                            v[4 * c] = __float_as_uint(ex2_approx(__uint_as_float(v[4 * c]) + sh));
+                            v[4 * c + 1] = __float_as_uint(ex2_approx(__uint_as_float(v[4 * c + 1]) + sh));
+                            v[4 * c + 2] = fast_p_bits(v[4 * c + 2], cf);
+                            v[4 * c + 3] = fast_p_bits(v[4 * c + 3], cf);
+                        }
+                        if (c >= kConvDepth) {
+                            const int d = c - kConvDepth;
+                            const uint32_t lo = cvt_e4m3x2(__uint_as_float(v[4 * d]), __uint_as_float(v[4 * d + 1]));
+                            const uint32_t hi = __byte_perm(v[4 * d + 2], v[4 * d + 3], 0x0040);
+                            pw[d] = __byte_perm(lo, hi, 0x5410);
+                        }
                     }
                 } else {
 #pragma unroll
