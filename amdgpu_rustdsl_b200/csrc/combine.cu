@@ -21,12 +21,6 @@ __device__ __forceinline__ float ex2f(float x) {
     return y;
 }
 
-__device__ __forceinline__ float4 ld_stream(const float4* p) {
-    float4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-    return v;
-}
-
 __device__ __forceinline__ uint4 ld_stream_u4(const uint4* p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
@@ -55,31 +49,41 @@ kvsplit_combine_kernel(const void* __restrict__ ohat, const float* __restrict__ 
         float acc[kE];
 #pragma unroll
         for (int k = 0; k < kE; ++k) acc[k] = 0.0f;
-        for (uint32_t s = 0; s < splits; ++s) {
-            const uint64_t prow = static_cast<uint64_t>(s) * rows_total + row;
-            const float ls = __ldg(lse2 + prow);
-            float v[kE];
-            if (kF32) {
-                const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(ohat) + (static_cast<uint64_t>(s) * ngroups + t) * 8u);
-                const float4 v0 = ld_stream(src), v1 = ld_stream(src + 1);
-                v[0] = v0.x; v[1] = v0.y; v[2] = v0.z; v[3] = v0.w; v[4] = v1.x; v[5] = v1.y; v[6] = v1.z; v[7] = v1.w;
-            } else {
+        // four splits at a time: all their loads are issued before the first is used (the kernel lives on bytes in flight)
+        for (uint32_t s0 = 0; s0 < splits; s0 += 4u) {
+            uint4 raw[4][2];
+            float ls[4];
+#pragma unroll
+            for (uint32_t i = 0; i < 4u; ++i) {
+                const uint32_t s = s0 + i < splits ? s0 + i : splits - 1u;   // a short last batch re-reads the last split (and skips it below)
+                ls[i] = __ldg(lse2 + static_cast<uint64_t>(s) * rows_total + row);
                 const uint4* src = reinterpret_cast<const uint4*>(ohat) + (static_cast<uint64_t>(s) * ngroups + t) * 2u;
-                const uint4 h0 = ld_stream_u4(src), h1 = ld_stream_u4(src + 1);
-                const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const float2 f = h2_to_f2(hw[k]);
-                    v[2 * k] = f.x;
-                    v[2 * k + 1] = f.y;
-                }
+                raw[i][0] = ld_stream_u4(src);
+                raw[i][1] = ld_stream_u4(src + 1);
             }
-            const float mn = fmaxf(m, ls);
-            const float a = ex2f(m - mn), w = ex2f(ls - mn);
-            den = den * a + w;
 #pragma unroll
-            for (int k = 0; k < kE; ++k) acc[k] = acc[k] * a + w * v[k];
-            m = mn;
+            for (uint32_t i = 0; i < 4u; ++i) {
+                if (s0 + i >= splits) break;
+                float v[kE];
+                const uint32_t hw[8] = {raw[i][0].x, raw[i][0].y, raw[i][0].z, raw[i][0].w, raw[i][1].x, raw[i][1].y, raw[i][1].z, raw[i][1].w};
+                if constexpr (kF32) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) v[k] = __uint_as_float(hw[k]);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const float2 f = h2_to_f2(hw[k]);
+                        v[2 * k] = f.x;
+                        v[2 * k + 1] = f.y;
+                    }
+                }
+                const float mn = fmaxf(m, ls[i]);
+                const float a = ex2f(m - mn), w = ex2f(ls[i] - mn);
+                den = den * a + w;
+#pragma unroll
+                for (int k = 0; k < kE; ++k) acc[k] = acc[k] * a + w * v[k];
+                m = mn;
+            }
         }
         const float rd = 1.0f / den;
         uint32_t wv[kE / 2];
