@@ -18,6 +18,7 @@ FLAG_EXACT_REBASE = 0x2
 FLAG_CAUSAL = 0x8
 FLAG_F32_PARTIALS = 0x10
 FLAG_NO_TAIL_SPLIT = 0x20
+FLAG_FUSED_COMBINE = 0x40
 TRACE_BYTES = 4 * (16384 + 16384 + 256 + 4096 + 2048)
 PEER_HANDLE_BYTES, PEER_MAX_GPUS, PEER_PLAN_BYTES = 64, 8, 1152
 STATIC_SCRATCH_MAX_ROW_SPLITS = 65536   # FMHA_MXFP8_STATIC_SCRATCH_MAX_ROW_SPLITS
@@ -52,6 +53,9 @@ class KvSplitArgs(C.Structure):
     """kvsplit kernel arguments (648 bytes)."""
     _pack_ = 1
     _fields_ = _COMMON + [_pad(12, 26), ("ptr_ohat", C.c_void_p), ("ptr_lse", C.c_void_p), ("kvs_splits", C.c_uint32), ("kvs_rows_total", C.c_uint32)]
+
+    # offset 0x040 is `ext_ptr_fused_counters` in this block (the unsplit kernels' `ext_ptr_lse`)
+    ext_ptr_fused_counters = property(lambda self: self.ext_ptr_lse, lambda self, v: setattr(self, "ext_ptr_lse", v))
 
 
 class CombineArgs(C.Structure):

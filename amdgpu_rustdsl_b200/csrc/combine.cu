@@ -15,21 +15,10 @@ namespace b200mx {
 
 namespace {
 
-__device__ __forceinline__ float ex2f(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
 __device__ __forceinline__ uint4 ld_stream_u4(const uint4* p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
-}
-__device__ __forceinline__ float2 h2_to_f2(uint32_t h2) {
-    float2 f;
-    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.f32.f16 %0, lo;\n\tcvt.f32.f16 %1, hi;\n\t}" : "=f"(f.x), "=f"(f.y) : "r"(h2));
-    return f;
 }
 
 // kScatter: the bf16 rows go to several output buffers (this GPU's and its peers': the all-gather of the row slices done by the stores).
@@ -72,24 +61,22 @@ kvsplit_combine_kernel(const void* __restrict__ ohat, const float* __restrict__ 
                 } else {
 #pragma unroll
                     for (int k = 0; k < 8; ++k) {
-                        const float2 f = h2_to_f2(hw[k]);
+                        const float2 f = combine_h2_to_f2(hw[k]);
                         v[2 * k] = f.x;
                         v[2 * k + 1] = f.y;
                     }
                 }
-                const float mn = fmaxf(m, ls[i]);
-                const float a = ex2f(m - mn), w = ex2f(ls[i] - mn);
-                den = den * a + w;
+                float a, w;
+                combine_weights(m, den, ls[i], a, w);
 #pragma unroll
-                for (int k = 0; k < kE; ++k) acc[k] = acc[k] * a + w * v[k];
-                m = mn;
+                for (int k = 0; k < kE; ++k) acc[k] = combine_accumulate(acc[k], a, w, v[k]);
             }
         }
         const float rd = 1.0f / den;
         uint32_t wv[kE / 2];
 #pragma unroll
         for (int e = 0; e < kE / 2; ++e) {
-            const __nv_bfloat162 b2 = __floats2bfloat162_rn(acc[2 * e] * rd, acc[2 * e + 1] * rd);
+            const __nv_bfloat162 b2 = __floats2bfloat162_rn(__fmul_rn(acc[2 * e], rd), __fmul_rn(acc[2 * e + 1], rd));
             wv[e] = *reinterpret_cast<const uint32_t*>(&b2);
         }
 #pragma unroll

@@ -69,8 +69,11 @@ constexpr int kThreads = 32 * (4 + 8 + 4);   // 4 service warps, 8 softmax warps
 #endif
 constexpr int kMaxRegs = 128;
 constexpr int kServiceRegs = MXA_SERVICE_REGS, kSoftmaxRegs = MXA_SOFTMAX_REGS, kEpilogueRegs = MXA_EPILOGUE_REGS;
-static_assert(4 * kServiceRegs + 8 * kSoftmaxRegs + 4 * kEpilogueRegs <= 16 * kMaxRegs && kServiceRegs % 8 == 0 && kSoftmaxRegs % 8 == 0 && kEpilogueRegs % 8 == 0,
-              "register file split");
+// setmaxnreg.inc waits, without a bound, until the CTA's own pool has the registers, and the pool is what the CTA got at launch
+// (kThreads x kMaxRegs), not the SM's register file: the roles together must never ask for more than that.
+static_assert(kThreads * kMaxRegs <= 65536, "the CTA must fit the register file at launch");
+static_assert(4 * kServiceRegs + 8 * kSoftmaxRegs + 4 * kEpilogueRegs <= (kThreads / 32) * kMaxRegs, "the roles' registers come out of the CTA's launch allocation");
+static_assert(kServiceRegs % 8 == 0 && kSoftmaxRegs % 8 == 0 && kEpilogueRegs % 8 == 0 && kServiceRegs >= 24 && kEpilogueRegs >= 24 && kSoftmaxRegs <= 256, "register file split");
 constexpr uint32_t kTileBytes = 128 * 128;   // one e4m3 tile
 constexpr uint32_t kSfBytes = 512;           // 128 rows x 4 scale bytes
 
@@ -115,13 +118,15 @@ struct SmemLayout {
     // behind the wait for this parity's previous P V: with one-tile items a softmax group is otherwise two items ahead of the epilogue
     static constexpr uint32_t xfin = xref + 4 * 128 * 8;
     static constexpr uint32_t xstat = xfin + 4 * 128 * 4;         // [row 128] x {row sum, reference} of the partner's half item (launches as pairs)
-    static constexpr uint32_t bars = xstat + 128 * 8;
+    static constexpr uint32_t xlse = xstat + 128 * 8;             // fused merge: [row 128][split 8] log-sum-exps of the block being merged
+    static constexpr uint32_t bars = xlse + 128 * 8 * 4;
     // barriers (8 bytes each): q_full[2], q_empty[2], k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], s_free[2],
-    // p_full[2], o_done[2], o_free, o_full, ref_ready[4], peer_rdy, peer_data
+    // p_full[2], o_done[2], o_free, o_full, four unused, peer_rdy, peer_data
     static constexpr uint32_t n_bars = 4 + 4 * kStages + 16;
     static constexpr uint32_t tmem_slot = bars + 8 * n_bars;
     static constexpr uint32_t abort_flag = tmem_slot + 4;
-    static constexpr uint32_t total = abort_flag + 4;
+    static constexpr uint32_t last_flag = abort_flag + 4;   // fused merge: "this CTA brought the row block's arrival count to `splits`"
+    static constexpr uint32_t total = last_flag + 4;
 };
 constexpr uint32_t kSmemBytes = SmemLayout::total + 1024;   // + slack to align the base to 1024
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget of one CTA");
@@ -270,7 +275,8 @@ __device__ __forceinline__ Item decode_item(uint32_t w, const AttnParams& p) {
 // epilogue of the item before has read O out (o_free).
 // kTrace = false compiles every diagnostic (tile dumps, time stamps) out of the tile loop: the production launches use that variant.
 // kLazy: the long-sequence softmax recipe. kCausal: the causal mask (never with kSplit).
-template <bool kSplit, bool kTrace, bool kLazy, bool kCausal, bool kPair, bool kVbs>
+// kFused: the split kernel with the merge of the partials built into its epilogue (no pairs, no diagnostics, f16 partials, no peer routing).
+template <bool kSplit, bool kTrace, bool kLazy, bool kCausal, bool kPair, bool kVbs, bool kFused = false>
 __global__ void __maxnreg__(kMaxRegs)
 mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const AttnParams p) {
@@ -301,7 +307,6 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     // pairs: "this CTA's exchange area is free" (one arrival, from the partner with the first half) and "the partner's half item has
     // landed in this CTA's exchange area" (128 arrivals, from the partner with the second half)
     const uint32_t bar_peer_rdy = bar0 + 8u * (18 + 4 * kStages), bar_peer_data = bar0 + 8u * (19 + 4 * kStages);
-    auto bar_ref_ready = [&](uint32_t g) { return bar0 + 8u * (14 + 4 * kStages + (g & 3u)); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + SmemLayout::tmem_slot);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + SmemLayout::abort_flag);
 
@@ -335,7 +340,6 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         mbar_init(bar_o_free, kRows);   // the epilogue warpgroup's 128 threads
         mbar_init(bar_o_full, 1);
-        for (uint32_t i = 0; i < 4; ++i) mbar_init(bar_ref_ready(i), kRows);
         mbar_init(bar_peer_rdy, 1);
         mbar_init(bar_peer_data, kRows);
         fence_mbar_init();
@@ -794,24 +798,13 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 // read, and the new reference is published before the rescale factor is worked out.
                 const float cand = lazy ? ceilf(mt) : mt;   // where the reference goes if it moves
                 const float mt_thr = mt - thr;
-                // (tile g - 1's 128 threads have all published: a parked wait on their barrier, then the row's own slot)
-#ifdef MXA_REF_MBAR
-                if (j > 0) {
-                    if (!mbar_wait(bar_ref_ready(g - 1u), ((g - 1u) >> 2) & 1u, abort_flag)) ok = false;
-                    ref = __uint_as_float(ld_shared_v2(ref_slot(g - 1u)).x);
-                }
-#else
                 if (ok && j > 0 && !wait_slot(ref_slot(g - 1u), g - 1u, ref)) ok = false;
-#endif
                 // the reference moves when this tile's maximum passes it by more than the threshold (negative for short sequences: it then
                 // also follows the tile maximum down, and f > 1 scales O and L up)
                 const bool move = mt_thr > ref;
                 const float old_ref = ref;
                 ref = move ? cand : ref;
                 st_shared_v2(ref_slot(g), __float_as_uint(ref), g);
-#ifdef MXA_REF_MBAR
-                mbar_arrive(bar_ref_ready(g));
-#endif
                 f = move ? ex2_approx(old_ref - ref) : 1.0f;   // 0 on the first tile (old reference -inf); an exact power of two for integer references
                 stamp(st_trace, par, static_cast<int>(g), 4);
                 // P V of this parity's previous tile must be done before its P columns are overwritten (and, observed in order, this keeps
@@ -977,7 +970,7 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 p.trace[32768 + r] = l;
                 p.trace[32768 + 128 + r] = ref_out;
             }
-            const bool half_out = !kSplit || (p.flags & kFlagF32Partials) == 0u;   // 16-bit rows (bf16 output, f16 partial) or f32 partial rows
+            const bool half_out = !kSplit || kFused || (p.flags & kFlagF32Partials) == 0u;   // 16-bit rows (bf16 output, f16 partial) or f32 partial rows
             if (half_out) {
                 // bf16 output, or the split kernel's f16 partial (the reference's partial format, block3.rs:291-356): four 32-column
                 // chunks, all staged before the stores go out; O is free after the last read
@@ -1093,7 +1086,7 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             if (row < p.S && want_fin) {   // rows past the sequence are computed on clamped scales and not stored (block3.rs:194)
                 const float lse2 = ref_out - kPOffset + lg2_approx(l);   // log2 of sum_j 2^(s_j)
-                if (kSplit && p.peer != nullptr) {
+                if (kSplit && !kFused && p.peer != nullptr) {
                     const uint32_t dest = it.row0 / p.peer->dest_rows, n_rows = p.peer->dest_rows * p.H;
                     p.peer->lse[dest][static_cast<size_t>(p.peer->rank) * n_rows + static_cast<size_t>(row - dest * p.peer->dest_rows) * p.H + it.head] = lse2;
                 } else if (kSplit) {
@@ -1101,6 +1094,103 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     p.lse2[prow] = lse2;
                 } else if (p.lse_nat != nullptr) {
                     p.lse_nat[(static_cast<size_t>(it.batch) * p.H + it.head) * p.S + row] = lse2 * 0.6931471805599453f;
+                }
+            }
+            if (kFused) {
+                // Fused merge (the reference's last-arriver combine, tests/gpu/ref_host.cpp:489-497, docs/last-arriver-memory-model.md): every
+                // CTA that has stored a partial of this 128-row block counts itself in; the one that completes the count merges the block's
+                // `splits` partials into the bf16 output, so no combine kernel follows.
+                // Writer side: the bulk stores of the partial are performed, every thread's log-sum-exp store is fenced, then one
+                // device-scope atomic publishes both. Reader side: the atomic, a fence, copies and loads that bypass L1.
+                volatile uint32_t* last_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + SmemLayout::last_flag);
+                if (issuer) bulk_wait_group_done0();
+                __threadfence();
+                named_bar_sync(kEpiBar, 128u);
+                if (issuer) {
+                    uint32_t* cnt = p.fused_counters + (static_cast<size_t>(it.batch) * p.H + it.head) * p.n_qtiles + it.row0 / kRows;
+                    __threadfence();
+                    const uint32_t old = atomicAdd(cnt, 1u);
+                    const bool last = old + 1u == p.splits;
+                    if (last) *cnt = 0u;   // nobody else touches the counter any more in this launch: the next launch finds it zero
+                    *last_flag = last ? 1u : 0u;
+                }
+                named_bar_sync(kEpiBar, 128u);
+                if (*last_flag != 0u) {
+                    __threadfence();
+                    // The block's partial rows (256 bytes each, `splits` per output row) come in through the two staging tiles with
+                    // asynchronous 16-byte copies (cp.async: no registers are tied up by loads in flight, which this warpgroup does not
+                    // have), 64 rows of 256 bytes per batch (= 64 / splits output rows), two batches in flight. Piece i of a batch = the
+                    // partial of split i % splits for output row i / splits, at byte 256 i of the tile; a warp's copy instruction moves two
+                    // whole pieces. For the merge a warp shares an output row, 4 columns per lane.
+                    const uint32_t rows_pb = 64u >> p.split_log2;
+                    const uint32_t rows_valid = min(static_cast<uint32_t>(kRows), p.S - it.row0);
+                    const uint32_t n_batches = (rows_valid + rows_pb - 1u) / rows_pb;
+                    const size_t head_row0 = (static_cast<size_t>(it.batch) * p.S + it.row0) * p.H + it.head;   // partial row index of the block's first row
+                    const uint8_t* part = static_cast<const uint8_t*>(p.ohat);
+                    const uint32_t et = threadIdx.x - 32u * kFirstEpilogueWarp;   // 0 .. 127
+                    auto issue = [&](uint32_t b) {   // always closes one copy group, also an empty one: two groups are in flight at any time
+                        if (b < n_batches) {
+                            const uint32_t first = b * rows_pb, pieces = min(rows_pb, rows_valid - first) << p.split_log2;
+                            const uint32_t dst = stg + (b & 1u) * 16384u;
+#pragma unroll
+                            for (uint32_t i = 0; i < 8u; ++i) {
+                                const uint32_t c = i * 128u + et, pc = c >> 4, ch = c & 15u;
+                                if (pc < pieces) {
+                                    const uint32_t row = first + (pc >> p.split_log2), sp = pc & (p.splits - 1u);
+                                    const uint8_t* src = part + (static_cast<size_t>(sp) * p.rows_total + head_row0 + static_cast<size_t>(row) * p.H) * 256u + ch * 16u;
+                                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + c * 16u), "l"(src) : "memory");
+                                }
+                            }
+                        }
+                        asm volatile("cp.async.commit_group;" ::: "memory");
+                    };
+                    issue(0u);
+                    issue(1u);
+                    // while the first batches fly: the block's log-sum-exps, thread r those of row r (all loads in flight at once), to shared memory
+                    {
+                        float lsv[8];
+                        const size_t g = head_row0 + static_cast<size_t>(min(r, rows_valid - 1u)) * p.H;
+#pragma unroll
+                        for (uint32_t sp = 0; sp < 8u; ++sp) lsv[sp] = sp < p.splits ? __ldcg(p.lse2 + static_cast<size_t>(sp) * p.rows_total + g) : 0.0f;
+                        float4* dst4 = reinterpret_cast<float4*>(smem_gen + SmemLayout::xlse + r * 32u);
+                        dst4[0] = make_float4(lsv[0], lsv[1], lsv[2], lsv[3]);
+                        dst4[1] = make_float4(lsv[4], lsv[5], lsv[6], lsv[7]);
+                    }
+                    const uint32_t tr = static_cast<uint32_t>(warp) & 3u, tc = static_cast<uint32_t>(lane);   // row within a group of 4, 8-byte column chunk
+                    for (uint32_t b = 0; b < n_batches; ++b) {
+                        const uint32_t first = b * rows_pb, rows_here = min(rows_pb, rows_valid - first);
+                        asm volatile("cp.async.wait_group 1;" ::: "memory");   // this thread's copies of batch b have landed
+                        named_bar_sync(kEpiBar, 128u);                          // everybody's have (and, the first time, the log-sum-exps are in place)
+                        for (uint32_t rg = 0; rg < rows_here; rg += 4u) {
+                            const uint32_t rb = rg + tr;   // row within the batch
+                            if (rb < rows_here) {
+                                const volatile float* ls_row = reinterpret_cast<const volatile float*>(smem_gen + SmemLayout::xlse + (first + rb) * 32u);
+                                float m = -1.0e30f, den = 0.0f, acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                                const uint32_t src = stg + (b & 1u) * 16384u + ((rb << p.split_log2) << 8) + tc * 8u;
+                                for (uint32_t sp = 0; sp < p.splits; ++sp) {
+                                    const float ls = ls_row[sp];
+                                    uint2 raw;
+                                    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(raw.x), "=r"(raw.y) : "r"(src + sp * 256u) : "memory");
+                                    float a, w;
+                                    combine_weights(m, den, ls, a, w);
+                                    const float2 f01 = combine_h2_to_f2(raw.x), f23 = combine_h2_to_f2(raw.y);
+                                    acc[0] = combine_accumulate(acc[0], a, w, f01.x);
+                                    acc[1] = combine_accumulate(acc[1], a, w, f01.y);
+                                    acc[2] = combine_accumulate(acc[2], a, w, f23.x);
+                                    acc[3] = combine_accumulate(acc[3], a, w, f23.y);
+                                }
+                                const float rd = 1.0f / den;
+                                const __nv_bfloat162 b01 = __floats2bfloat162_rn(__fmul_rn(acc[0], rd), __fmul_rn(acc[1], rd));
+                                const __nv_bfloat162 b23 = __floats2bfloat162_rn(__fmul_rn(acc[2], rd), __fmul_rn(acc[3], rd));
+                                uint8_t* dst = p.o + static_cast<size_t>(it.batch) * p.o_batch_stride + static_cast<size_t>(it.row0 + first + rb) * p.o_row_stride +
+                                               static_cast<size_t>(it.head) * 256u + tc * 8u;
+                                *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&b01), *reinterpret_cast<const uint32_t*>(&b23));
+                            }
+                        }
+                        named_bar_sync(kEpiBar, 128u);   // everybody has read this tile out
+                        issue(b + 2u);
+                    }
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");   // (only empty groups are left)
                 }
             }
             stamp(ep_trace, 3, 24 + static_cast<int>(n), 7);
@@ -1130,9 +1220,9 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
     using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
     // The instantiations: [causal][recipe][trace][split] (the causal mask has no split form); behind them the variants for launches as pairs
     // of CTAs (long-sequence recipe, no mask): [trace][split]; behind those the variants with V block scales (no mask, no trace):
-    // [pair][recipe][split], pairs only with the long-sequence recipe.
+    // [pair][recipe][split], pairs only with the long-sequence recipe; last the split kernels with the fused merge: [V block scales][recipe].
 #define MXA_K(split, trace, lazy, causal, pair, vbs) mxfp8_prefill_kernel<split, trace, lazy, causal, pair, vbs>
-    static const Kernel kernels[28] = {
+    static const Kernel kernels[32] = {
         MXA_K(false, false, false, false, false, false), MXA_K(true, false, false, false, false, false), MXA_K(false, true, false, false, false, false),
         MXA_K(true, true, false, false, false, false),   MXA_K(false, false, true, false, false, false), MXA_K(true, false, true, false, false, false),
         MXA_K(false, true, true, false, false, false),   MXA_K(true, true, true, false, false, false),   MXA_K(false, false, false, true, false, false),
@@ -1143,9 +1233,11 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
         MXA_K(true, true, true, false, true, false),
         MXA_K(false, false, false, false, false, true),  MXA_K(true, false, false, false, false, true),  MXA_K(false, false, true, false, false, true),
         MXA_K(true, false, true, false, false, true),    nullptr,                                        nullptr,
-        MXA_K(false, false, true, false, true, true),    MXA_K(true, false, true, false, true, true)};
+        MXA_K(false, false, true, false, true, true),    MXA_K(true, false, true, false, true, true),
+        mxfp8_prefill_kernel<true, false, false, false, false, false, true>, mxfp8_prefill_kernel<true, false, true, false, false, false, true>,
+        mxfp8_prefill_kernel<true, false, false, false, false, true, true>,  mxfp8_prefill_kernel<true, false, true, false, false, true, true>};
 #undef MXA_K
-    constexpr int kKernels = 28;
+    constexpr int kKernels = 32;
     constexpr int kMaxDevices = 64;
     // per-device set-up done lazily from whichever thread launches first: plain flags would be a data race, and both steps are idempotent
     static std::atomic<bool> attr_done[kMaxDevices][kKernels];   // the shared-memory attribute is per device
@@ -1163,6 +1255,9 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
     const bool vbs = p.v_blockscale != nullptr;
     if (vbs && (causal || p.trace != nullptr)) return cudaErrorInvalidValue;   // V block scales: no mask, no diagnostics
     int which = vbs ? 20 + (split ? 1 : 0) + (lazy_recipe ? 2 : 0) : (split ? 1 : 0) + (p.trace != nullptr ? 2 : 0) + (lazy_recipe ? 4 : 0) + (causal ? 8 : 0);
+    const bool fused = p.fused_counters != nullptr;
+    if (fused && (!split || p.trace != nullptr || p.peer != nullptr || (p.flags & kFlagF32Partials) || p.splits > 8u || p.o == nullptr)) return cudaErrorInvalidValue;
+    if (fused) which = 28 + (lazy_recipe ? 1 : 0) + (vbs ? 2 : 0);
     const int which_pair = vbs ? 26 + (split ? 1 : 0) : 16 + (split ? 1 : 0) + (p.trace != nullptr ? 2 : 0);   // only for the long-sequence recipe without a mask
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -1208,7 +1303,7 @@ cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, c
     }
     const uint32_t even_sms = static_cast<uint32_t>(sms) & ~1u;
     constexpr uint32_t kMinTilesForPairs = 48u;
-    if (lazy_recipe && !causal && min_tiles >= kMinTilesForPairs && even_sms >= 2u && !(p.flags & kFlagNoTailSplit)) {
+    if (lazy_recipe && !causal && !fused && min_tiles >= kMinTilesForPairs && even_sms >= 2u && !(p.flags & kFlagNoTailSplit)) {
         const uint32_t rounds = q.n_items / even_sms, tail = q.n_items - rounds * even_sms;
         if (tail > 0u && 2u * tail <= even_sms) {
             const uint32_t grid = rounds > 0u ? even_sms : 2u * tail;

@@ -252,6 +252,13 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
         if (p.peer != nullptr && (!(p.flags & FMHA_MXFP8_FLAG_F32_PARTIALS) || grid[2] != s->kvs_splits || s->kvs_splits != 1u)) return FMHA_MXFP8_E_ARG;
         p.lse2 = static_cast<float*>(s->ptr_lse);
         B = grid[2] / p.splits;
+        // the fused merge (extension): counters, the final output, f16 partials that stay on this GPU
+        if (p.flags & FMHA_MXFP8_FLAG_FUSED_COMBINE) {
+            p.fused_counters = static_cast<uint32_t*>(s->ext_ptr_fused_counters);
+            if (p.fused_counters == nullptr || (reinterpret_cast<uintptr_t>(p.fused_counters) & 3u) || p.o == nullptr || p.peer != nullptr ||
+                (p.flags & FMHA_MXFP8_FLAG_F32_PARTIALS) || p.splits > 8u || g_trace.load(std::memory_order_relaxed) != nullptr)
+                return FMHA_MXFP8_E_ARG;
+        }
     }
     CUtensorMap tq, tk, tv;
     int r = make_tile_map(&tq, a->ptr_q, p.S, p.H, B, a->s_Hs, a->s_Seqs, a->s_Bs, 128u);
@@ -401,7 +408,7 @@ int fmha_mxfp8_auto(const fmha_mxfp8_problem* pr, int path, uint32_t splits, voi
     a.ptr_q_descale = const_cast<void*>(pr->q_descale); a.ptr_k_descale = const_cast<void*>(pr->k_descale); a.ptr_v_descale = const_cast<void*>(pr->v_descale);
     a.s_descale_q_Bs = static_cast<uint32_t>(S * H * 4); a.s_descale_q_Hs = 4;
     a.s_descale_k_Bs = static_cast<uint32_t>(SK * HK * 4); a.s_descale_k_Hs = 4;
-    a.ext_flags = pr->flags | (pr->v_blockscale ? FMHA_MXFP8_FLAG_V_BLOCKSCALE : 0u);
+    a.ext_flags = (pr->flags & ~FMHA_MXFP8_FLAG_FUSED_COMBINE) | (pr->v_blockscale ? FMHA_MXFP8_FLAG_V_BLOCKSCALE : 0u);
     a.ext_ptr_v_blockscale = const_cast<void*>(pr->v_blockscale);
     if (S * H * 256 * 1ull > 0xFFFFFFFFull || SK * HK * 128 > 0xFFFFFFFFull) return fail(err, cap, FMHA_MXFP8_E_ARG, "a batch stride does not fit the u32 kernel argument");
 
@@ -440,6 +447,18 @@ int fmha_mxfp8_auto(const fmha_mxfp8_problem* pr, int path, uint32_t splits, voi
     fmha_mxfp8_grid(FMHA_MXFP8_COMBINE8H, &c, nullptr, cgrid);
     r = fmha_mxfp8_validate(FMHA_MXFP8_COMBINE8H, &c, &csz, cgrid, nullptr, err, cap);
     if (r) return r;
+    if (pr->flags & FMHA_MXFP8_FLAG_FUSED_COMBINE) {
+        // one kernel: the counters sit behind the f16 partials in the f32-sized allocation and are cleared in front of every call
+        const uint64_t n_blocks = B * H * ((S + 127) / 128), off = static_cast<uint64_t>(splits) * rows_total * 256u;
+        if (off + n_blocks * 4u > pr->ws_ohat_bytes) return fail(err, cap, FMHA_MXFP8_E_ARG, "ws_ohat too small for the fused merge's counters");
+        a.ext_flags |= FMHA_MXFP8_FLAG_FUSED_COMBINE;
+        a.ext_ptr_fused_counters = static_cast<uint8_t*>(pr->ws_ohat) + off;
+        const cudaError_t e = cudaMemsetAsync(a.ext_ptr_fused_counters, 0, n_blocks * 4u, static_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return fail(err, cap, -static_cast<int>(e), "clearing the counters failed");
+        r = fmha_mxfp8_launch(FMHA_MXFP8_KVSPLIT, &a, grid, stream);
+        if (r) return fail(err, cap, r, "kvsplit launch failed");
+        return 0;
+    }
     r = fmha_mxfp8_launch(FMHA_MXFP8_KVSPLIT, &a, grid, stream);
     if (r) return fail(err, cap, r, "kvsplit launch failed");
     r = fmha_mxfp8_launch(FMHA_MXFP8_COMBINE8H, &c, cgrid, stream);

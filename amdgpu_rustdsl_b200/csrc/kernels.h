@@ -38,6 +38,8 @@ struct AttnParams {
     const uint8_t* k_descale;   // E8M0 [B,SK,HK,4]
     const float* v_descale;     // one f32
     const uint8_t* v_blockscale;  // extension: E8M0 [B,ceil(SK/32),HK,128], may be null
+    uint32_t* fused_counters;     // extension (split kernel, f16 partials): one arrival counter per 128-row block, zero at launch and at exit; the
+                                  // CTA that brings a block's count to `splits` merges the block's partials into `o`. Null: the combine is a kernel of its own
     const PeerPlan* peer;         // extension (split kernel, f32 partials, B = 1): store the partial rows to the GPUs that combine them; may be null
     // shape
     uint32_t S, SK, H, HK, gqa_shift;
@@ -60,6 +62,25 @@ struct AttnParams {
 // partials as a 5-D map (split kernel): f16 with a 128-row x 64-column box, or f32 with a 128-row x 32-column box
 cudaError_t launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnParams& p,
                              uint32_t B, bool split, uint32_t rows_per_cta, cudaStream_t stream);
+
+#ifdef __CUDACC__
+// The merge of the split partials, one split at a time, shared by the combine kernel and by the split kernel's fused merge so that both
+// give the same bits (crates/amdgpu-tile/src/epilogue.rs:117-146): m' = max(m, lse); a = 2^(m - m'); w = 2^(lse - m');
+// den = den a + w; acc = acc a + w v. The products and sums are spelled out so that no two call sites contract them differently.
+__device__ __forceinline__ void combine_weights(float& m, float& den, float lse, float& a, float& w) {
+    const float mn = fmaxf(m, lse);
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(a) : "f"(m - mn));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(w) : "f"(lse - mn));
+    den = __fmaf_rn(den, a, w);
+    m = mn;
+}
+__device__ __forceinline__ float combine_accumulate(float acc, float a, float w, float v) { return __fmaf_rn(acc, a, __fmul_rn(w, v)); }
+__device__ __forceinline__ float2 combine_h2_to_f2(uint32_t h2) {
+    float2 f;
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.f32.f16 %0, lo;\n\tcvt.f32.f16 %1, hi;\n\t}" : "=f"(f.x), "=f"(f.y) : "r"(h2));
+    return f;
+}
+#endif
 
 cudaError_t launch_combine_scatter(const void* ohat, const float* lse2, const OutPointers& outs, uint32_t rows, uint32_t splits, cudaStream_t stream);
 cudaError_t launch_combine(const void* ohat, bool f32_partials, const float* lse2, uint8_t* out, uint32_t rows_total, uint32_t splits, cudaStream_t stream);

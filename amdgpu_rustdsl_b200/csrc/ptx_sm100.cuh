@@ -196,6 +196,9 @@ __device__ __forceinline__ void tma_store_5d(const CUtensorMap* m, uint32_t src,
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // the stores of this thread's groups have read their shared-memory source / have completed
 __device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all of this thread's bulk stores have been performed (not only read out of shared memory); the proxy fence orders them, writes of the
+// async proxy, before what this thread does next through the generic proxy
+__device__ __forceinline__ void bulk_wait_group_done0() { asm volatile("cp.async.bulk.wait_group 0;\n\tfence.proxy.async.global;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // named barrier among `count` threads (a multiple of 32); id 0 is __syncthreads
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }

@@ -33,7 +33,7 @@ def _ws_key(name, device, stream):
     return (name, device.index if device.index is not None else -1, int(stream))
 
 
-def _ws(name, nbytes, device, stream):
+def _ws(name, nbytes, device, stream, zero=False):
     """Grow-only per-device, per-stream workspace for the KV-split partials (the reference's ``_ws``, ops.py:72-85, which frees the old
     buffer with a synchronising ``hipFree``). Here the old buffer goes back to torch's caching allocator, which only orders its reuse
     against torch's own current stream: a split or combine still running on ``stream`` is therefore waited for first."""
@@ -43,7 +43,11 @@ def _ws(name, nbytes, device, stream):
     if buf is None or buf.numel() < nbytes:
         if buf is not None:
             (torch.cuda.ExternalStream(int(stream), device=device) if stream else torch.cuda.default_stream(device)).synchronize()
-        buf = _workspace[key] = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        if zero:   # cleared once; its users leave it cleared. The fill runs on torch's current stream: it must be done before `stream` uses it
+            buf = _workspace[key] = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+            torch.cuda.current_stream(device).synchronize()
+        else:
+            buf = _workspace[key] = torch.empty(nbytes, dtype=torch.uint8, device=device)
     return buf
 
 
@@ -81,7 +85,7 @@ def fill_common(a, q, k, v, q_scale, k_scale, v_scale, out, B, S, H, SK, HK, fla
 
 
 def fmha_fwd_mxfp8(q, k, v, q_scale, k_scale, v_scale, out, *, path="auto", splits=None, stream=None, check=True, flags=0,
-                   v_blockscale=None, lse=None, causal=False):
+                   v_blockscale=None, lse=None, causal=False, fused_combine=False):
     """MXFP8 attention forward, head dim 128: ``out = softmax2(q k^T) v`` with E8M0 1x32 scales on q and k and a scalar f32 V descale.
 
     q        [B, S, H, 128]  e4m3 bytes (uint8 or float8_e4m3fn)      k, v  [B, SK, HK, 128]  (H = gqa * HK, gqa a power of two <= 16)
@@ -90,6 +94,9 @@ def fmha_fwd_mxfp8(q, k, v, q_scale, k_scale, v_scale, out, *, path="auto", spli
     v_scale  f32 buffer of at least 4096 bytes, element 0 is the V descale
     out      [B, S, H, 128]  bf16
     path     "auto" | "vs128" | "t128" | "kvsplit" (splits in {2, 4, 8}).  Returns (path, splits) like the reference.
+    fused_combine  extension: on the kvsplit path the split kernel also merges the partials (the CTA that stores a row block's last partial
+             does it), so no combine kernel is launched; same bytes as the two-kernel form. Ignored on the unsplit paths. If a launch ever
+             fails (``device_status() != 0``), call ``reset_workspaces()`` before the next fused call: the arrival counters may be left non-zero.
     causal   extension (the reference's MXFP8 path has no mask): key k visible to row i when k < min(i + SK - S + 1, SK); needs SK >= S,
              unsplit paths only ("auto" then never picks the split).
     """
@@ -106,6 +113,8 @@ def fmha_fwd_mxfp8(q, k, v, q_scale, k_scale, v_scale, out, *, path="auto", spli
         raise ValueError("fmha_fwd_mxfp8: q, k, v are 1-byte e4m3 tensors and out is bf16")
     if _nbytes(v_scale) < 4:
         raise ValueError("v_scale: needs at least one f32")
+    if fused_combine:
+        flags |= _abi.FLAG_FUSED_COMBINE
     if causal:
         flags |= _abi.FLAG_CAUSAL
         if SK < S:
@@ -129,7 +138,7 @@ def _launch_path(lib, q, k, v, q_scale, k_scale, v_scale, out, path, splits, str
     syms = _abi.Symbols(B=B, HK=HK, KL=0)
     if path in ("vs128", "t128"):
         rows = 256 if path == "vs128" else 128
-        a = fill_common(_abi.AttnArgs(), q, k, v, q_scale, k_scale, v_scale, out, B, S, H, SK, HK, flags, v_blockscale, lse)
+        a = fill_common(_abi.AttnArgs(), q, k, v, q_scale, k_scale, v_scale, out, B, S, H, SK, HK, flags & ~_abi.FLAG_FUSED_COMBINE, v_blockscale, lse)
         _check_launch(lib, PATH_IDS[path], a, sizes, _abi.grid3(math.ceil(S / rows), H, B), syms, stream, check)
         return path, 0
     if path != "kvsplit" or splits not in (2, 4, 8):
@@ -140,12 +149,23 @@ def _launch_path(lib, q, k, v, q_scale, k_scale, v_scale, out, path, splits, str
     a = fill_common(_abi.KvSplitArgs(), q, k, v, q_scale, k_scale, v_scale, out, B, S, H, SK, HK, flags, v_blockscale, None)
     a.ptr_ohat, a.ptr_lse, a.kvs_splits, a.kvs_rows_total = ohat.data_ptr(), lse_ws.data_ptr(), splits, rows_total
     sizes.ptr_ohat, sizes.ptr_lse = splits * rows_total * D * 4, splits * rows_total * 4
+    if flags & _abi.FLAG_FUSED_COMBINE:
+        a.ext_ptr_fused_counters = _ws("fused_counters", 4 * B * H * math.ceil(S / 128), q.device, stream, zero=True).data_ptr()
     _check_launch(lib, KVSPLIT, a, sizes, _abi.grid3(math.ceil(S / 256), H, B * splits), syms, stream, check)
+    if flags & _abi.FLAG_FUSED_COMBINE:
+        return path, splits
     c = _abi.CombineArgs(ptr_ohat=ohat.data_ptr(), ptr_lse=lse_ws.data_ptr(), ptr_out=out.data_ptr(), rows_total=rows_total, d=D, splits=splits)
     csizes = _abi.BufferSizes(ptr_ohat=sizes.ptr_ohat, ptr_lse=sizes.ptr_lse, ptr_out=_nbytes(out))
     cgrid = max(1, math.ceil(rows_total * D / (256 * 8)))
     _check_launch(lib, COMBINE8H, c, csizes, _abi.grid3(cgrid, 1, 1), None, stream, check)
     return path, splits
+
+
+def reset_workspaces():
+    """Drops the cached KV-split workspaces (partials, log-sum-exps, the fused merge's counters) after a synchronise; the next call makes new ones."""
+    import torch
+    torch.cuda.synchronize()
+    _workspace.clear()
 
 
 def device_status() -> int:

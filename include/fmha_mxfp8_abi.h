@@ -67,6 +67,17 @@ enum fmha_mxfp8_error {
  * memory. This flag keeps every item whole. Results agree to f32 summation order either way.
  */
 #define FMHA_MXFP8_FLAG_NO_TAIL_SPLIT 0x20u
+/*
+ * Fused merge (extension; the reference tried the same idea as its "last arriver" combine, tests/gpu/ref_host.cpp:489-497, and kept the
+ * two-kernel form): the kvsplit kernel also produces the final bf16 output at `ptr_o`, so no combine8h launch follows. Every CTA that has
+ * stored a partial of a 128-row block adds one to the block's counter; the CTA that completes the count merges the block's partials with
+ * the arithmetic of combine8h (same bits). Needs `ext_ptr_fused_counters` of the kvsplit Args: uint32 [B * H * ceil(S / 128)], zero
+ * before the first launch that uses them; a launch that ends with status 0 leaves them zero. f16 partials only (not with
+ * FMHA_MXFP8_FLAG_F32_PARTIALS or a peer plan), at most 8 splits; such a launch is refused with FMHA_MXFP8_E_ARG otherwise. With this bit
+ * in fmha_mxfp8_problem.flags, fmha_mxfp8_auto keeps the counters behind the f16 partials in `ws_ohat` (the allocation is sized for f32)
+ * and clears them in front of every call; the bit is ignored when the path is not kvsplit.
+ */
+#define FMHA_MXFP8_FLAG_FUSED_COMBINE 0x40u
 
 #pragma pack(push, 1)
 /*
@@ -150,7 +161,7 @@ typedef struct fmha_mxfp8_kvsplit_args {
     uint8_t _pad2[8];
     void* ptr_v;
     void* ext_ptr_peer_plan;     /* 0x038 optional: a device plan from fmha_mxfp8_peer_plan_build; the partial rows then go to other GPUs */
-    void* ext_ptr_lse;           /* unused by kvsplit */
+    void* ext_ptr_fused_counters; /* 0x040 with FMHA_MXFP8_FLAG_FUSED_COMBINE: uint32 [B * H * ceil(S / 128)] arrival counters, zero on entry; else unused */
     void* ext_ptr_v_blockscale;
     uint8_t _pad3b[8];
     uint32_t ext_flags;
