@@ -579,6 +579,18 @@ def run_sharded(R, wl):
     step(s)
     torch.cuda.synchronize()
     res["parity"] = parity_sample(R, W, s)
+    if wl == "c3":
+        # the same step with the merge of the partials built into the split kernel (one launch instead of two): same bytes, its own timing
+        from amdgpu_rustdsl_b200 import fmha_fwd_mxfp8
+        want = s["out"].clone()
+        fused = lambda i: fmha_fwd_mxfp8(s["q"], s["k"], s["v"], s["qs"], s["ks"], s["vs"], s["out"], path=W["path"], splits=W["splits"], fused_combine=True)
+        for _ in range(3):
+            fused(0)
+        torch.cuda.synchronize()
+        same = bool(torch.equal(s["out"].view(torch.int16), want.view(torch.int16)))
+        fwin = R.windows(fused, 1, per_window)
+        fms = statistics.median(fwin) / per_window
+        res["fused_merge"] = {"ms_per_step": fms, "value": flops(B, H, S, SK) / (fms * 1e-3) / 1e12, "same_bytes_as_two_kernels": same, "windows_ms": fwin}
     if wl == "c5":
         W["plan"].close()
     W["sets"] = None
