@@ -165,14 +165,32 @@ __device__ __forceinline__ uint32_t p_word(uint32_t s0, uint32_t s1, uint32_t s2
 // tensor rate, so two of every four P values are produced on the FMA pipe instead, straight as e4m3 bit patterns:
 // byte = rne(8 (x + 7)) with x = log2 P, i.e. exponent field = floor(x) + 7 and a mantissa that is linear in the fraction of x
 // (the piecewise-linear exp2 the reference uses for all of P, crates/amdgpu-tile/src/reduce.rs:94-113, docs/vendor-spec.md:271-281).
-// fma.sat clamps to [0, 1] = bytes 0..256 (so -inf scores give 0), and adding 2^15 leaves rne(256 t) in the low byte of the sum.
+// fma.sat clamps t = s / 32 + c to [0, 1] = bytes 0..256 (so -inf scores give 0), and adding 2^15 leaves rne(256 t) in the low byte of the
+// sum. The additions (this one, and the shift in front of the exp2 of the other two values) are done two at a time (add.f32x2); the
+// two-wide fma has no saturating form, so the clamped fma stays one per value.
 // The linear mantissa overestimates 2^frac by 3.97 % on average; kFastBias shifts x so that the two kinds of P values agree on
 // average, otherwise mixing them in one row sum would bias the weights.
 constexpr float kFastBias = 0.0562f;
-__device__ __forceinline__ uint32_t fast_p_bits(uint32_t s, float c) {
+// Two f32 additions in one instruction (sm_100 has two-wide f32 add / mul / fma on 64-bit register pairs): a += c, b += c.
+__device__ __forceinline__ void add2(uint32_t& a, uint32_t& b, float c) {
+    unsigned long long p, q;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(p) : "r"(a), "r"(b));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(q) : "f"(c));
+    asm("add.rn.ftz.f32x2 %0, %1, %2;" : "=l"(p) : "l"(p), "l"(q));
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(p));
+}
+// a *= c, b *= c in one instruction
+__device__ __forceinline__ void mul2(uint32_t& a, uint32_t& b, float c) {
+    unsigned long long p, q;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(p) : "r"(a), "r"(b));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(q) : "f"(c));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(p) : "l"(p), "l"(q));
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(p));
+}
+__device__ __forceinline__ uint32_t fast_p_sat(uint32_t s, float c) {   // s / 32 + c clamped to [0, 1]
     float t;
-    asm("fma.rn.sat.f32 %0, %1, 0f3D000000, %2;" : "=f"(t) : "f"(__uint_as_float(s)), "f"(c));   // s / 32 + c
-    return __float_as_uint(t + 32768.0f);
+    asm("fma.rn.sat.f32 %0, %1, 0f3D000000, %2;" : "=f"(t) : "f"(__uint_as_float(s)), "f"(c));
+    return __float_as_uint(t);
 }
 __device__ __forceinline__ void st_shared_v2(uint32_t addr, uint32_t a, uint32_t b) {
     asm volatile("st.volatile.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
@@ -843,10 +861,12 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
                     for (int c = 0; c < 32 + kConvDepth; ++c) {
                         if (c < 32) {
-                            v[4 * c] = __float_as_uint(ex2_approx(__uint_as_float(v[4 * c]) + sh));
-                            v[4 * c + 1] = __float_as_uint(ex2_approx(__uint_as_float(v[4 * c + 1]) + sh));
-                            v[4 * c + 2] = fast_p_bits(v[4 * c + 2], cf);
-                            v[4 * c + 3] = fast_p_bits(v[4 * c + 3], cf);
+                            add2(v[4 * c], v[4 * c + 1], sh);
+                            v[4 * c] = __float_as_uint(ex2_approx(__uint_as_float(v[4 * c])));
+                            v[4 * c + 1] = __float_as_uint(ex2_approx(__uint_as_float(v[4 * c + 1])));
+                            v[4 * c + 2] = fast_p_sat(v[4 * c + 2], cf);
+                            v[4 * c + 3] = fast_p_sat(v[4 * c + 3], cf);
+                            add2(v[4 * c + 2], v[4 * c + 3], 32768.0f);
                         }
                         if (c >= kConvDepth) {
                             const int d = c - kConvDepth;
@@ -1006,7 +1026,8 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         uint32_t wv[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const float a = __uint_as_float(o[8 * q4 + 2 * e]) * fin, b = __uint_as_float(o[8 * q4 + 2 * e + 1]) * fin;
+                            mul2(o[8 * q4 + 2 * e], o[8 * q4 + 2 * e + 1], fin);
+                            const float a = __uint_as_float(o[8 * q4 + 2 * e]), b = __uint_as_float(o[8 * q4 + 2 * e + 1]);
                             if (kSplit) {
                                 asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(wv[e]) : "f"(b), "f"(a));
                             } else {
