@@ -94,13 +94,14 @@ kvsplit_combine_kernel(const void* __restrict__ ohat, const float* __restrict__ 
 
 }  // namespace
 
-cudaError_t launch_combine_scatter(const void* ohat, const float* lse2, const OutPointers& outs, uint32_t rows, uint32_t splits, cudaStream_t stream) {
-    const uint64_t ngroups = static_cast<uint64_t>(rows) * 16u;
+cudaError_t launch_combine_scatter(const void* ohat, bool f32_partials, const float* lse2, const OutPointers& outs, uint32_t rows, uint32_t splits, cudaStream_t stream) {
+    const uint64_t ngroups = static_cast<uint64_t>(rows) * (f32_partials ? 16u : 8u);
     uint64_t blocks = (ngroups + 255u) / 256u;
     const uint64_t cap = 148u * 8u * 4u;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    kvsplit_combine_kernel<true, true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(ohat, lse2, nullptr, rows, splits, outs);
+    if (f32_partials) kvsplit_combine_kernel<true, true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(ohat, lse2, nullptr, rows, splits, outs);
+    else kvsplit_combine_kernel<false, true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(ohat, lse2, nullptr, rows, splits, outs);
     return cudaGetLastError();
 }
 

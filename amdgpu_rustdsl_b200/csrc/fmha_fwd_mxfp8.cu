@@ -1044,8 +1044,17 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 named_bar_sync(kEpiBar, 128u);
                 if (issuer) {
                     if (kSplit) {
-                        tma_store_5d(&tm_o, stg, 0, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch), static_cast<int>(it.split));
-                        tma_store_5d(&tm_o, stg + 16384u, 64, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch), static_cast<int>(it.split));
+                        // with a routing plan the rows go to the GPU that combines them (its receive slot of this GPU), else to this launch's own partial buffer
+                        const CUtensorMap* omap = &tm_o;
+                        int o_row = static_cast<int>(it.row0), o_split = static_cast<int>(it.split);
+                        if (!kFused && p.peer != nullptr) {
+                            const uint32_t dest = it.row0 / p.peer->dest_rows;
+                            omap = &p.peer->maps[dest];
+                            o_row = static_cast<int>(it.row0 - dest * p.peer->dest_rows);
+                            o_split = static_cast<int>(p.peer->rank);
+                        }
+                        tma_store_5d(omap, stg, 0, static_cast<int>(it.head), o_row, static_cast<int>(it.batch), o_split);
+                        tma_store_5d(omap, stg + 16384u, 64, static_cast<int>(it.head), o_row, static_cast<int>(it.batch), o_split);
                     } else {
                         tma_store_4d(&tm_o, stg, 0, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));
                         tma_store_4d(&tm_o, stg + 16384u, 64, static_cast<int>(it.head), static_cast<int>(it.row0), static_cast<int>(it.batch));

@@ -247,9 +247,9 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
         p.split_log2 = log2_u32(p.splits);
         p.rows_total = s->kvs_rows_total;
         p.ohat = s->ptr_ohat;
-        // the partial rows go to the GPUs that combine them (extension): f32 partials, one batch element, no V block scales
+        // the partial rows go to the GPUs that combine them (extension): one batch element; the plan was built for f16 or f32 partials and the launch must use the same
         p.peer = static_cast<const b200mx::PeerPlan*>(a->ext_ptr_peer_plan);
-        if (p.peer != nullptr && (!(p.flags & FMHA_MXFP8_FLAG_F32_PARTIALS) || grid[2] != s->kvs_splits || s->kvs_splits != 1u)) return FMHA_MXFP8_E_ARG;
+        if (p.peer != nullptr && (grid[2] != s->kvs_splits || s->kvs_splits != 1u)) return FMHA_MXFP8_E_ARG;
         p.lse2 = static_cast<float*>(s->ptr_lse);
         B = grid[2] / p.splits;
         // the fused merge (extension): counters, the final output, f16 partials that stay on this GPU
@@ -282,8 +282,8 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
 }  // namespace
 
 namespace b200mx {
-int encode_partial_map_f32(CUtensorMap* m, void* base, uint64_t seq, uint64_t heads, uint64_t batches, uint64_t splits) {
-    return make_partial_map(m, base, seq, heads, batches, splits, true);
+int encode_partial_map(CUtensorMap* m, void* base, uint64_t seq, uint64_t heads, uint64_t batches, uint64_t splits, bool f32) {
+    return make_partial_map(m, base, seq, heads, batches, splits, f32);
 }
 __device__ uint32_t g_status_word = 0;
 uint32_t* device_status_word() {

@@ -40,7 +40,7 @@ struct AttnParams {
     const uint8_t* v_blockscale;  // extension: E8M0 [B,ceil(SK/32),HK,128], may be null
     uint32_t* fused_counters;     // extension (split kernel, f16 partials): one arrival counter per 128-row block, zero at launch and at exit; the
                                   // CTA that brings a block's count to `splits` merges the block's partials into `o`. Null: the combine is a kernel of its own
-    const PeerPlan* peer;         // extension (split kernel, f32 partials, B = 1): store the partial rows to the GPUs that combine them; may be null
+    const PeerPlan* peer;         // extension (split kernel, B = 1): store the partial rows to the GPUs that combine them (the plan's maps must be of the launch's partial format); may be null
     // shape
     uint32_t S, SK, H, HK, gqa_shift;
     uint32_t o_row_stride, o_batch_stride;    // bytes
@@ -82,7 +82,7 @@ __device__ __forceinline__ float2 combine_h2_to_f2(uint32_t h2) {
 }
 #endif
 
-cudaError_t launch_combine_scatter(const void* ohat, const float* lse2, const OutPointers& outs, uint32_t rows, uint32_t splits, cudaStream_t stream);
+cudaError_t launch_combine_scatter(const void* ohat, bool f32_partials, const float* lse2, const OutPointers& outs, uint32_t rows, uint32_t splits, cudaStream_t stream);
 cudaError_t launch_combine(const void* ohat, bool f32_partials, const float* lse2, uint8_t* out, uint32_t rows_total, uint32_t splits, cudaStream_t stream);
 
 // Quantisers in front of the path (quantize.cu): bf16 -> e4m3 + E8M0 per 32 head-dim elements (Q with `mul` folded in, K), bf16 -> e4m3 +

@@ -1,5 +1,5 @@
 // Key-range sharding across the GPUs of one node without a collective for the partials: every GPU's split kernel stores the rows of
-// its f32 partial straight into the memory of the GPU that will combine them (TMA tile stores and plain stores to peer memory over
+// its partial (f16, or f32 on request) straight into the memory of the GPU that will combine them (TMA tile stores and plain stores to peer memory over
 // NVLink, as the tiles come out of tensor memory, so the transfer runs under the remaining compute), and every GPU's combine kernel
 // stores its bf16 row slice into every GPU's output buffer. Between the two kernels, and after the second, the ranks only need a barrier.
 // The reference has no multi-GPU code; the algebra is its KV-split one with "split = GPU" (crates/amdgpu-stage/src/components.rs:58-74,
@@ -14,7 +14,7 @@
 #include <cstring>
 
 namespace b200mx {
-int encode_partial_map_f32(CUtensorMap* m, void* base, uint64_t seq, uint64_t heads, uint64_t batches, uint64_t splits);   // host_api.cu
+int encode_partial_map(CUtensorMap* m, void* base, uint64_t seq, uint64_t heads, uint64_t batches, uint64_t splits, bool f32);   // host_api.cu
 }
 
 extern "C" {
@@ -54,7 +54,8 @@ int fmha_mxfp8_peer_free(void* dev_ptr) {
     return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }
 
-int fmha_mxfp8_peer_plan_build(uint32_t world, uint32_t rank, uint32_t H, uint32_t S, void* const* ohat_recv, void* const* lse_recv, void* plan_dev, void* stream) {
+int fmha_mxfp8_peer_plan_build(uint32_t world, uint32_t rank, uint32_t H, uint32_t S, int f32_partials, void* const* ohat_recv, void* const* lse_recv, void* plan_dev,
+                               void* stream) {
     if (world < 2 || world > FMHA_MXFP8_PEER_MAX_GPUS || rank >= world || H == 0 || S == 0 || !ohat_recv || !lse_recv || !plan_dev) return FMHA_MXFP8_E_ARG;
     // a 128-row block of queries must belong to one destination: whole blocks per GPU
     if (S % world != 0 || (S / world) % 128u != 0) return FMHA_MXFP8_E_ARG;
@@ -67,8 +68,8 @@ int fmha_mxfp8_peer_plan_build(uint32_t world, uint32_t rank, uint32_t H, uint32
     plan.dest_rows = S / world;
     for (uint32_t d = 0; d < world; ++d) {
         if (!ohat_recv[d] || !lse_recv[d]) return FMHA_MXFP8_E_ARG;
-        // destination d's receive buffer: f32 [source GPU][its S / world query rows][H][128]
-        const int r = b200mx::encode_partial_map_f32(&plan.maps[d], ohat_recv[d], plan.dest_rows, H, 1, world);
+        // destination d's receive buffer: f16 or f32 [source GPU][its S / world query rows][H][128]
+        const int r = b200mx::encode_partial_map(&plan.maps[d], ohat_recv[d], plan.dest_rows, H, 1, world, f32_partials != 0);
         if (r) return r;
         plan.lse[d] = static_cast<float*>(lse_recv[d]);
     }
@@ -78,8 +79,8 @@ int fmha_mxfp8_peer_plan_build(uint32_t world, uint32_t rank, uint32_t H, uint32
     return e2 == cudaSuccess ? 0 : -static_cast<int>(e2);
 }
 
-int fmha_mxfp8_combine_f32_scatter(const void* ohat, const void* lse, void* const* outs, uint32_t n_outs, uint64_t row_offset, uint32_t rows, uint32_t splits,
-                                   void* stream) {
+int fmha_mxfp8_combine_scatter(const void* ohat, int f32_partials, const void* lse, void* const* outs, uint32_t n_outs, uint64_t row_offset, uint32_t rows,
+                               uint32_t splits, void* stream) {
     if (!ohat || !lse || !outs || n_outs == 0 || n_outs > FMHA_MXFP8_PEER_MAX_GPUS || rows == 0 || splits == 0) return FMHA_MXFP8_E_ARG;
     b200mx::OutPointers op;
     std::memset(&op, 0, sizeof op);
@@ -88,7 +89,7 @@ int fmha_mxfp8_combine_f32_scatter(const void* ohat, const void* lse, void* cons
         op.out[i] = static_cast<uint8_t*>(outs[i]) + row_offset * 256u;
     }
     op.n = n_outs;
-    const cudaError_t e = b200mx::launch_combine_scatter(ohat, static_cast<const float*>(lse), op, rows, splits, static_cast<cudaStream_t>(stream));
+    const cudaError_t e = b200mx::launch_combine_scatter(ohat, f32_partials != 0, static_cast<const float*>(lse), op, rows, splits, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }
 

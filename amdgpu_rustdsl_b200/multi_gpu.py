@@ -41,9 +41,10 @@ def kv_range_shard(SK: int, rank: int, world: int):
     return lo, hi
 
 
-def local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, lse, *, stream=None, check=True, peer_plan=None):
+def local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, lse, *, stream=None, check=True, peer_plan=None, f32_partials=True):
     """One rank's contribution to a key-range-sharded forward: the split kernel with splits = 1 over the local keys, writing the
-    normalised f32 partial O [rows_total,128] and base-2 log-sum-exp [rows_total] of all queries."""
+    normalised partial O [rows_total,128] (f32, or f16 with ``f32_partials=False``) and base-2 log-sum-exp [rows_total] of all queries.
+    With ``peer_plan`` (a device plan built for the same partial format) the rows go to the GPUs that combine them instead."""
     import ctypes as C
     import torch
     from . import _abi
@@ -54,12 +55,15 @@ def local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, l
     if stream is None:
         stream = torch.cuda.current_stream(q.device).cuda_stream
     rows_total = B * S * H
-    # f32 partials: these travel between GPUs before they are combined
-    a = fill_common(_abi.KvSplitArgs(), q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, B, S, H, SKl, HK, flags=_abi.FLAG_F32_PARTIALS)
+    a = fill_common(_abi.KvSplitArgs(), q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, B, S, H, SKl, HK,
+                    flags=_abi.FLAG_F32_PARTIALS if f32_partials else 0)
     a.ptr_o = None
     a.ptr_ohat, a.ptr_lse, a.kvs_splits, a.kvs_rows_total = ohat.data_ptr(), lse.data_ptr(), 1, rows_total
     sizes = _abi.BufferSizes(ptr_q=_nbytes(q), ptr_k=_nbytes(k_local), ptr_v=_nbytes(v_local), ptr_o=B * S * H * 256, ptr_q_descale=_nbytes(q_scale),
                              ptr_k_descale=_nbytes(k_scale_local), ptr_v_descale=_nbytes(v_scale), ptr_ohat=_nbytes(ohat), ptr_lse=_nbytes(lse))
+    if not f32_partials:
+        # the contract sizes ptr_ohat for f32 rows whatever the kernel writes; this helper's f16 buffers hold exactly the f16 rows
+        sizes.ptr_ohat = 2 * _nbytes(ohat)
     if peer_plan is not None:
         # the partial rows go to the GPUs that combine them (fmha_mxfp8_peer_plan_build): ohat / lse are not written and only stand in
         # for the contract's pointer fields; their extents are not this launch's concern
@@ -71,7 +75,7 @@ def local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ohat, l
 
 
 def combine_gathered(ohat_all, lse_all, out, world: int, *, stream=None, check=True):
-    """The combine kernel over the gathered f32 partials: ohat_all f32 [world, rows_total, 128], lse_all f32 [world, rows_total] -> bf16 out."""
+    """The combine kernel over the gathered partials: ohat_all f32 or f16 [world, rows_total, 128], lse_all f32 [world, rows_total] -> bf16 out."""
     import ctypes as C
     import torch
     from . import _abi
@@ -79,14 +83,18 @@ def combine_gathered(ohat_all, lse_all, out, world: int, *, stream=None, check=T
     rows_total = out.numel() // D
     if stream is None:
         stream = torch.cuda.current_stream(out.device).cuda_stream
-    if ohat_all.dtype != torch.float32 or lse_all.dtype != torch.float32 or out.dtype != torch.bfloat16:
-        raise ValueError("combine_gathered: f32 partials and log-sum-exps, bf16 output")
+    if ohat_all.dtype not in (torch.float32, torch.float16) or lse_all.dtype != torch.float32 or out.dtype != torch.bfloat16:
+        raise ValueError("combine_gathered: f32 or f16 partials, f32 log-sum-exps, bf16 output")
     if check and (ohat_all.numel() < world * rows_total * D or lse_all.numel() < world * rows_total):
         raise ValueError("combine_gathered: partial buffers smaller than world x rows_total")
     with torch.cuda.device(out.device):
-        rc = lib.fmha_mxfp8_combine_f32(ohat_all.data_ptr(), lse_all.data_ptr(), out.data_ptr(), rows_total, world, C.c_void_p(stream))
+        if ohat_all.dtype == torch.float32:
+            rc = lib.fmha_mxfp8_combine_f32(ohat_all.data_ptr(), lse_all.data_ptr(), out.data_ptr(), rows_total, world, C.c_void_p(stream))
+        else:   # the reference's own combine8h over f16 partials
+            c = _abi.CombineArgs(ptr_ohat=ohat_all.data_ptr(), ptr_lse=lse_all.data_ptr(), ptr_out=out.data_ptr(), rows_total=rows_total, d=D, splits=world)
+            rc = lib.fmha_mxfp8_launch(_abi.COMBINE8H, C.byref(c), _abi.grid3(max(1, math.ceil(rows_total * D / (256 * 8))), 1, 1), C.c_void_p(stream))
     if rc:
-        raise RuntimeError(f"fmha_mxfp8_combine_f32 failed with code {rc}")
+        raise RuntimeError(f"the combine failed with code {rc}")
 
 
 def exchange_partials(ohat, lse, ohat_all, lse_all, group=None):
@@ -147,10 +155,10 @@ def fmha_fwd_mxfp8_kv_sharded(q, k_local, v_local, q_scale, k_scale_local, v_sca
 
 class PeerBuffers:
     """One device allocation per rank that every process of the node maps (CUDA IPC through the library's fmha_mxfp8_peer_* entries), cut
-    into this rank's receive slots for the partials [world][n][128] f32, for their log-sum-exps [world][n] f32, and a whole bf16 output
+    into this rank's receive slots for the partials [world][n][128] (f16 or f32), for their log-sum-exps [world][n] f32, and a whole bf16 output
     [rows_total][128] that every rank's combine stores its row slice into. `ptr[r]` is rank r's allocation as mapped here."""
 
-    def __init__(self, rows_total: int, world: int, rank: int, device, group=None):
+    def __init__(self, rows_total: int, world: int, rank: int, device, group=None, f32_partials: bool = True):
         """Collective over `group`: every rank allocates, the ranks agree that all succeeded, exchange the handles, map each other's
         buffers and agree again. `ok` tells whether the buffers are usable on every rank; a rank never stops half way through the
         collectives, whatever failed locally."""
@@ -163,7 +171,8 @@ class PeerBuffers:
         n = rows_total // world
         self.n = n
         al = lambda x: (x + 255) // 256 * 256   # noqa: E731
-        self.off_lse = al(world * n * D * 4)
+        self.f32_partials = f32_partials
+        self.off_lse = al(world * n * D * (4 if f32_partials else 2))
         self.off_out = self.off_lse + al(world * n * 4)
         self.bytes = self.off_out + al(rows_total * D * 2)
         self.own = C.c_void_p()
@@ -222,15 +231,19 @@ class KvShardedPlan:
     """Workspaces and schedule of the key-range-sharded forward for one problem size on one rank (`world` = 1 runs the same two
     kernels without an exchange). `forward` runs a step; `timed_stages` runs steps with CUDA events between the stages.
 
-    transport "peer" (one batch element, S / world a multiple of 128 rows): the split kernel stores each row block of its f32 partial
-    straight into the memory of the GPU that combines it, as the block leaves tensor memory (no collective moves partials; the transfer
-    runs under the remaining compute); barrier; every GPU's combine stores its bf16 row slice into every GPU's output; barrier.
+    transport "peer" (one batch element, S / world a multiple of 128 rows): the split kernel stores each row block of its partial
+    (``partials`` "f32", or "f16", the reference's partial format and half the bytes over NVLink; measured no faster) straight into the memory of the GPU that
+    combines it, as the block leaves tensor memory (no collective moves partials; the transfer runs under the remaining compute); barrier;
+    every GPU's combine stores its bf16 row slice into every GPU's output; barrier.
     transport "nccl": split kernel -> all-to-all of the partial row slices -> combine of the own slice -> all-gather of the bf16 slices
     (or, when the rows do not divide, an all-gather of the whole partials)."""
 
-    def __init__(self, rows_total: int, world: int, device, group=None, transport: str = "auto", B: int = 1, S: int = 0, H: int = 0):
+    def __init__(self, rows_total: int, world: int, device, group=None, transport: str = "auto", B: int = 1, S: int = 0, H: int = 0, partials: str = "f32"):
         import torch
+        if partials not in ("f16", "f32"):
+            raise ValueError("partials: 'f16' or 'f32'")
         self.rows_total, self.world, self.device, self.group = rows_total, world, device, group
+        self.f32_partials = partials == "f32"   # of the peer transport; the NCCL exchange moves f32
         self.transport = "none" if world == 1 else "nccl"
         self.peer = None
         if world > 1 and transport in ("auto", "peer"):
@@ -251,7 +264,7 @@ class KvShardedPlan:
         import torch.distributed as dist
         from . import _abi
         rank = dist.get_rank(self.group)
-        self.peer = PeerBuffers(self.rows_total, self.world, rank, self.device, self.group)
+        self.peer = PeerBuffers(self.rows_total, self.world, rank, self.device, self.group, self.f32_partials)
         good, err = self.peer.ok, self.peer.error
         if good:
             try:
@@ -261,7 +274,7 @@ class KvShardedPlan:
                 ohat = (C.c_void_p * self.world)(*[pb.ptr[r] for r in range(self.world)])
                 lse = (C.c_void_p * self.world)(*[pb.ptr[r] + pb.off_lse for r in range(self.world)])
                 with torch.cuda.device(self.device):
-                    rc = pb.lib.fmha_mxfp8_peer_plan_build(self.world, rank, H, S, ohat, lse, C.c_void_p(self.plan_ptr), None)
+                    rc = pb.lib.fmha_mxfp8_peer_plan_build(self.world, rank, H, S, 1 if self.f32_partials else 0, ohat, lse, C.c_void_p(self.plan_ptr), None)
                 if rc:
                     raise RuntimeError(f"fmha_mxfp8_peer_plan_build failed with code {rc}")
                 self.outs = (C.c_void_p * self.world)(*[pb.ptr[r] + pb.off_out for r in range(self.world)])
@@ -281,7 +294,7 @@ class KvShardedPlan:
         if self.world == 1:
             return "one rank: split kernel over all keys + combine (splits = 1), no exchange"
         if self.transport == "peer":
-            return ("key-range shards: the split kernel stores its f32 partial row blocks into the combining GPU's memory over NVLink as they leave tensor memory "
+            return (f"key-range shards: the split kernel stores its {'f32' if self.f32_partials else 'f16'} partial row blocks into the combining GPU's memory over NVLink as they leave tensor memory "
                     "-> barrier -> every GPU's combine stores its bf16 row slice into every GPU's output -> barrier (no collective moves data)")
         if self.sliced:
             return "key-range shards: split kernel -> NCCL all-to-all of the f32 partial row slices and their log-sum-exps -> combine of the own slice -> NCCL all-gather of the bf16 slices"
@@ -303,10 +316,10 @@ class KvShardedPlan:
 
             def combine():
                 with torch.cuda.device(self.device):
-                    rc = pb.lib.fmha_mxfp8_combine_f32_scatter(C.c_void_p(pb.own.value), C.c_void_p(pb.own.value + pb.off_lse), self.outs, world,
-                                                               pb.rank * pb.n, pb.n, world, stream())
+                    rc = pb.lib.fmha_mxfp8_combine_scatter(C.c_void_p(pb.own.value), 1 if self.f32_partials else 0, C.c_void_p(pb.own.value + pb.off_lse), self.outs, world,
+                                                           pb.rank * pb.n, pb.n, world, stream())
                 if rc:
-                    raise RuntimeError(f"fmha_mxfp8_combine_f32_scatter failed with code {rc}")
+                    raise RuntimeError(f"fmha_mxfp8_combine_scatter failed with code {rc}")
 
             def take_output():
                 with torch.cuda.device(self.device):
@@ -315,7 +328,7 @@ class KvShardedPlan:
                     raise RuntimeError(f"fmha_mxfp8_copy_async failed with code {rc}")
 
             return [("split_kernel_storing_to_peers", lambda: local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ws["ohat"], ws["lse"], check=False,
-                                                                            peer_plan=self.plan_ptr)),
+                                                                            peer_plan=self.plan_ptr, f32_partials=self.f32_partials)),
                     ("barrier", self._barrier), ("combine_storing_to_peers", combine), ("barrier_2", self._barrier), ("copy_out", take_output)]
         st = [("split_kernel", lambda: local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ws["ohat"], ws["lse"], check=False))]
         if world == 1:

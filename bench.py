@@ -406,7 +406,7 @@ def make_step(R, W):
     Hl = W["local"][0]
     rows_total = B * S * Hl
     if wl == "c5":
-        W["plan"] = multi_gpu.KvShardedPlan(rows_total, R.world, R.dev, transport=R.args.c5_transport, B=B, S=S, H=Hl)
+        W["plan"] = multi_gpu.KvShardedPlan(rows_total, R.world, R.dev, transport=R.args.c5_transport, B=B, S=S, H=Hl, partials=R.args.c5_partials)
 
     def step(s):
         if wl == "c5":
@@ -612,6 +612,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sharded", action="store_true", help="skip the two sharded configurations of the `sharded` object")
     ap.add_argument("--c5-transport", default="auto", choices=["auto", "peer", "nccl"], help="how the key-range shards' partials reach the combining GPU")
+    ap.add_argument("--c5-partials", default="f32", choices=["f16", "f32"], help="format of the partial rows the key-range shards store into the combining GPU (peer transport)")
     ap.add_argument("--sets", type=int, default=0, help="number of rotating input sets (0 = enough to exceed L2)")
     args = ap.parse_args()
     if args.impl == "reference":

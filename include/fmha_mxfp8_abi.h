@@ -342,12 +342,14 @@ int fmha_mxfp8_combine_f32(const void* ohat, const void* lse, void* out, uint32_
  *       pointer and a 64-byte handle to pass to the peers, which open (and later close) it; the owner frees it after the peers closed.
  *   peer_plan_build: GPU d of `world` combines the query rows [d * S / world, (d + 1) * S / world) (S / world a multiple of 128, one batch
  *       element). ohat_recv[d] / lse_recv[d] are GPU d's receive buffers as mapped into this process (this GPU's own for d == rank):
- *       f32 [world][S / world][H][128] and f32 [world][S / world * H]. Writes FMHA_MXFP8_PEER_PLAN_BYTES to `plan_dev` (device memory,
- *       128-byte aligned), to be passed as ext_ptr_peer_plan of a kvsplit launch with kvs_splits = 1 and FMHA_MXFP8_FLAG_F32_PARTIALS: that
- *       launch stores row block x of its partial to slot [rank] of the receive buffers of GPU x * 128 / (S / world) (TMA tile stores and
- *       plain stores to peer memory; ptr_ohat / ptr_lse are then not written). The ranks must barrier before combining.
- *   combine_f32_scatter: the f32 combine over `rows` rows of `splits` partials, each bf16 row stored to all `n_outs` output buffers at
- *       row `row_offset` (the all-gather of the row slices done by the combine's stores). The ranks must barrier before reading.
+ *       f16 (f32 with f32_partials != 0) [world][S / world][H][128] and f32 [world][S / world * H]. Writes FMHA_MXFP8_PEER_PLAN_BYTES to
+ *       `plan_dev` (device memory, 128-byte aligned), to be passed as ext_ptr_peer_plan of a kvsplit launch with kvs_splits = 1 and with
+ *       FMHA_MXFP8_FLAG_F32_PARTIALS set exactly when the plan was built for f32 partials (nothing can check that at launch): that launch
+ *       stores row block x of its partial to slot [rank] of the receive buffers of GPU x * 128 / (S / world) (TMA tile stores and plain
+ *       stores to peer memory; ptr_ohat / ptr_lse are then not written). The ranks must barrier before combining. f16 is the format of the
+ *       reference's partials and half the bytes over NVLink; f32 keeps the partials exact to the kernel's accumulators.
+ *   combine_scatter: the combine over `rows` rows of `splits` partials (f16, or f32 with f32_partials != 0), each bf16 row stored to all
+ *       `n_outs` output buffers at row `row_offset` (the all-gather of the row slices done by the combine's stores). The ranks must barrier before reading.
  *   copy_async: cudaMemcpyAsync device to device (for hosts that hold raw pointers only).
  * Return 0, FMHA_MXFP8_E_ARG, or minus a cudaError_t.
  */
@@ -358,9 +360,10 @@ int fmha_mxfp8_peer_alloc(size_t bytes, void** dev_ptr, void* handle64);
 int fmha_mxfp8_peer_open(const void* handle64, void** dev_ptr);
 int fmha_mxfp8_peer_close(void* dev_ptr);
 int fmha_mxfp8_peer_free(void* dev_ptr);
-int fmha_mxfp8_peer_plan_build(uint32_t world, uint32_t rank, uint32_t H, uint32_t S, void* const* ohat_recv, void* const* lse_recv, void* plan_dev, void* stream);
-int fmha_mxfp8_combine_f32_scatter(const void* ohat, const void* lse, void* const* outs, uint32_t n_outs, uint64_t row_offset, uint32_t rows, uint32_t splits,
-                                   void* stream);
+int fmha_mxfp8_peer_plan_build(uint32_t world, uint32_t rank, uint32_t H, uint32_t S, int f32_partials, void* const* ohat_recv, void* const* lse_recv,
+                               void* plan_dev, void* stream);
+int fmha_mxfp8_combine_scatter(const void* ohat, int f32_partials, const void* lse, void* const* outs, uint32_t n_outs, uint64_t row_offset, uint32_t rows,
+                               uint32_t splits, void* stream);
 int fmha_mxfp8_copy_async(void* dst, const void* src, size_t bytes, void* stream);
 
 /*

@@ -181,10 +181,11 @@ def test_bounded_wait_gives_up_and_leaves_the_device_usable(oracle, abi):
     assert np.array_equal(attend(), before)
 
 
-def test_peer_store_routing_with_two_ranks_emulated_on_one_gpu(oracle, abi):
+@pytest.mark.parametrize("f32", [False, True], ids=["f16_partials", "f32_partials"])
+def test_peer_store_routing_with_two_ranks_emulated_on_one_gpu(oracle, abi, f32):
     """The key-range sharding whose split kernel stores its partial rows straight into the combining GPU's receive slots
     (fmha_mxfp8_peer_plan_build, ext_ptr_peer_plan) and whose combine stores its rows into every GPU's output
-    (fmha_mxfp8_combine_f32_scatter), with both "GPUs" being buffers of this one: rank r's launch covers key range r and is routed by
+    (fmha_mxfp8_combine_scatter), with both "GPUs" being buffers of this one: rank r's launch covers key range r and is routed by
     rank r's plan; then each rank combines its slice of the rows and scatters it into both outputs. Both outputs must equal, byte for byte,
     what the local-memory form (partials into ohat_all[r], one combine over all rows) gives, and pass the gate against the oracle."""
     import ctypes as C
@@ -207,17 +208,18 @@ def test_peer_store_routing_with_two_ranks_emulated_on_one_gpu(oracle, abi):
         return k_all[:, lo:hi].contiguous(), v_all[:, lo:hi].contiguous(), torch.from_numpy(ks_local).cuda()
 
     # the local-memory form
-    ohat_all = torch.empty(world, rows_total, 128, dtype=torch.float32, device="cuda")
+    pdt = torch.float32 if f32 else torch.float16
+    ohat_all = torch.empty(world, rows_total, 128, dtype=pdt, device="cuda")
     lse_all = torch.empty(world, rows_total, dtype=torch.float32, device="cuda")
     for r in range(world):
         kl, vl, ksl = local_inputs(r)
-        multi_gpu.local_partials(q, kl, vl, qs, ksl, vs, ohat_all[r], lse_all[r])
+        multi_gpu.local_partials(q, kl, vl, qs, ksl, vs, ohat_all[r], lse_all[r], f32_partials=f32)
     want = torch.empty(B, S, H, 128, dtype=torch.bfloat16, device="cuda")
     multi_gpu.combine_gathered(ohat_all, lse_all, want, world)
     torch.cuda.synchronize()
 
-    # the peer-store form: per "GPU" a receive area [world][n][128] f32 + [world][n] f32 and a whole output, all on this device
-    recv = [torch.full((world, n, 128), float("nan"), dtype=torch.float32, device="cuda") for _ in range(world)]
+    # the peer-store form: per "GPU" a receive area [world][n][128] (f16 or f32) + [world][n] f32 and a whole output, all on this device
+    recv = [torch.full((world, n, 128), float("nan"), dtype=pdt, device="cuda") for _ in range(world)]
     lrecv = [torch.full((world, n), float("nan"), dtype=torch.float32, device="cuda") for _ in range(world)]
     outs = [torch.full((B, S, H, 128), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
     dummy_o, dummy_l = torch.empty(4, dtype=torch.float32, device="cuda"), torch.empty(4, dtype=torch.float32, device="cuda")
@@ -226,20 +228,20 @@ def test_peer_store_routing_with_two_ranks_emulated_on_one_gpu(oracle, abi):
     for r in range(world):
         plan = torch.zeros(abi.PEER_PLAN_BYTES + 128, dtype=torch.uint8, device="cuda")
         plan_ptr = (plan.data_ptr() + 127) // 128 * 128
-        assert lib.fmha_mxfp8_peer_plan_build(world, r, H, S, ohat_ptrs, lse_ptrs, C.c_void_p(plan_ptr), None) == 0
+        assert lib.fmha_mxfp8_peer_plan_build(world, r, H, S, int(f32), ohat_ptrs, lse_ptrs, C.c_void_p(plan_ptr), None) == 0
         kl, vl, ksl = local_inputs(r)
-        multi_gpu.local_partials(q, kl, vl, qs, ksl, vs, dummy_o, dummy_l, peer_plan=plan_ptr)
+        multi_gpu.local_partials(q, kl, vl, qs, ksl, vs, dummy_o, dummy_l, peer_plan=plan_ptr, f32_partials=f32)
         torch.cuda.synchronize()
     out_ptrs = (C.c_void_p * world)(*[t.data_ptr() for t in outs])
     for r in range(world):
         assert torch.isfinite(recv[r]).all() and torch.isfinite(lrecv[r]).all(), "every receive slot must have been stored to"
         # the slots hold exactly the row slices of the local-memory partials
         assert torch.equal(recv[r], ohat_all[:, r * n:(r + 1) * n]) and torch.equal(lrecv[r], lse_all[:, r * n:(r + 1) * n])
-        assert lib.fmha_mxfp8_combine_f32_scatter(recv[r].data_ptr(), lrecv[r].data_ptr(), out_ptrs, world, r * n, n, world, None) == 0
+        assert lib.fmha_mxfp8_combine_scatter(recv[r].data_ptr(), int(f32), lrecv[r].data_ptr(), out_ptrs, world, r * n, n, world, None) == 0
     torch.cuda.synchronize()
     for o in outs:
         assert torch.equal(o.view(torch.int16), want.view(torch.int16))
     _gate_rows(oracle, inp, _bf16_bytes(outs[1]), oracle.spread_rows(S), "peer-store routing, two ranks on one GPU")
-    # refusals: rows that do not divide into whole 128-row blocks per rank, a plan without f32 partials
-    assert lib.fmha_mxfp8_peer_plan_build(world, 0, H, 1000, ohat_ptrs, lse_ptrs, C.c_void_p(plan_ptr), None) == 6
-    assert lib.fmha_mxfp8_peer_plan_build(1, 0, H, S, ohat_ptrs, lse_ptrs, C.c_void_p(plan_ptr), None) == 6
+    # refusals: rows that do not divide into whole 128-row blocks per rank, a plan for one GPU
+    assert lib.fmha_mxfp8_peer_plan_build(world, 0, H, 1000, int(f32), ohat_ptrs, lse_ptrs, C.c_void_p(plan_ptr), None) == 6
+    assert lib.fmha_mxfp8_peer_plan_build(1, 0, H, S, int(f32), ohat_ptrs, lse_ptrs, C.c_void_p(plan_ptr), None) == 6
