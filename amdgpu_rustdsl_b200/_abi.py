@@ -140,6 +140,8 @@ def load():
     lib.fmha_mxfp8_peer_plan_build.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_int, vpp, vpp, C.c_void_p, C.c_void_p]
     lib.fmha_mxfp8_combine_scatter.restype = C.c_int
     lib.fmha_mxfp8_combine_scatter.argtypes = [C.c_void_p, C.c_int, C.c_void_p, vpp, C.c_uint32, C.c_uint64, C.c_uint32, C.c_uint32, C.c_void_p]
+    lib.fmha_mxfp8_peer_barrier.restype = C.c_int
+    lib.fmha_mxfp8_peer_barrier.argtypes = [vpp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]
     lib.fmha_mxfp8_copy_async.restype = C.c_int
     lib.fmha_mxfp8_copy_async.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
     lib.fmha_mxfp8_quantize_qk.restype = C.c_int
@@ -162,7 +164,7 @@ EXPORTS = (
     "fmha_mxfp8_kernel_name", "fmha_mxfp8_kernarg_size", "fmha_mxfp8_workgroup_size", "fmha_mxfp8_validate", "fmha_mxfp8_grid",
     "fmha_mxfp8_launch", "fmha_mxfp8_dispatch", "fmha_mxfp8_auto", "fmha_mxfp8_device_status", "fmha_mxfp8_trace_attach",
     "fmha_mxfp8_mma_issue_ceiling", "fmha_mxfp8_selftest_bounded_wait", "fmha_mxfp8_kvsplit_static_scratch", "fmha_mxfp8_quantize_qk", "fmha_mxfp8_quantize_v", "fmha_mxfp8_combine_f32", "fmha_mxfp8_peer_alloc", "fmha_mxfp8_peer_open", "fmha_mxfp8_peer_close", "fmha_mxfp8_peer_free",
-    "fmha_mxfp8_peer_plan_build", "fmha_mxfp8_combine_scatter", "fmha_mxfp8_copy_async",
+    "fmha_mxfp8_peer_plan_build", "fmha_mxfp8_combine_scatter", "fmha_mxfp8_copy_async", "fmha_mxfp8_peer_barrier",
 )
 
 

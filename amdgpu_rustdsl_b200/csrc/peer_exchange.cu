@@ -11,13 +11,75 @@
 #include "../../include/fmha_mxfp8_abi.h"
 #include "kernels.h"
 
+#include <atomic>
 #include <cstring>
 
 namespace b200mx {
 int encode_partial_map(CUtensorMap* m, void* base, uint64_t seq, uint64_t heads, uint64_t batches, uint64_t splits, bool f32);   // host_api.cu
 }
 
+namespace b200mx {
+namespace {
+
+struct FlagArrays {
+    uint32_t* a[FMHA_MXFP8_PEER_MAX_GPUS];   // a[r]: rank r's arrival flags [world], as mapped into this process
+};
+
+// The ranks of a node line up on their streams: thread t of the one warp tells rank t that this rank has arrived (a release store at
+// system scope into rank t's flag array, behind a system-scope fence: what this GPU's earlier kernels stored to its peers is performed
+// before the flag) and waits, with a clock budget, until rank t's arrival shows in this rank's own array. The arrival numbers only grow
+// (one per barrier of a plan), so a peer that is already one barrier further does no harm. Each GPU runs its own launch of this kernel;
+// the launches wait for launches on *other* GPUs, never for one another on the same GPU.
+__global__ void peer_barrier_kernel(FlagArrays f, uint32_t world, uint32_t rank, uint32_t arrival, long long budget_cycles, uint32_t* status) {
+    const uint32_t t = threadIdx.x;
+    if (t >= world) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f.a[t] + rank), "r"(arrival) : "memory");
+    const uint32_t* mine = f.a[rank] + t;
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if (static_cast<int32_t>(v - arrival) >= 0) break;
+        if (clock64() - t0 > budget_cycles) {
+            atomicOr(status, 2u);   // bit 1: a barrier between GPUs ran out of time
+            break;
+        }
+    }
+    __threadfence_system();
+}
+
+}  // namespace
+}  // namespace b200mx
+
 extern "C" {
+
+int fmha_mxfp8_peer_barrier(void* const* flag_arrays, uint32_t world, uint32_t rank, uint32_t arrival, uint32_t budget_us, void* status_dev, void* stream) {
+    if (!flag_arrays || world < 1 || world > FMHA_MXFP8_PEER_MAX_GPUS || rank >= world || arrival == 0 || budget_us == 0) return FMHA_MXFP8_E_ARG;
+    b200mx::FlagArrays f;
+    std::memset(&f, 0, sizeof f);
+    for (uint32_t r = 0; r < world; ++r) {
+        if (!flag_arrays[r] || (reinterpret_cast<uintptr_t>(flag_arrays[r]) & 3u)) return FMHA_MXFP8_E_ARG;
+        f.a[r] = static_cast<uint32_t*>(flag_arrays[r]);
+    }
+    uint32_t* status = status_dev ? static_cast<uint32_t*>(status_dev) : b200mx::device_status_word();
+    if (!status) return -static_cast<int>(cudaErrorInvalidSymbol);
+    // the budget in SM clocks at the GPU's maximum clock, asked for once per device (the attribute query takes milliseconds)
+    static std::atomic<int> khz_of[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return -static_cast<int>(e);
+    int khz = (dev >= 0 && dev < 64) ? khz_of[dev].load(std::memory_order_relaxed) : 0;
+    if (khz == 0) {
+        e = cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev);
+        if (e != cudaSuccess || khz <= 0) khz = 2000000;
+        if (dev >= 0 && dev < 64) khz_of[dev].store(khz, std::memory_order_relaxed);
+    }
+    const long long budget_cycles = static_cast<long long>(budget_us) * khz / 1000;
+    b200mx::peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, world, rank, arrival, budget_cycles, status);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
 
 int fmha_mxfp8_peer_alloc(size_t bytes, void** dev_ptr, void* handle64) {
     if (!dev_ptr || !handle64 || bytes == 0) return FMHA_MXFP8_E_ARG;

@@ -174,7 +174,8 @@ class PeerBuffers:
         self.f32_partials = f32_partials
         self.off_lse = al(world * n * D * (4 if f32_partials else 2))
         self.off_out = self.off_lse + al(world * n * 4)
-        self.bytes = self.off_out + al(rows_total * D * 2)
+        self.off_flags = self.off_out + al(rows_total * D * 2)   # [world] uint32 arrival flags of the barrier between the GPUs (zero at first)
+        self.bytes = self.off_flags + 256
         self.own = C.c_void_p()
         handle = (C.c_ubyte * _abi.PEER_HANDLE_BYTES)()
         self.ptr, self.opened, self.error = [None] * world, [], None
@@ -238,12 +239,16 @@ class KvShardedPlan:
     transport "nccl": split kernel -> all-to-all of the partial row slices -> combine of the own slice -> all-gather of the bf16 slices
     (or, when the rows do not divide, an all-gather of the whole partials)."""
 
-    def __init__(self, rows_total: int, world: int, device, group=None, transport: str = "auto", B: int = 1, S: int = 0, H: int = 0, partials: str = "f32"):
+    def __init__(self, rows_total: int, world: int, device, group=None, transport: str = "auto", B: int = 1, S: int = 0, H: int = 0, partials: str = "f32",
+                 barrier: str = "flags"):
         import torch
         if partials not in ("f16", "f32"):
             raise ValueError("partials: 'f16' or 'f32'")
         self.rows_total, self.world, self.device, self.group = rows_total, world, device, group
         self.f32_partials = partials == "f32"   # of the peer transport; the NCCL exchange moves f32
+        if barrier not in ("flags", "nccl"):
+            raise ValueError("barrier: 'flags' (arrival flags in the peer buffers) or 'nccl' (an all-reduce of one float)")
+        self.flag_barrier, self.arrivals = barrier == "flags", 0
         self.transport = "none" if world == 1 else "nccl"
         self.peer = None
         if world > 1 and transport in ("auto", "peer"):
@@ -278,6 +283,7 @@ class KvShardedPlan:
                 if rc:
                     raise RuntimeError(f"fmha_mxfp8_peer_plan_build failed with code {rc}")
                 self.outs = (C.c_void_p * self.world)(*[pb.ptr[r] + pb.off_out for r in range(self.world)])
+                self.flag_arrays = (C.c_void_p * self.world)(*[pb.ptr[r] + pb.off_flags for r in range(self.world)])
                 self.flag = torch.zeros(1, dtype=torch.float32, device=self.device)
             except Exception as e:   # noqa: BLE001
                 good, err = False, repr(e)
@@ -295,18 +301,44 @@ class KvShardedPlan:
             return "one rank: split kernel over all keys + combine (splits = 1), no exchange"
         if self.transport == "peer":
             return (f"key-range shards: the split kernel stores its {'f32' if self.f32_partials else 'f16'} partial row blocks into the combining GPU's memory over NVLink as they leave tensor memory "
-                    "-> barrier -> every GPU's combine stores its bf16 row slice into every GPU's output -> barrier (no collective moves data)")
+                    "-> barrier -> every GPU's combine stores its bf16 row slice into every GPU's output -> barrier (no collective moves data; barrier = "
+                    + ("arrival flags in peer memory)" if self.flag_barrier else "NCCL all-reduce of one float)"))
         if self.sliced:
             return "key-range shards: split kernel -> NCCL all-to-all of the f32 partial row slices and their log-sum-exps -> combine of the own slice -> NCCL all-gather of the bf16 slices"
         return "key-range shards: split kernel -> NCCL all-gather of the f32 partials -> combine of all rows"
 
+    def output(self):
+        """Peer transport: this rank's whole bf16 output [rows_total, 128] where the combines of all ranks store it (a view of the peer buffer, no
+        copy). Valid after `forward(..., out=None)` until the next `forward`; gone after `close`."""
+        import torch
+        if self.transport != "peer":
+            raise ValueError("output(): only the peer transport keeps the output in a buffer of its own")
+
+        class _View:   # the CUDA array interface of the output region; bf16 has no typestr of its own: 16-bit words, viewed as bf16 below
+            __cuda_array_interface__ = {"shape": (self.rows_total, D), "typestr": "<i2", "data": (self.peer.own.value + self.peer.off_out, False), "version": 3,
+                                        "strides": None}
+
+        return torch.as_tensor(_View(), device=self.device).view(torch.bfloat16)
+
     def _barrier(self):
-        """The ranks line up on the stream: an all-reduce of one float (what follows on the stream starts after every rank got here)."""
+        """The ranks line up on the stream (what follows on the stream starts after every rank got here): arrival flags in the peer buffers,
+        written and polled by a one-warp kernel per GPU (`fmha_mxfp8_peer_barrier`, bounded wait of 2 s), or an all-reduce of one float."""
+        if self.flag_barrier:
+            import ctypes as C
+            import torch
+            self.arrivals += 1
+            with torch.cuda.device(self.device):
+                rc = self.peer.lib.fmha_mxfp8_peer_barrier(self.flag_arrays, self.world, self.peer.rank, self.arrivals, 2_000_000, None,
+                                                           C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+            if rc:
+                raise RuntimeError(f"fmha_mxfp8_peer_barrier failed with code {rc}")
+            return
         import torch.distributed as dist
         dist.all_reduce(self.flag, group=self.group)
 
     def stages(self, q, k_local, v_local, q_scale, k_scale_local, v_scale, out):
-        """The step as a list of (name, callable) in stream order."""
+        """The step as a list of (name, callable) in stream order. Peer transport: `out` may be None, the result is then `output()` and
+        the copy into a tensor of the caller's is left out."""
         ws, world = self.ws, self.world
         if self.transport == "peer":
             import ctypes as C
@@ -327,9 +359,14 @@ class KvShardedPlan:
                 if rc:
                     raise RuntimeError(f"fmha_mxfp8_copy_async failed with code {rc}")
 
-            return [("split_kernel_storing_to_peers", lambda: local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ws["ohat"], ws["lse"], check=False,
-                                                                            peer_plan=self.plan_ptr, f32_partials=self.f32_partials)),
-                    ("barrier", self._barrier), ("combine_storing_to_peers", combine), ("barrier_2", self._barrier), ("copy_out", take_output)]
+            st = [("split_kernel_storing_to_peers", lambda: local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ws["ohat"], ws["lse"], check=False,
+                                                                          peer_plan=self.plan_ptr, f32_partials=self.f32_partials)),
+                  ("barrier", self._barrier), ("combine_storing_to_peers", combine), ("barrier_2", self._barrier)]
+            if out is not None:
+                st.append(("copy_out", take_output))
+            return st
+        if out is None:
+            raise ValueError("only the peer transport runs without an output tensor")
         st = [("split_kernel", lambda: local_partials(q, k_local, v_local, q_scale, k_scale_local, v_scale, ws["ohat"], ws["lse"], check=False))]
         if world == 1:
             st.append(("combine", lambda: combine_gathered(ws["ohat"].view(1, self.rows_total, D), ws["lse"].view(1, self.rows_total), out, 1, check=False)))

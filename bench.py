@@ -406,11 +406,19 @@ def make_step(R, W):
     Hl = W["local"][0]
     rows_total = B * S * Hl
     if wl == "c5":
-        W["plan"] = multi_gpu.KvShardedPlan(rows_total, R.world, R.dev, transport=R.args.c5_transport, B=B, S=S, H=Hl, partials=R.args.c5_partials)
+        W["plan"] = multi_gpu.KvShardedPlan(rows_total, R.world, R.dev, transport=R.args.c5_transport, B=B, S=S, H=Hl, partials=R.args.c5_partials, barrier=R.args.c5_barrier)
+
+        if W["plan"].transport == "peer":
+            # the result stays where every rank's combine stores it (the plan's own output buffer): no copy into another tensor
+            W["out_view"] = W["plan"].output().view(B, S, Hl, 128)
 
     def step(s):
         if wl == "c5":
-            W["plan"].forward(s["q"], s["k"], s["v"], s["qs"], s["ks"], s["vs"], s["out"])
+            if "out_view" in W:
+                s["out"] = W["out_view"]
+                W["plan"].forward(s["q"], s["k"], s["v"], s["qs"], s["ks"], s["vs"], None)
+            else:
+                W["plan"].forward(s["q"], s["k"], s["v"], s["qs"], s["ks"], s["vs"], s["out"])
             W["ran"] = ("kvshard", R.world)
         else:
             W["ran"] = fmha_fwd_mxfp8(s["q"], s["k"], s["v"], s["qs"], s["ks"], s["vs"], s["out"], path=W["path"], splits=W["splits"])
@@ -574,7 +582,7 @@ def run_sharded(R, wl):
            "clocks": clocks, "parallelism": ("heads dealt out over the ranks, no collective" if wl == "c4" else W["plan"].describe() if wl == "c5"
                                              else f"one GPU: {W['ran'][0]} with {W['ran'][1]} splits (f16 partials) + combine")}
     if wl == "c5":
-        stages = W["plan"].timed_stages(s["q"], s["k"], s["v"], s["qs"], s["ks"], s["vs"], s["out"], reps=5)
+        stages = W["plan"].timed_stages(s["q"], s["k"], s["v"], s["qs"], s["ks"], s["vs"], None if "out_view" in W else s["out"], reps=5)
         res["stages_ms"] = {k: R.max_over_ranks(v) for k, v in stages.items()}
     step(s)
     torch.cuda.synchronize()
@@ -592,6 +600,8 @@ def run_sharded(R, wl):
         fms = statistics.median(fwin) / per_window
         res["fused_merge"] = {"ms_per_step": fms, "value": flops(B, H, S, SK) / (fms * 1e-3) / 1e12, "same_bytes_as_two_kernels": same, "windows_ms": fwin}
     if wl == "c5":
+        W.pop("out_view", None)
+        s.pop("out", None)
         W["plan"].close()
     W["sets"] = None
     del s
@@ -613,6 +623,7 @@ def main():
     ap.add_argument("--no-sharded", action="store_true", help="skip the two sharded configurations of the `sharded` object")
     ap.add_argument("--c5-transport", default="auto", choices=["auto", "peer", "nccl"], help="how the key-range shards' partials reach the combining GPU")
     ap.add_argument("--c5-partials", default="f32", choices=["f16", "f32"], help="format of the partial rows the key-range shards store into the combining GPU (peer transport)")
+    ap.add_argument("--c5-barrier", default="flags", choices=["flags", "nccl"], help="how the key-range shards' ranks line up between the kernels (peer transport)")
     ap.add_argument("--sets", type=int, default=0, help="number of rotating input sets (0 = enough to exceed L2)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -350,6 +350,11 @@ int fmha_mxfp8_combine_f32(const void* ohat, const void* lse, void* out, uint32_
  *       reference's partials and half the bytes over NVLink; f32 keeps the partials exact to the kernel's accumulators.
  *   combine_scatter: the combine over `rows` rows of `splits` partials (f16, or f32 with f32_partials != 0), each bf16 row stored to all
  *       `n_outs` output buffers at row `row_offset` (the all-gather of the row slices done by the combine's stores). The ranks must barrier before reading.
+ *   peer_barrier: the ranks line up on their streams without a collective library: flag_arrays[r] is rank r's array of `world` uint32
+ *       arrival flags (in a peer buffer, zero at first) as mapped into this process; one warp tells every rank that this rank has arrived for
+ *       the `arrival`-th time (1, 2, ... per plan; release stores at system scope behind a system-scope fence, so what this GPU's earlier kernels
+ *       stored to its peers is performed first) and waits, for at most budget_us, until every rank's arrival shows in the own array. A wait
+ *       that runs out sets bit 1 of *status_dev (NULL: the library's device status word) and the kernel ends normally.
  *   copy_async: cudaMemcpyAsync device to device (for hosts that hold raw pointers only).
  * Return 0, FMHA_MXFP8_E_ARG, or minus a cudaError_t.
  */
@@ -364,6 +369,7 @@ int fmha_mxfp8_peer_plan_build(uint32_t world, uint32_t rank, uint32_t H, uint32
                                void* plan_dev, void* stream);
 int fmha_mxfp8_combine_scatter(const void* ohat, int f32_partials, const void* lse, void* const* outs, uint32_t n_outs, uint64_t row_offset, uint32_t rows,
                                uint32_t splits, void* stream);
+int fmha_mxfp8_peer_barrier(void* const* flag_arrays, uint32_t world, uint32_t rank, uint32_t arrival, uint32_t budget_us, void* status_dev, void* stream);
 int fmha_mxfp8_copy_async(void* dst, const void* src, size_t bytes, void* stream);
 
 /*

@@ -245,3 +245,37 @@ def test_peer_store_routing_with_two_ranks_emulated_on_one_gpu(oracle, abi, f32)
     # refusals: rows that do not divide into whole 128-row blocks per rank, a plan for one GPU
     assert lib.fmha_mxfp8_peer_plan_build(world, 0, H, 1000, int(f32), ohat_ptrs, lse_ptrs, C.c_void_p(plan_ptr), None) == 6
     assert lib.fmha_mxfp8_peer_plan_build(1, 0, H, S, int(f32), ohat_ptrs, lse_ptrs, C.c_void_p(plan_ptr), None) == 6
+
+
+def test_barrier_between_gpus_on_one_gpu(abi):
+    """fmha_mxfp8_peer_barrier with the other rank played by the host: its arrival flag is already in this rank's array when the kernel is
+    launched (nothing waits for another launch), so the kernel ends at once, having told both ranks of its own arrival. And the bounded form:
+    an arrival that never comes makes the wait run out after its budget, sets bit 1 of the status word it was given and ends normally."""
+    import ctypes as C
+    import time
+    lib = abi.load()
+    mine = torch.zeros(2, dtype=torch.int32, device="cuda")     # this rank's (rank 0) flag array
+    theirs = torch.zeros(2, dtype=torch.int32, device="cuda")   # rank 1's
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    arrays = (C.c_void_p * 2)(mine.data_ptr(), theirs.data_ptr())
+    mine[1] = 1   # rank 1 has arrived for the first time
+    torch.cuda.synchronize()
+    assert lib.fmha_mxfp8_peer_barrier(arrays, 2, 0, 1, 1_000_000, C.c_void_p(status.data_ptr()), None) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and mine.tolist() == [1, 1] and theirs.tolist() == [1, 0]
+    # a peer that is already one barrier further does no harm
+    mine[1] = 3
+    torch.cuda.synchronize()
+    assert lib.fmha_mxfp8_peer_barrier(arrays, 2, 0, 2, 1_000_000, C.c_void_p(status.data_ptr()), None) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and theirs.tolist() == [2, 0]
+    # the arrival that never comes: 1 ms budget
+    t0 = time.perf_counter()
+    assert lib.fmha_mxfp8_peer_barrier(arrays, 2, 0, 4, 1000, C.c_void_p(status.data_ptr()), None) == 0
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0 and int(status.item()) == 2 and theirs.tolist() == [4, 0]
+    # refusals
+    assert lib.fmha_mxfp8_peer_barrier(arrays, 2, 2, 1, 1000, None, None) == 6
+    assert lib.fmha_mxfp8_peer_barrier(arrays, 2, 0, 0, 1000, None, None) == 6
+    from amdgpu_rustdsl_b200 import device_status
+    assert device_status() == 0
