@@ -4,4 +4,4 @@
 include/fmha_mxfp8_abi.h. The CUDA library is built in-tree (csrc/Makefile); there is no other backend.
 """
 from ._abi import ContractError  # noqa: F401
-from .ops import Q_PRESCALE, device_status, fmha_fwd_mxfp8, quantize_qk, quantize_v, select_path  # noqa: F401
+from .ops import Q_PRESCALE, device_status, fmha_fwd_mxfp8, quantize_qk, quantize_v, reset_workspaces, select_path  # noqa: F401

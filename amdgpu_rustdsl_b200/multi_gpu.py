@@ -240,7 +240,7 @@ class KvShardedPlan:
     (or, when the rows do not divide, an all-gather of the whole partials)."""
 
     def __init__(self, rows_total: int, world: int, device, group=None, transport: str = "auto", B: int = 1, S: int = 0, H: int = 0, partials: str = "f32",
-                 barrier: str = "flags"):
+                 barrier: str = "flags", barrier_timeout_s: float = 30.0):
         import torch
         if partials not in ("f16", "f32"):
             raise ValueError("partials: 'f16' or 'f32'")
@@ -249,6 +249,9 @@ class KvShardedPlan:
         if barrier not in ("flags", "nccl"):
             raise ValueError("barrier: 'flags' (arrival flags in the peer buffers) or 'nccl' (an all-reduce of one float)")
         self.flag_barrier, self.arrivals = barrier == "flags", 0
+        # how long a rank waits for the others at a flag barrier before it gives up (sets bit 1 of the device status word and goes on): ranks
+        # may reach a step seconds apart (data loading), a rank that is gone never arrives
+        self.barrier_budget_us = int(min(max(barrier_timeout_s, 0.001), 4000.0) * 1e6)
         self.transport = "none" if world == 1 else "nccl"
         self.peer = None
         if world > 1 and transport in ("auto", "peer"):
@@ -322,13 +325,13 @@ class KvShardedPlan:
 
     def _barrier(self):
         """The ranks line up on the stream (what follows on the stream starts after every rank got here): arrival flags in the peer buffers,
-        written and polled by a one-warp kernel per GPU (`fmha_mxfp8_peer_barrier`, bounded wait of 2 s), or an all-reduce of one float."""
+        written and polled by a one-warp kernel per GPU (`fmha_mxfp8_peer_barrier`, bounded wait of `barrier_timeout_s`), or an all-reduce of one float."""
         if self.flag_barrier:
             import ctypes as C
             import torch
             self.arrivals += 1
             with torch.cuda.device(self.device):
-                rc = self.peer.lib.fmha_mxfp8_peer_barrier(self.flag_arrays, self.world, self.peer.rank, self.arrivals, 2_000_000, None,
+                rc = self.peer.lib.fmha_mxfp8_peer_barrier(self.flag_arrays, self.world, self.peer.rank, self.arrivals, self.barrier_budget_us, None,
                                                            C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
             if rc:
                 raise RuntimeError(f"fmha_mxfp8_peer_barrier failed with code {rc}")
