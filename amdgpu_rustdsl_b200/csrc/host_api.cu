@@ -260,21 +260,53 @@ int launch_attention_kernel(int kernel, const void* args, const uint32_t grid[3]
                 return FMHA_MXFP8_E_ARG;
         }
     }
-    CUtensorMap tq, tk, tv;
-    int r = make_tile_map(&tq, a->ptr_q, p.S, p.H, B, a->s_Hs, a->s_Seqs, a->s_Bs, 128u);
-    if (r) return r;
-    r = make_tile_map(&tk, a->ptr_k, p.SK, p.HK, B, a->s_k_Hs, a->s_k_Seqs, a->s_k_Bs, b200mx::kKeysPerTile);
-    if (r) return r;
-    r = make_tile_map(&tv, a->ptr_v, p.SK, p.HK, B, a->s_v_Hs, a->s_v_Seqs, a->s_v_Bs, b200mx::kKeysPerTile);
-    if (r) return r;
-    CUtensorMap to;   // the output of the kernel's TMA stores: bf16 O, or the split kernel's f32 partials
-    if (!split) {
-        r = make_out_map(&to, a->ptr_o, p.S, p.H, B, a->s_o_Hs, a->s_o_Seqs, a->s_o_Bs);
-    } else {
-        if (static_cast<uint64_t>(p.rows_total) != static_cast<uint64_t>(B) * p.S * p.H) return FMHA_MXFP8_E_KA_IS;
-        r = make_partial_map(&to, p.ohat, p.S, p.H, B, p.splits, (p.flags & FMHA_MXFP8_FLAG_F32_PARTIALS) != 0u);
+    if (split && static_cast<uint64_t>(p.rows_total) != static_cast<uint64_t>(B) * p.S * p.H) return FMHA_MXFP8_E_KA_IS;
+    // The four tensor maps depend on nothing but the argument block (pointers, extents, strides, flags): a call with the bytes of an
+    // earlier one reuses its maps instead of encoding them again (four driver calls; a framework calls a layer with the same buffers
+    // step after step). A few entries, replaced in turn; the lock is held for two short copies.
+    struct MapSet {
+        bool valid;
+        int kernel;
+        uint32_t grid_z;
+        unsigned char args[sizeof(fmha_mxfp8_attn_args) > sizeof(fmha_mxfp8_kvsplit_args) ? sizeof(fmha_mxfp8_attn_args) : sizeof(fmha_mxfp8_kvsplit_args)];
+        CUtensorMap tq, tk, tv, to;
+    };
+    constexpr int kMapSets = 8;
+    static MapSet sets[kMapSets];
+    static int next_set = 0;
+    static std::mutex sets_lock;
+    const size_t arg_bytes = split ? sizeof(fmha_mxfp8_kvsplit_args) : sizeof(fmha_mxfp8_attn_args);
+    CUtensorMap tq, tk, tv, to;   // to: the output of the kernel's TMA stores: bf16 O, or the split kernel's partials
+    bool have = false;
+    {
+        std::lock_guard<std::mutex> g(sets_lock);
+        for (int i = 0; i < kMapSets && !have; ++i) {
+            const MapSet& m = sets[i];
+            if (m.valid && m.kernel == kernel && m.grid_z == grid[2] && std::memcmp(m.args, args, arg_bytes) == 0) {
+                tq = m.tq; tk = m.tk; tv = m.tv; to = m.to;
+                have = true;
+            }
+        }
     }
-    if (r) return r;
+    if (!have) {
+        int r = make_tile_map(&tq, a->ptr_q, p.S, p.H, B, a->s_Hs, a->s_Seqs, a->s_Bs, 128u);
+        if (r) return r;
+        r = make_tile_map(&tk, a->ptr_k, p.SK, p.HK, B, a->s_k_Hs, a->s_k_Seqs, a->s_k_Bs, b200mx::kKeysPerTile);
+        if (r) return r;
+        r = make_tile_map(&tv, a->ptr_v, p.SK, p.HK, B, a->s_v_Hs, a->s_v_Seqs, a->s_v_Bs, b200mx::kKeysPerTile);
+        if (r) return r;
+        if (!split) r = make_out_map(&to, a->ptr_o, p.S, p.H, B, a->s_o_Hs, a->s_o_Seqs, a->s_o_Bs);
+        else r = make_partial_map(&to, p.ohat, p.S, p.H, B, p.splits, (p.flags & FMHA_MXFP8_FLAG_F32_PARTIALS) != 0u);
+        if (r) return r;
+        std::lock_guard<std::mutex> g(sets_lock);
+        MapSet& m = sets[next_set];
+        next_set = (next_set + 1) % kMapSets;
+        m.valid = true;
+        m.kernel = kernel;
+        m.grid_z = grid[2];
+        std::memcpy(m.args, args, arg_bytes);
+        m.tq = tq; m.tk = tk; m.tv = tv; m.to = to;
+    }
     const cudaError_t e = b200mx::launch_attention(tq, tk, tv, to, p, B, split, kernel == FMHA_MXFP8_T128 ? 128u : 256u, stream);
     return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }

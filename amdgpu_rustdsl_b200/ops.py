@@ -33,6 +33,13 @@ def _ws_key(name, device, stream):
     return (name, device.index if device.index is not None else -1, int(stream))
 
 
+# Calls already made, by their tensors' addresses, shapes and options: the kernels, filled argument blocks and grids they came to. A call
+# with the same key (a layer run step after step on the same buffers) replays them without building and validating the blocks again
+# (20 us of host time per call without, 8 with; the smallest shapes are host-bound). Entries die with the workspaces they point into.
+_calls = {}
+_ws_generation = 0
+
+
 def _ws(name, nbytes, device, stream, zero=False):
     """Grow-only per-device, per-stream workspace for the KV-split partials (the reference's ``_ws``, ops.py:72-85, which frees the old
     buffer with a synchronising ``hipFree``). Here the old buffer goes back to torch's caching allocator, which only orders its reuse
@@ -41,6 +48,8 @@ def _ws(name, nbytes, device, stream, zero=False):
     key = _ws_key(name, device, stream)
     buf = _workspace.get(key)
     if buf is None or buf.numel() < nbytes:
+        global _ws_generation
+        _ws_generation += 1   # remembered calls hold the old buffers' addresses
         if buf is not None:
             (torch.cuda.ExternalStream(int(stream), device=device) if stream else torch.cuda.default_stream(device)).synchronize()
         if zero:   # cleared once; its users leave it cleared. The fill runs on torch's current stream: it must be done before `stream` uses it
@@ -55,7 +64,9 @@ def _nbytes(t):
     return t.numel() * t.element_size()
 
 
-def _check_launch(lib, kernel, args, sizes, grid, syms, stream, check):
+def _check_launch(lib, kernel, args, sizes, grid, syms, stream, check, record=None):
+    if record is not None:
+        record.append((kernel, args, grid))
     if check:
         err = C.create_string_buffer(256)
         rc = lib.fmha_mxfp8_validate(kernel, C.byref(args), C.byref(sizes), grid, C.byref(syms) if syms is not None else None, err, 256)
@@ -102,6 +113,28 @@ def fmha_fwd_mxfp8(q, k, v, q_scale, k_scale, v_scale, out, *, path="auto", spli
     """
     import torch
     lib = _abi.load()
+    dev = q.device
+    if not q.is_cuda:
+        raise ValueError("fmha_fwd_mxfp8: q must be a contiguous CUDA tensor")
+    raw_stream = stream if stream is not None else _raw_stream(torch, dev)
+    key = (raw_stream, q.data_ptr(), k.data_ptr(), v.data_ptr(), q_scale.data_ptr(), k_scale.data_ptr(), v_scale.data_ptr(), out.data_ptr(), q.shape, k.shape, v.shape,
+           out.shape, out.dtype, q_scale.numel(), k_scale.numel(), path, splits, flags, causal, fused_combine, check,
+           None if v_blockscale is None else v_blockscale.data_ptr(), None if lse is None else lse.data_ptr(), dev.index)
+    hit = _calls.get(key)
+    if hit is not None and hit[0] == _ws_generation and q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and out.is_contiguous():
+        raw = raw_stream
+        if torch.cuda.current_device() == (dev.index or 0):
+            for kernel, args, grid in hit[1]:
+                rc = lib.fmha_mxfp8_launch(kernel, C.byref(args), grid, C.c_void_p(raw))
+                if rc:
+                    raise RuntimeError(f"fmha_mxfp8_launch({lib.fmha_mxfp8_kernel_name(kernel).decode()}) failed with code {rc}")
+        else:
+            with torch.cuda.device(dev):
+                for kernel, args, grid in hit[1]:
+                    rc = lib.fmha_mxfp8_launch(kernel, C.byref(args), grid, C.c_void_p(raw))
+                    if rc:
+                        raise RuntimeError(f"fmha_mxfp8_launch({lib.fmha_mxfp8_kernel_name(kernel).decode()}) failed with code {rc}")
+        return hit[2]
     B, S, H, d = q.shape
     _, SK, HK, dk = k.shape
     if d != D or dk != D or HK == 0 or H % HK or (H // HK) & (H // HK - 1) or H // HK > 16:
@@ -125,21 +158,31 @@ def fmha_fwd_mxfp8(q, k, v, q_scale, k_scale, v_scale, out, *, path="auto", spli
             path, splits = "vs128", 0
     elif path == "kvsplit":
         splits = splits or 4
-    if stream is None:
-        stream = torch.cuda.current_stream(q.device).cuda_stream
+    stream = raw_stream
     # the library works on the current device (status word, SM count, kernel attributes, stream 0): make it the tensors' device
+    record = []
     with torch.cuda.device(q.device):
-        return _launch_path(lib, q, k, v, q_scale, k_scale, v_scale, out, path, splits, stream, check, flags, v_blockscale, lse, B, S, H, SK, HK)
+        ran = _launch_path(lib, q, k, v, q_scale, k_scale, v_scale, out, path, splits, stream, check, flags, v_blockscale, lse, B, S, H, SK, HK, record)
+    if len(_calls) >= 256:
+        _calls.clear()
+    _calls[key] = (_ws_generation, record, ran)   # the key holds the stream: the split path's workspaces belong to one
+    return ran
 
 
-def _launch_path(lib, q, k, v, q_scale, k_scale, v_scale, out, path, splits, stream, check, flags, v_blockscale, lse, B, S, H, SK, HK):
+def _raw_stream(torch, dev):
+    """The handle of torch's current stream on `dev` (what ``torch.cuda.current_stream(dev).cuda_stream`` gives, without building the object)."""
+    get = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    return get(dev.index or 0) if get is not None else torch.cuda.current_stream(dev).cuda_stream
+
+
+def _launch_path(lib, q, k, v, q_scale, k_scale, v_scale, out, path, splits, stream, check, flags, v_blockscale, lse, B, S, H, SK, HK, record=None):
     sizes = _abi.BufferSizes(ptr_q=_nbytes(q), ptr_k=_nbytes(k), ptr_v=_nbytes(v), ptr_o=_nbytes(out), ptr_q_descale=_nbytes(q_scale),
                              ptr_k_descale=_nbytes(k_scale), ptr_v_descale=_nbytes(v_scale))
     syms = _abi.Symbols(B=B, HK=HK, KL=0)
     if path in ("vs128", "t128"):
         rows = 256 if path == "vs128" else 128
         a = fill_common(_abi.AttnArgs(), q, k, v, q_scale, k_scale, v_scale, out, B, S, H, SK, HK, flags & ~_abi.FLAG_FUSED_COMBINE, v_blockscale, lse)
-        _check_launch(lib, PATH_IDS[path], a, sizes, _abi.grid3(math.ceil(S / rows), H, B), syms, stream, check)
+        _check_launch(lib, PATH_IDS[path], a, sizes, _abi.grid3(math.ceil(S / rows), H, B), syms, stream, check, record)
         return path, 0
     if path != "kvsplit" or splits not in (2, 4, 8):
         raise ValueError(f"fmha_fwd_mxfp8: unknown path {path!r} / splits {splits}")
@@ -151,21 +194,24 @@ def _launch_path(lib, q, k, v, q_scale, k_scale, v_scale, out, path, splits, str
     sizes.ptr_ohat, sizes.ptr_lse = splits * rows_total * D * 4, splits * rows_total * 4
     if flags & _abi.FLAG_FUSED_COMBINE:
         a.ext_ptr_fused_counters = _ws("fused_counters", 4 * B * H * math.ceil(S / 128), q.device, stream, zero=True).data_ptr()
-    _check_launch(lib, KVSPLIT, a, sizes, _abi.grid3(math.ceil(S / 256), H, B * splits), syms, stream, check)
+    _check_launch(lib, KVSPLIT, a, sizes, _abi.grid3(math.ceil(S / 256), H, B * splits), syms, stream, check, record)
     if flags & _abi.FLAG_FUSED_COMBINE:
         return path, splits
     c = _abi.CombineArgs(ptr_ohat=ohat.data_ptr(), ptr_lse=lse_ws.data_ptr(), ptr_out=out.data_ptr(), rows_total=rows_total, d=D, splits=splits)
     csizes = _abi.BufferSizes(ptr_ohat=sizes.ptr_ohat, ptr_lse=sizes.ptr_lse, ptr_out=_nbytes(out))
     cgrid = max(1, math.ceil(rows_total * D / (256 * 8)))
-    _check_launch(lib, COMBINE8H, c, csizes, _abi.grid3(cgrid, 1, 1), None, stream, check)
+    _check_launch(lib, COMBINE8H, c, csizes, _abi.grid3(cgrid, 1, 1), None, stream, check, record)
     return path, splits
 
 
 def reset_workspaces():
     """Drops the cached KV-split workspaces (partials, log-sum-exps, the fused merge's counters) after a synchronise; the next call makes new ones."""
     import torch
+    global _ws_generation
     torch.cuda.synchronize()
     _workspace.clear()
+    _calls.clear()
+    _ws_generation += 1
 
 
 def device_status() -> int:
