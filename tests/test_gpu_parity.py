@@ -284,3 +284,34 @@ def test_stress_repeated_split_launches(oracle):
     for _ in range(100):
         _, o = dev.run("auto", poison=False)
         assert np.array_equal(o, first)
+
+
+def test_remembered_calls_replay_the_same_launches(oracle):
+    """The Python entry remembers a call by its tensors' addresses, shapes and options and replays its launches: the replay gives the
+    same bytes (split path included, whose workspaces the remembered argument blocks point into), a view that is not contiguous is
+    still refused although its address and shape are known, another stream makes another entry, and dropping the workspaces drops
+    the remembered calls with them."""
+    from amdgpu_rustdsl_b200 import fmha_fwd_mxfp8, ops
+    inp = oracle.generate("normal", 1, 4, 384, 2048, 2)
+    dev = Device(inp)
+    for path, splits in (("vs128", None), ("kvsplit", 4)):
+        (_, _), first = dev.run(path, splits)
+        n_known = len(ops._calls)
+        (_, _), again = dev.run(path, splits)
+        assert len(ops._calls) == n_known and np.array_equal(first, again)
+    # same address and shape, other strides: [1, 384, 4, 128] seen through a transposed [1, 4, 384, 128] buffer
+    base = torch.empty(1, 4, 384, 128, dtype=torch.bfloat16, device="cuda")
+    out_t = base.transpose(1, 2)
+    assert out_t.shape == dev.out.shape and not out_t.is_contiguous()
+    fmha_fwd_mxfp8(dev.q, dev.k, dev.v, dev.qs, dev.ks, dev.vs, base.view(1, 384, 4, 128), path="vs128")   # the address becomes known
+    with pytest.raises(ValueError):
+        fmha_fwd_mxfp8(dev.q, dev.k, dev.v, dev.qs, dev.ks, dev.vs, out_t, path="vs128")
+    side = torch.cuda.Stream()
+    n_known = len(ops._calls)
+    with torch.cuda.stream(side):
+        (_, _), on_side = dev.run("kvsplit", 4)
+    assert len(ops._calls) == n_known + 1 and np.array_equal(on_side, first)
+    ops.reset_workspaces()
+    assert not ops._calls
+    (_, _), fresh = dev.run("kvsplit", 4)
+    assert np.array_equal(fresh, first)
