@@ -64,8 +64,8 @@ constexpr int kThreads = 32 * (4 + 8 + 4);   // 4 service warps, 8 softmax warps
 // epilogue warpgroups give most of theirs back and the two softmax warpgroups take them.
 #ifndef MXA_SERVICE_REGS
 #define MXA_SERVICE_REGS 56
-#define MXA_SOFTMAX_REGS 200
-#define MXA_EPILOGUE_REGS 56
+#define MXA_SOFTMAX_REGS 176
+#define MXA_EPILOGUE_REGS 104
 #endif
 constexpr int kMaxRegs = 128;
 constexpr int kServiceRegs = MXA_SERVICE_REGS, kSoftmaxRegs = MXA_SOFTMAX_REGS, kEpilogueRegs = MXA_EPILOGUE_REGS;
@@ -994,16 +994,11 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             if (half_out) {
                 // bf16 output, or the split kernel's f16 partial (the reference's partial format, block3.rs:291-356): four 32-column
                 // chunks, all staged before the stores go out; O is free after the last read
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t o[32];
-                    tmem_ld32(t_o + 32 * c, o);
-                    tmem_wait_ld();
-                    if (c == 3) {
-                        tc_fence_before_sync();
-                        mbar_arrive(bar_o_free);   // O and L are out: the next item's first P V may overwrite them
-                        stamp(ep_trace, 3, 24 + static_cast<int>(n), 5);
-                    }
+                // Two chunks are in flight at a time: the read-out of O, which the next item's first P V waits for (o_free), then takes two
+                // tensor-memory round trips and the conversion of two chunks instead of four and three (this warpgroup only gets an
+                // instruction issued every few dozen clocks while the softmax warps of its scheduler run, so what stands between o_full
+                // and o_free is counted in instructions)
+                auto process = [&](int c, uint32_t (&o)[32]) {
                     if (dumping) {
 #pragma unroll
                         for (int e = 0; e < 32; ++e) p.trace[16384 + r * 128 + 32 * c + e] = __uint_as_float(o[e]);
@@ -1039,7 +1034,21 @@ mxfp8_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(tile_base + ((chunk ^ (r & 7u)) << 4)),
                                      "r"(wv[0]), "r"(wv[1]), "r"(wv[2]), "r"(wv[3]) : "memory");
                     }
-                }
+                };
+                uint32_t oa[32], ob[32];
+                tmem_ld32(t_o, oa);
+                tmem_ld32(t_o + 32, ob);
+                tmem_wait_ld();
+                process(0, oa);
+                tmem_ld32(t_o + 64, oa);
+                process(1, ob);
+                tmem_ld32(t_o + 96, ob);
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                mbar_arrive(bar_o_free);   // O and L are out: the next item's first P V may overwrite them
+                stamp(ep_trace, 3, 24 + static_cast<int>(n), 5);
+                process(2, oa);
+                process(3, ob);
                 fence_proxy_async_smem();
                 named_bar_sync(kEpiBar, 128u);
                 if (issuer) {
