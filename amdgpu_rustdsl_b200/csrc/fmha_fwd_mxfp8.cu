@@ -11,7 +11,7 @@
 //   out    : O * v_descale / l as bf16 (state.rs:79-82), or for the split kernel the normalised f32 partial plus a base-2
 //            log-sum-exp per row (block3.rs:291-356).
 //
-// Mapping onto the SM (not a translation of the gfx950 wave layout): a persistent kernel, one CTA of 12 warps per SM, each CTA walking
+// Mapping onto the SM (not a translation of the gfx950 wave layout): a persistent kernel, one CTA of 16 warps per SM, each CTA walking
 // work items (128 query rows of one (batch, head[, split])) with its rings, buffers and barriers running on across items.
 // The four service warps run their loops with all 32 lanes in step on warp-uniform values and let an elected lane issue the tcgen05 /
 // TMA instructions (operands then stay in uniform registers).
@@ -27,13 +27,17 @@
 //              scheduler with softmax warps only gets an instruction in every few clocks.
 //   warp  3    V producer: TMA loads of the V ring (K is freed after Q K^T, V after P V, so the two rings run apart), and the K scale
 //              gathers of the tiles with an odd counter.
-//   warps 4-11 softmax + epilogue, two warpgroups: warpgroup p works on the tiles with
-//              counter g = p (mod 2). Thread r of a group owns query row r = TMEM lane r: it reads the row's 128 scores with one
-//              tensor-memory round trip and hands the S buffer back at once, takes the row's reference from the group of the previous
-//              tile through an 8-byte shared-memory slot {value, tile counter}, converts in place, writes P (packed e4m3) with
-//              tcgen05.st, and rescales O in TMEM on the rare tiles that move the reference. 12 warps start with 168 registers per thread;
-//              the service warps then drop to 80 and the softmax warps rise to 208 (setmaxnreg).
-//              The output tile leaves through shared memory and one TMA store per warpgroup.
+//   warps 4-11 softmax, two warpgroups: warpgroup p works on the tiles with counter g = p (mod 2). Thread r of a group owns query row
+//              r = TMEM lane r: it reads the row's 128 scores with one tensor-memory round trip and hands the S buffer back at once,
+//              takes the row's reference from the group of the previous tile through an 8-byte shared-memory slot {value, tile
+//              counter}, converts in place, writes P (packed e4m3) with tcgen05.st, and rescales O in TMEM on the rare tiles that move
+//              the reference.
+//   warps 12-15 epilogue, one warpgroup: takes an item's O and row sums out of tensor memory when its last P V is done, hands the
+//              columns back (the next item's first P V waits for that), normalises, stages the tile in shared memory and stores it
+//              with TMA (bf16 output, or the split kernel's partial), while the softmax warpgroups are on the next item's tiles.
+//              Merges the two halves of an item cut between a pair of CTAs; in the fused instantiations merges a row block's partials.
+//   Every thread starts with 128 registers; the service warps then keep 56, the softmax warps take 176 and the epilogue warps 104
+//   (setmaxnreg: the roles' shares must come out of the CTA's launch allocation).
 // TMEM columns: S0 [0,128) S1 [128,256) O [256,384) L [384,400) P0 [400,432) P1 [432,464) SFQ [464,468) SFK0 [468,472) SFK1 [472,476).
 #include "kernels.h"
 #include "ptx_sm100.cuh"
@@ -56,8 +60,8 @@ constexpr int kStages = 4;          // depth of the K ring and of the V ring (fr
 // The four service warps get the lowest warp ids, one per scheduler (scheduler = warp % 4). Softmax = warps 4-19: a warp's TMEM lane
 // quadrant is warp % 4, so any four consecutive warps cover the 128 rows.
 constexpr int kMmaWarp = 0, kKProducerWarp = 1, kPvWarp = 2, kVProducerWarp = 3, kFirstSoftmaxWarp = 4, kFirstEpilogueWarp = 12;
-// A softmax thread owns a whole score row of a tile: 128 scores in registers, read from tensor memory once. 4 service + 8 softmax warps;
-// the register file is 16 K registers per scheduler, so three warps per scheduler get 168 registers each.
+// A softmax thread owns a whole score row of a tile: 128 scores in registers, read from tensor memory once. 4 service + 8 softmax + 4
+// epilogue warps: every scheduler has one service, two softmax and one epilogue warp and 16 K registers to deal out among them.
 constexpr int kCols = 128;                  // score columns per softmax thread
 constexpr int kThreads = 32 * (4 + 8 + 4);   // 4 service warps, 8 softmax warps, 4 epilogue warps
 // The register file (64 K registers) is dealt out unevenly once the roles part: every thread starts with kMaxRegs, the service and the
